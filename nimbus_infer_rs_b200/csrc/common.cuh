@@ -1,0 +1,127 @@
+// Shared declarations of the sm_100a kernel library.
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers plus the CUDA
+// stream to launch on, and returns 0 or an error code; the text of the last error of
+// the calling thread is available through nb_last_error().  Nothing in this library
+// allocates device memory: callers pass inputs, outputs and scratch.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define NB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Element types of tensors handed to launchers.
+enum NbDType : int { NB_F32 = 0, NB_BF16 = 1 };
+// Activation applied in a matrix product's epilogue.
+enum NbAct : int { NB_ACT_NONE = 0, NB_ACT_GELU_TANH = 1, NB_ACT_GELU_ERF = 2 };
+
+// Error codes above the range of cudaError_t.
+#define NB_ERR_BAD_ARG 10001
+#define NB_ERR_UNSUPPORTED 10002
+#define NB_ERR_DEVICE_FLAG 10003
+
+void nb_set_error(const char* fmt, ...);
+
+#define NB_REQUIRE(cond, code, ...)                                                     \
+  do {                                                                                  \
+    if (!(cond)) {                                                                      \
+      nb_set_error(__VA_ARGS__);                                                        \
+      return (code);                                                                    \
+    }                                                                                   \
+  } while (0)
+
+#define NB_CHECK_LAUNCH(name)                                                           \
+  do {                                                                                  \
+    cudaError_t e__ = cudaGetLastError();                                               \
+    if (e__ != cudaSuccess) {                                                           \
+      nb_set_error("%s: launch failed: %s", (name), cudaGetErrorString(e__));           \
+      return (int)e__;                                                                  \
+    }                                                                                   \
+  } while (0)
+
+#define NB_CUDA(call)                                                                   \
+  do {                                                                                  \
+    cudaError_t e__ = (call);                                                           \
+    if (e__ != cudaSuccess) {                                                           \
+      nb_set_error("%s: %s", #call, cudaGetErrorString(e__));                           \
+      return (int)e__;                                                                  \
+    }                                                                                   \
+  } while (0)
+
+// ---------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ float nb_to_f32(float v) { return v; }
+__device__ __forceinline__ float nb_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T nb_from_f32(float v);
+template <>
+__device__ __forceinline__ float nb_from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 nb_from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// GELU, tanh form: 0.5 x (1 + tanh(0.79788456 (x + 0.044715 x^3)))  (src/ops.rs:21-24)
+__device__ __forceinline__ float nb_gelu_tanh(float x) {
+  const float c = 0.7978845608028654f;
+  return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+// GELU, exact form: 0.5 x (1 + erf(x / sqrt 2))
+__device__ __forceinline__ float nb_gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float nb_apply_act(float x, int act) {
+  if (act == NB_ACT_GELU_TANH) return nb_gelu_tanh(x);
+  if (act == NB_ACT_GELU_ERF) return nb_gelu_erf(x);
+  return x;
+}
+
+__device__ __forceinline__ float nb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float nb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum / max for blocks of up to 1024 threads; `red` holds 32 floats.
+__device__ __forceinline__ float nb_block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = nb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? red[lane] : 0.0f;
+  return nb_warp_sum(t);
+}
+__device__ __forceinline__ float nb_block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = nb_warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? red[lane] : -INFINITY;
+  return nb_warp_max(t);
+}
+
+// The paged key/value store of one layer: pages of `page` tokens, each
+// [n_kv_heads][page][head_dim]; a sequence's pages are listed in its row of the block table.
+struct NbPagedKV {
+  void* k;                  // [n_pages][n_kv_heads][page][head_dim]
+  void* v;
+  const int* block_table;   // [n_slots][max_pages]
+  int max_pages;
+  int page;                 // tokens per page
+  int n_kv_heads;
+  int head_dim;
+};

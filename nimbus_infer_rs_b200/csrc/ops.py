@@ -1,0 +1,189 @@
+"""Tensor-level face of the kernel library.
+
+Each function checks its tensors and hands raw pointers plus the current CUDA stream to one
+``extern "C"`` launcher of ``libnimbus_b200.so``.  There is no other implementation in the
+package: if the library cannot be built or loaded, the first call raises.
+
+The functions go through a backend object so that a test can drive the engine's host logic
+(batching, paging, slots) with a stand-in of its own; the package itself only ever
+installs :class:`CudaBackend`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_void_p
+
+import torch
+
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[t]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t}") from None
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor, got device {t.device}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: expected a contiguous tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name}: expected {ndim} dimensions, got {t.dim()}")
+
+
+class CudaBackend:
+    """Calls into the compiled library."""
+
+    name = "cuda"
+
+    def __init__(self):
+        from . import build
+        self.lib = build.load()
+        self.lib.nb_last_error.restype = ctypes.c_char_p
+        self.launches = 0  # kernels launched through this backend (for measurement reports)
+
+    # -- plumbing ---------------------------------------------------------------------
+    def _stream(self) -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _call(self, fn_name: str, *args) -> None:
+        rc = getattr(self.lib, fn_name)(*args)
+        self.launches += 1
+        if rc != 0:
+            msg = self.lib.nb_last_error().decode("utf-8", "replace")
+            raise KernelError(f"{fn_name} failed ({rc}): {msg}")
+
+    # -- row-wise ---------------------------------------------------------------------
+    def embed_pos(self, tokens, pos, wte, wpe, out):
+        _check(tokens, "tokens", torch.int32, 1)
+        _check(pos, "pos", torch.int32, 1)
+        _check(wte, "wte", None, 2)
+        _check(out, "out", torch.float32, 2)
+        if wpe is not None:
+            _check(wpe, "wpe", wte.dtype, 2)
+        n, d = out.shape
+        if tokens.numel() < n or pos.numel() < n or wte.shape[1] != d:
+            raise KernelError("embed_pos: shapes do not agree")
+        self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
+                   c_int(dtype_code(wte.dtype)), _ptr(out), c_int(n), c_int(d), self._stream())
+
+    def layernorm(self, x, gamma, beta, eps, out, rows=None):
+        _check(x, "x", torch.float32, 2)
+        _check(gamma, "gamma", torch.float32, 1)
+        if beta is not None:
+            _check(beta, "beta", torch.float32, 1)
+        _check(out, "out", None, 2)
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+        n, d = out.shape
+        if x.shape[1] != d or gamma.numel() != d or (rows is None and x.shape[0] < n):
+            raise KernelError("layernorm: shapes do not agree")
+        self._call("nb_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
+                   c_int(dtype_code(out.dtype)), c_int(n), c_int(d), c_float(eps), self._stream())
+
+    # -- matrix products --------------------------------------------------------------
+    def linear(self, x, w, bias, out, act=ACT_NONE, residual=None):
+        """out = act(x @ w.T + bias) (+ residual).  x [M,K], w [N,K], out [M,N]."""
+        _check(x, "x", None, 2)
+        _check(w, "w", None, 2)
+        _check(out, "out", None, 2)
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError(f"linear: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, "
+                              f"out {tuple(out.shape)}")
+        if bias is not None:
+            _check(bias, "bias", torch.float32, 1)
+            if bias.numel() != N:
+                raise KernelError("linear: bias length does not match")
+        if residual is not None:
+            _check(residual, "residual", torch.float32, 2)
+            if residual.shape != out.shape:
+                raise KernelError("linear: residual shape does not match")
+        self._call("nb_gemm_simt", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w),
+                   c_int(dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
+                   c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),
+                   self._stream())
+
+    # -- cache and attention ----------------------------------------------------------
+    def kv_append(self, src, k_col, v_col, row_slot, row_pos, kv, n_rows):
+        _check(src, "src", kv.k.dtype, 2)
+        self._call("nb_kv_append", _ptr(src), c_int(dtype_code(src.dtype)), c_int(src.shape[1]),
+                   c_int(k_col), c_int(v_col), _ptr(row_slot), _ptr(row_pos), _ptr(kv.k),
+                   _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),
+                   c_int(kv.page), c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(n_rows),
+                   self._stream())
+
+    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0):
+        """Causal attention of the packed rows of ``layout`` over the cache ``kv``."""
+        _check(q_src, "q", kv.k.dtype, 2)
+        _check(out, "out", None, 2)
+        n_rows = layout.n_rows
+        if out.shape[0] < n_rows or out.shape[1] != n_heads * kv.head_dim:
+            raise KernelError("attention: output shape does not match")
+        self._call("nb_attention_generic", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
+                   c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
+                   _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),
+                   c_int(kv.page), c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim),
+                   _ptr(out), c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
+                   c_int(window), c_int(n_rows), self._stream())
+
+    # -- sampling ---------------------------------------------------------------------
+    def argmax(self, logits, out):
+        _check(logits, "logits", torch.float32, 2)
+        _check(out, "out", torch.int32, 1)
+        n, v = logits.shape
+        self._call("nb_argmax", _ptr(logits), c_int(n), c_int(v), _ptr(out), self._stream())
+
+    def sample_temperature(self, logits, temperature, u, out):
+        _check(logits, "logits", torch.float32, 2)
+        _check(u, "u", torch.float64, 1)
+        _check(out, "out", torch.int32, 1)
+        n, v = logits.shape
+        self._call("nb_sample_temperature", _ptr(logits), c_int(n), c_int(v),
+                   c_float(temperature), _ptr(u), _ptr(out), self._stream())
+
+    def repetition_penalty(self, logits, history, history_len, penalty):
+        _check(logits, "logits", torch.float32, 2)
+        _check(history, "history", torch.int32, 2)
+        _check(history_len, "history_len", torch.int32, 1)
+        n, v = logits.shape
+        self._call("nb_repetition_penalty", _ptr(logits), c_int(n), c_int(v), _ptr(history),
+                   c_int(history.shape[1]), _ptr(history_len), c_float(penalty), self._stream())
+
+
+_backend = None
+
+
+def backend():
+    """The installed backend; the CUDA library is loaded (and built) on first use."""
+    global _backend
+    if _backend is None:
+        if not torch.cuda.is_available():
+            raise KernelError(
+                "no CUDA device: this library runs its models only through its sm_100a kernels "
+                "and has no CPU path")
+        _backend = CudaBackend()
+    return _backend
+
+
+def set_backend(b) -> None:
+    """Install another backend object (tests of host logic) or ``None`` to reset."""
+    global _backend
+    _backend = b

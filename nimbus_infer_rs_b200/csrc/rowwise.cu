@@ -1,0 +1,180 @@
+// Row-wise kernels: token+position embedding, LayerNorm, key/value append into the paged
+// cache.  One thread block per row; any width.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// error text of the calling thread
+// ---------------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+
+void nb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+NB_EXPORT const char* nb_last_error() { return g_error; }
+
+NB_EXPORT int nb_abi_version() { return 1; }
+
+// ---------------------------------------------------------------------------------
+// x[r] = wte[token[r]] + wpe[pos[r]]   (src/model.rs:285-295), fp32 result.
+// A negative token marks a padding row: it is written as zeros.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
+                                 const T* __restrict__ wte, const T* __restrict__ wpe,
+                                 float* __restrict__ out, int d) {
+  const int r = blockIdx.x;
+  const int tok = tokens[r];
+  float* o = out + (size_t)r * d;
+  if (tok < 0) {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.0f;
+    return;
+  }
+  const T* e = wte + (size_t)tok * d;
+  if (wpe != nullptr) {
+    const T* p = wpe + (size_t)pos[r] * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]) + nb_to_f32(p[i]);
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]);
+  }
+}
+
+NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, const void* wpe,
+                           int table_dtype, float* out, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "embed_pos: bad sizes rows=%d d=%d", n_rows, d);
+  const int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
+  if (table_dtype == NB_F32)
+    embed_pos_kernel<float><<<n_rows, threads, 0, stream>>>(tokens, pos, (const float*)wte,
+                                                            (const float*)wpe, out, d);
+  else if (table_dtype == NB_BF16)
+    embed_pos_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+        tokens, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d);
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "embed_pos: unknown table dtype %d", table_dtype);
+  NB_CHECK_LAUNCH("embed_pos");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// LayerNorm of fp32 rows (src/ops.rs:32-40): mean, biased variance of (x - mean), both in
+// fp32 and in two passes; y = (x - mean) / sqrt(var + eps) * gamma + beta.
+// `rows` (optional) selects the source row of each output row; a negative entry gives zeros.
+// The row is kept in shared memory between the passes.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 TOut* __restrict__ out, int d, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  TOut* o = out + (size_t)r * d;
+  if (src < 0) {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_from_f32<TOut>(0.0f);
+    return;
+  }
+  const float* xr = x + (size_t)src * d;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i];
+    row[i] = v;
+    s += v;
+  }
+  const float mean = nb_block_sum(s, red) / (float)d;
+  float q = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float c = row[i] - mean;
+    q += c * c;
+  }
+  const float var = nb_block_sum(q, red) / (float)d;
+  const float inv = 1.0f / sqrtf(var + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float y = (row[i] - mean) * inv * gamma[i];
+    if (beta) y += beta[i];
+    o[i] = nb_from_f32<TOut>(y);
+  }
+}
+
+NB_EXPORT int nb_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
+                           void* out, int out_dtype, int n_rows, int d, float eps,
+                           cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "layernorm: bad sizes rows=%d d=%d", n_rows, d);
+  const size_t smem = (size_t)d * sizeof(float);
+  NB_REQUIRE(smem <= 200 * 1024, NB_ERR_UNSUPPORTED,
+             "layernorm: width %d needs %zu bytes of shared memory (limit 204800)", d, smem);
+  const int threads = d >= 1024 ? 256 : (d >= 256 ? 128 : 64);
+  if (out_dtype == NB_F32) {
+    if (smem > 48 * 1024)
+      NB_CUDA(cudaFuncSetAttribute(layernorm_kernel<float>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (float*)out,
+                                                               d, eps);
+  } else if (out_dtype == NB_BF16) {
+    if (smem > 48 * 1024)
+      NB_CUDA(cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(
+        x, rows, gamma, beta, (__nv_bfloat16*)out, d, eps);
+  } else {
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "layernorm: unknown output dtype %d", out_dtype);
+  }
+  NB_CHECK_LAUNCH("layernorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Append this step's keys and values to the paged cache (src/cache.rs:44-57 writes rows
+// P..P+T of every head).  Row r of `src` holds [.. | K: n_kv_heads*head_dim | V: same ..]
+// starting at column k_col / v_col; it goes to token `pos[r]` of sequence slot `slot[r]`.
+// Rows with a negative slot are padding and are skipped.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ src, int src_stride, int k_col, int v_col,
+                                 const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                 NbPagedKV kv) {
+  const int r = blockIdx.x;
+  const int slot = row_slot[r];
+  if (slot < 0) return;
+  const int pos = row_pos[r];
+  const int page_id = kv.block_table[(size_t)slot * kv.max_pages + pos / kv.page];
+  const int in_page = pos % kv.page;
+  const int width = kv.n_kv_heads * kv.head_dim;
+  const T* srow = src + (size_t)r * src_stride;
+  T* kdst = (T*)kv.k;
+  T* vdst = (T*)kv.v;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const int h = i / kv.head_dim, c = i - h * kv.head_dim;
+    const size_t o =
+        (((size_t)page_id * kv.n_kv_heads + h) * kv.page + in_page) * kv.head_dim + c;
+    kdst[o] = srow[k_col + i];
+    vdst[o] = srow[v_col + i];
+  }
+}
+
+NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col, int v_col,
+                           const int* row_slot, const int* row_pos, void* k_cache, void* v_cache,
+                           const int* block_table, int max_pages, int page, int n_kv_heads,
+                           int head_dim, int n_rows, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NbPagedKV kv{k_cache, v_cache, block_table, max_pages, page, n_kv_heads, head_dim};
+  const int width = n_kv_heads * head_dim;
+  const int threads = width >= 256 ? 256 : (width >= 128 ? 128 : 64);
+  if (dtype == NB_F32)
+    kv_append_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)src, src_stride, k_col,
+                                                            v_col, row_slot, row_pos, kv);
+  else if (dtype == NB_BF16)
+    kv_append_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+        (const __nv_bfloat16*)src, src_stride, k_col, v_col, row_slot, row_pos, kv);
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "kv_append: unknown dtype %d", dtype);
+  NB_CHECK_LAUNCH("kv_append");
+  return 0;
+}

@@ -1,0 +1,160 @@
+// Token selection on the device: repetition penalty, greedy argmax, temperature sampling.
+// One thread block per sequence; any vocabulary size.
+//
+// Reference (src/sampler.rs:163-217): logits are widened to f64; the penalty is applied
+// first (:83-101); greedy takes the first index of the maximum (:172-180); otherwise the
+// logits are divided by max(T, 1e-6), softmax is taken in f64 and the token is found by
+// walking the cumulative sum until u * total is used up (:201-216).
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+// For each distinct token of the sequence's history: logit > 0 ? logit / penalty
+// : logit * penalty  (src/sampler.rs:83-101).  A token that occurs several times is
+// penalised once: only its first occurrence acts.
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
+                                          const int* __restrict__ history, int history_stride,
+                                          const int* __restrict__ history_len, float penalty) {
+  const int r = blockIdx.x;
+  const int n = history_len[r];
+  const int* hist = history + (size_t)r * history_stride;
+  float* row = logits + (size_t)r * vocab;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int tok = hist[i];
+    if (tok < 0 || tok >= vocab) continue;
+    bool first = true;
+    for (int j = 0; j < i; ++j)
+      if (hist[j] == tok) { first = false; break; }
+    if (!first) continue;
+    const float v = row[tok];
+    row[tok] = (v > 0.0f) ? (float)((double)v / (double)penalty) : (float)((double)v * (double)penalty);
+  }
+}
+
+// First index of the maximum: an element replaces the best only if it is strictly greater
+// (src/sampler.rs:173-179), so NaN never wins and ties go to the lower index.
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+  __shared__ float s_val[THREADS];
+  __shared__ int s_idx[THREADS];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  // every thread starts from element 0, as the reference's scan does
+  float best = row[0];
+  int best_i = 0;
+  for (int i = tid; i < vocab; i += THREADS) {
+    const float v = row[i];
+    if (v > best) { best = v; best_i = i; }
+  }
+  s_val[tid] = best;
+  s_idx[tid] = best_i;
+  __syncthreads();
+  for (int off = THREADS / 2; off > 0; off >>= 1) {
+    if (tid < off) {
+      const float v = s_val[tid + off];
+      const int i = s_idx[tid + off];
+      if (v > s_val[tid] || (v == s_val[tid] && i < s_idx[tid])) {
+        s_val[tid] = v;
+        s_idx[tid] = i;
+      }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) out[r] = s_idx[0];
+}
+
+// Temperature sampling by inverse CDF in f64.  u[r] in [0,1) comes from the sequence's own
+// generator on the host.  Each thread owns a contiguous segment of the vocabulary, so the
+// walk over the cumulative sum visits the tokens in index order as the reference does.
+__global__ void __launch_bounds__(THREADS)
+sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
+                          const double* __restrict__ u, int* __restrict__ out) {
+  __shared__ double s_red[THREADS];
+  __shared__ int s_choice;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const double temp = fmax((double)temperature, 1e-6);
+  const int per = (vocab + THREADS - 1) / THREADS;
+  const int i0 = min(tid * per, vocab), i1 = min(i0 + per, vocab);
+
+  double mx = -INFINITY;
+  for (int i = i0; i < i1; ++i) mx = fmax(mx, (double)row[i] / temp);
+  s_red[tid] = mx;
+  __syncthreads();
+  for (int off = THREADS / 2; off > 0; off >>= 1) {
+    if (tid < off) s_red[tid] = fmax(s_red[tid], s_red[tid + off]);
+    __syncthreads();
+  }
+  mx = s_red[0];
+  __syncthreads();
+  if (!isfinite(mx)) {  // all -inf (or NaN): the reference falls back to argmax -> index 0 scan
+    if (tid == 0) {
+      int best = 0;
+      for (int i = 1; i < vocab; ++i)
+        if ((double)row[i] / temp > (double)row[best] / temp) best = i;
+      out[r] = best;
+    }
+    return;
+  }
+  double seg = 0.0;
+  for (int i = i0; i < i1; ++i) seg += exp((double)row[i] / temp - mx);
+  s_red[tid] = seg;
+  if (tid == 0) s_choice = -1;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int t = 0; t < THREADS; ++t) total += s_red[t];
+    if (!isfinite(total) || total <= 0.0) {
+      s_choice = -2;  // the reference returns token 0
+    } else {
+      double rem = u[r] * total;
+      int t = 0;
+      // skip whole segments that the remainder outlasts
+      while (t < THREADS - 1 && rem - s_red[t] > 0.0) { rem -= s_red[t]; ++t; }
+      s_choice = t;
+      s_red[0] = rem;
+    }
+  }
+  __syncthreads();
+  if (s_choice == -2) { if (tid == 0) out[r] = 0; return; }
+  if (tid == s_choice) {
+    double rem = s_red[0];
+    int pick = vocab - 1;
+    for (int i = i0; i < vocab; ++i) {  // may run past the segment on rounding
+      rem -= exp((double)row[i] / temp - mx);
+      if (rem <= 0.0) { pick = i; break; }
+    }
+    out[r] = pick;
+  }
+}
+
+}  // namespace
+
+NB_EXPORT int nb_repetition_penalty(float* logits, int n_rows, int vocab, const int* history,
+                                    int history_stride, const int* history_len, float penalty,
+                                    cudaStream_t stream) {
+  if (n_rows == 0 || penalty == 1.0f) return 0;
+  repetition_penalty_kernel<<<n_rows, 128, 0, stream>>>(logits, vocab, history, history_stride,
+                                                        history_len, penalty);
+  NB_CHECK_LAUNCH("repetition_penalty");
+  return 0;
+}
+
+NB_EXPORT int nb_argmax(const float* logits, int n_rows, int vocab, int* out, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0, NB_ERR_BAD_ARG, "argmax: empty vocabulary");
+  argmax_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, out);
+  NB_CHECK_LAUNCH("argmax");
+  return 0;
+}
+
+NB_EXPORT int nb_sample_temperature(const float* logits, int n_rows, int vocab, float temperature,
+                                    const double* u, int* out, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0, NB_ERR_BAD_ARG, "sample_temperature: empty vocabulary");
+  sample_temperature_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, temperature, u, out);
+  NB_CHECK_LAUNCH("sample_temperature");
+  return 0;
+}

@@ -1,0 +1,168 @@
+"""The engine: a loaded model, its cache, the step function and the generation loop.
+
+Reference analogue: ``Engine`` (src/engine.rs:44-48,71-239,255-293) with ``Model::
+forward_hidden`` / ``logits_last`` (src/model.rs:271-325) as its step.  There one call runs
+one sequence from the cache's single position; here ``step`` runs a batch of sequences, each
+from its own cached length, and returns logits at the rows asked for.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Callable, Sequence
+
+import numpy as np
+import torch
+
+from .. import models  # noqa: F401  (registers the architectures)
+from ..cache import PAGE, CacheError, SequenceCache, pages_for
+from ..config.registry import get_architecture, load_config
+from ..csrc import ops as ops_mod
+from ..sampling import BatchSampler, SamplingParams, SequenceSampler
+from ..weights.loader import find_weight_file, load_params
+from ..weights.safetensors_io import SafeTensorsFile
+from .batch import build_layout
+from .context import StepContext
+from .generate import plan_batches, run_batch, token_budget
+from .model import PRECISIONS, Model, Runtime
+
+
+class Engine:
+    def __init__(self, model: Model, config, *, cache_tokens: int | None = None,
+                 n_slots: int | None = None):
+        self.model = model
+        self.spec = model.spec
+        self.config = config
+        self.rt = model.rt
+        self.ops = ops_mod.backend()
+        if cache_tokens is None:
+            cache_tokens = 8 * self.spec.max_seq_len
+        kv_req, st_req = {}, {}
+        for layer in model.layers:
+            if layer.spec.cache_from is None:
+                r = layer.mixer.cache_request()
+                if r is not None:
+                    kv_req[layer.index] = r
+            s = layer.mixer.state_request()
+            if s is not None:
+                st_req[layer.index] = s
+        self.cache = SequenceCache(kv_req, st_req, cache_tokens=cache_tokens,
+                                   max_seq_len=self.spec.max_seq_len, dtype=self.rt.act_dtype,
+                                   device=self.rt.device, n_slots=n_slots)
+        for layer in model.layers:
+            src = layer.index if layer.spec.cache_from is None else layer.spec.cache_from
+            layer.mixer.attach_cache(self.cache.layer_kv(src), self.cache.layer_state(layer.index))
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def load(cls, model_dir: str | Path, dtype: str = "bfloat16", device: str = "cuda:0", *,
+             cache_tokens: int | None = None, n_slots: int | None = None,
+             cast_weights: bool = False) -> "Engine":
+        """Load ``config.json`` and the weight file of ``model_dir``.  ``dtype``: ``bfloat16``
+        (the serving precision) or ``float32`` (everything in true 32-bit)."""
+        if dtype not in PRECISIONS:
+            raise ValueError(f"dtype must be one of {sorted(PRECISIONS)}, got {dtype!r}")
+        arch, config = load_config(model_dir)
+        rt = Runtime(torch.device(device), PRECISIONS[dtype])
+        spec = arch.build_spec(config)
+        model = Model(spec, rt)
+        with SafeTensorsFile(find_weight_file(model_dir)) as f:
+            plan = arch.weight_plan(config, spec, set(f.names()))
+            params = load_params(model.param_specs(), plan, f, precision=rt.precision,
+                                 device=rt.device, cast_weights=cast_weights)
+        model.bind(params)
+        return cls(model, config, cache_tokens=cache_tokens, n_slots=n_slots)
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ------------------------------------------------------------------ the step function
+    def _check_entries(self, entries):
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        V = self.spec.vocab_size
+        out = []
+        for e in entries:
+            slot, tokens = int(e[0]), e[1]
+            want = e[2] if len(e) > 2 else None
+            arr = np.asarray(tokens)
+            if arr.ndim != 1 or arr.size == 0:
+                raise ValueError(f"slot {slot}: a step needs at least one token per sequence")
+            if not np.issubdtype(arr.dtype, np.integer):
+                raise ValueError(f"slot {slot}: token ids must be integers")
+            if arr.min() < 0 or arr.max() >= V:
+                raise ValueError(f"slot {slot}: token id outside 0..{V - 1}")
+            if want is None:
+                want = [arr.size - 1]
+            want = [int(w) for w in want]
+            for w in want:
+                if not 0 <= w < arr.size:
+                    raise ValueError(f"slot {slot}: wanted place {w} is outside this step's "
+                                     f"{arr.size} tokens")
+            out.append((slot, arr.astype(np.int32), want))
+        return out
+
+    def step(self, entries: Sequence) -> torch.Tensor | None:
+        """Run one step.  ``entries``: ``(slot, tokens, want)`` per sequence; ``tokens`` are the
+        sequence's next tokens (its whole prompt, or one token, or any chunk), ``want`` the
+        places among them whose logits are returned (default: the last).  Only these tokens
+        are run, as one batch, against what earlier steps left in the cache.  Returns fp32
+        logits ``[wanted, vocab]`` in the order of the entries and of ``want``, or ``None``
+        when nothing is wanted.  Everything is checked on the host before the first launch."""
+        entries = self._check_entries(entries)
+        self.cache.reserve([(slot, len(toks)) for slot, toks, _ in entries])
+        pos0 = [self.cache.lens[slot] for slot, _, _ in entries]
+        layout = build_layout(entries, pos0, self.rt.device)
+        ctx = StepContext(self.rt, self.ops, layout, self.model.position, self.cache)
+        logits = self.model.forward(ctx)
+        for slot, toks, _ in entries:
+            self.cache.advance(slot, len(toks))
+        return logits
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | None = None,
+                 on_token: Callable[[int, int, int], None] | None = None,
+                 max_batch: int | None = None) -> list[list[int]]:
+        """Generate for every prompt (token ids); returns the new ids per prompt, the prompt
+        not included.  ``on_token(request_index, token, step)`` is called per sampled token."""
+        params = params or SamplingParams()
+        params.validate()
+        prompts = [list(map(int, p)) for p in prompts]
+        for i, p in enumerate(prompts):
+            if not p:  # src/engine.rs:261-263
+                raise ValueError(f"prompt {i} is an empty token sequence")
+        n_new = [token_budget(len(p), params.max_new_tokens, self.spec.max_seq_len) for p in prompts]
+        free_pages = min(g.pool.n_free for g in self.cache.groups) if self.cache.groups \
+            else self.cache.n_pages
+        batches = plan_batches([len(p) for p in prompts], n_new,
+                               max_batch=max_batch or self.cache.slots.n_free,
+                               cache_pages=free_pages)
+        sampler = BatchSampler(params, self.ops, self.rt.device)
+        seq_samplers = {i: SequenceSampler(params, i) for i in range(len(prompts))}
+        out: list[list[int]] = [[] for _ in prompts]
+        for batch in batches:
+            res = run_batch(self, prompts, batch, params, sampler, seq_samplers, on_token)
+            for i, ids in res.items():
+                out[i] = ids
+        return out
+
+    # ------------------------------------------------------------------ reports
+    def inspect(self) -> dict:
+        """What the reference's ``inspect`` prints (src/main.rs:333-369)."""
+        c = self.config
+        return {
+            "name": getattr(c, "name", "model"), "architecture": self.spec.architecture,
+            "n_params": self.model.n_params(),
+            "weight_mb": round(sum(t.numel() * t.element_size() for t in self.model.params.values()
+                                   if t is not None) / 2 ** 20, 2),
+            "kv_cache_mb": round(self.cache.bytes() / 2 ** 20, 2),
+            "vocab": self.spec.vocab_size, "layers": len(self.spec.layers),
+            "heads": getattr(c, "n_heads", None), "kv_heads": getattr(c, "n_kv_heads", None),
+            "d_model": self.spec.width, "head_dim": getattr(c, "head_dim", None),
+            "max_seq_len": self.spec.max_seq_len, "norm": "layernorm",
+            "activation": getattr(c, "activation", None), "pos": self.spec.position.kind,
+            "dtype": self.rt.precision, "cache_tokens": self.cache.cache_tokens,
+        }

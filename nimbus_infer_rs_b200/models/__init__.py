@@ -1,0 +1,2 @@
+"""Architectures known to the registry.  Importing this package registers them."""
+from . import gpt2  # noqa: F401
