@@ -18,8 +18,8 @@ class SequenceCache:
     def __init__(self, kv_requests: dict[int, KVRequest], state_requests: dict[int, StateRequest],
                  *, cache_tokens: int, max_seq_len: int, dtype: torch.dtype, device,
                  n_slots: int | None = None):
-        """``kv_requests`` / ``state_requests``: per layer index, for layers that keep storage
-        of their own.  ``cache_tokens``: the most tokens live sequences hold at any time, each
+        """``kv_requests`` / ``state_requests``: per schedule entry (a layer that runs twice
+        has two), for entries that keep storage of their own.  ``cache_tokens``: the most tokens live sequences hold at any time, each
         sequence counted in whole pages of 64."""
         if cache_tokens <= 0:
             raise ValueError("cache_tokens must be positive")

@@ -27,6 +27,7 @@ class BatchLayout:
     seq_pos0: torch.Tensor      # int32 [n_seqs]: tokens cached before this step
     seq_lens: list[int]         # host: tokens of each sequence in this step
     seq_pos0_host: list[int]
+    seq_slots_host: list[int]
     max_q_len: int
     max_kv_len: int             # longest sequence after this step
     is_decode: bool             # one token per sequence
@@ -73,7 +74,7 @@ def build_layout(entries, pos0: list[int], device, pad_rows_to: int = 1) -> Batc
         n_rows=n_rows, n_tokens=n_tokens, n_seqs=n_seqs, n_want=n_want,
         tokens=parts[0], row_pos=parts[1], row_slot=parts[2], cu_rows=parts[3],
         seq_slot=parts[4], seq_pos0=parts[5], want_rows=parts[6],
-        seq_lens=lens, seq_pos0_host=list(pos0),
+        seq_lens=lens, seq_pos0_host=list(pos0), seq_slots_host=[int(e[0]) for e in entries],
         max_q_len=max(lens) if lens else 0,
         max_kv_len=max((p + t for p, t in zip(pos0, lens)), default=0),
         is_decode=all(t == 1 for t in lens))

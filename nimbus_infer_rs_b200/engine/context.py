@@ -15,3 +15,7 @@ class StepContext:
     layout: BatchLayout
     position: Any            # the model's position-encoding part
     cache: Any               # SequenceCache
+    # storage of the schedule entry that is running (set by the model before each layer)
+    kv: Any = None           # LayerKV or None
+    state: Any = None        # fp32 [n_slots, n_elements] or None
+    writes_cache: bool = True

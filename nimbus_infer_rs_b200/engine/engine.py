@@ -36,21 +36,12 @@ class Engine:
         self.ops = ops_mod.backend()
         if cache_tokens is None:
             cache_tokens = 8 * self.spec.max_seq_len
-        kv_req, st_req = {}, {}
-        for layer in model.layers:
-            if layer.spec.cache_from is None:
-                r = layer.mixer.cache_request()
-                if r is not None:
-                    kv_req[layer.index] = r
-            s = layer.mixer.state_request()
-            if s is not None:
-                st_req[layer.index] = s
+        kv_req, st_req = model.storage_requests()
+        for entry in range(len(model.run_order)):
+            model.kv_source(entry)          # a bad cache_from fails here, not in a step
         self.cache = SequenceCache(kv_req, st_req, cache_tokens=cache_tokens,
                                    max_seq_len=self.spec.max_seq_len, dtype=self.rt.act_dtype,
                                    device=self.rt.device, n_slots=n_slots)
-        for layer in model.layers:
-            src = layer.index if layer.spec.cache_from is None else layer.spec.cache_from
-            layer.mixer.attach_cache(self.cache.layer_kv(src), self.cache.layer_state(layer.index))
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -70,6 +61,33 @@ class Engine:
             params = load_params(model.param_specs(), plan, f, precision=rt.precision,
                                  device=rt.device, cast_weights=cast_weights)
         model.bind(params)
+        return cls(model, config, cache_tokens=cache_tokens, n_slots=n_slots)
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", *,
+               cache_tokens: int | None = None, n_slots: int | None = None,
+               **random_options) -> "Engine":
+        """A model with seeded random weights, loaded through the same by-name plan as a
+        weight file (nothing is written to disk).  ``config``: a typed configuration or a
+        config.json object."""
+        from ..config.registry import resolve_architecture
+        from ..weights.loader import TensorDict
+        if dtype not in PRECISIONS:
+            raise ValueError(f"dtype must be one of {sorted(PRECISIONS)}, got {dtype!r}")
+        if isinstance(config, dict):
+            arch = resolve_architecture(config)
+            config = arch.config_cls.from_json(config)
+        else:
+            arch = get_architecture(config.architecture)
+        if arch.random_tensors is None:
+            raise ValueError(f"architecture {arch.name!r} has no random-weights mode")
+        rt = Runtime(torch.device(device), PRECISIONS[dtype])
+        spec = arch.build_spec(config)
+        model = Model(spec, rt)
+        source = TensorDict(arch.random_tensors(config, seed, **random_options))
+        plan = arch.weight_plan(config, spec, set(source.names()))
+        model.bind(load_params(model.param_specs(), plan, source, precision=rt.precision,
+                               device=rt.device))
         return cls(model, config, cache_tokens=cache_tokens, n_slots=n_slots)
 
     # ------------------------------------------------------------------ slots

@@ -41,8 +41,6 @@ class Layer:
         self.mixer = build_part("mixer", spec.mixer)
         self.norm_ffn = build_part("norm", spec.norm_ffn)
         self.ffn = build_part("ffn", spec.ffn)
-        if spec.cache_from is not None:
-            self.mixer.writes_cache = False
 
     def parts(self):
         return {"norm_mixer": self.norm_mixer, "mixer": self.mixer,
@@ -105,10 +103,42 @@ class Model:
     def forward_hidden(self, ctx) -> torch.Tensor:
         """The fp32 residual stream after the last scheduled layer, [rows, width]."""
         x = self.embedding.forward(ctx, self.position)
-        for li in self.run_order:
+        for entry, li in enumerate(self.run_order):
             layer = self.layers[li]
+            ctx.kv, ctx.state, ctx.writes_cache = self.storage_of(ctx.cache, entry)
             layer.block.forward(ctx, x, layer)
         return x
+
+    def storage_requests(self):
+        """What each schedule entry keeps per sequence: ``({entry: KVRequest}, {entry:
+        StateRequest})``.  An entry of a layer with ``cache_from`` keeps no keys/values."""
+        kv, st = {}, {}
+        for entry, li in enumerate(self.run_order):
+            layer = self.layers[li]
+            if layer.spec.cache_from is None:
+                r = layer.mixer.cache_request()
+                if r is not None:
+                    kv[entry] = r
+            s = layer.mixer.state_request()
+            if s is not None:
+                st[entry] = s
+        return kv, st
+
+    def kv_source(self, entry: int) -> int:
+        """The schedule entry whose key/value store ``entry`` uses: itself, or the latest
+        earlier run of the layer named by ``cache_from``."""
+        src = self.layers[self.run_order[entry]].spec.cache_from
+        if src is None:
+            return entry
+        for e in range(entry - 1, -1, -1):
+            if self.run_order[e] == src:
+                return e
+        raise ValueError(f"schedule entry {entry}: layer {src}, whose cache it reads, has not "
+                         "run before it")
+
+    def storage_of(self, cache, entry: int):
+        src = self.kv_source(entry)
+        return cache.layer_kv(src), cache.layer_state(entry), src == entry
 
     def logits(self, ctx, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
         """Final norm and head on the selected rows → fp32 [n_rows, vocab]."""

@@ -21,18 +21,15 @@ class CausalSelfAttention(Mixer):
     """
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                 window: int = 0, bias: bool = True, writes_cache: bool = True):
+                 window: int = 0, bias: bool = True):
         self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
         self.head_dim, self.scale, self.window = int(head_dim), float(scale), int(window)
-        self.writes_cache = bool(writes_cache)
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be divisible by n_kv_heads")
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv_heads * self.head_dim
         self.qkv = Linear(self.width, self.q_width + 2 * self.kv_width, bias)
         self.out = Linear(self.q_width, self.width, bias)
-        self.kv = None
-        self.state = None
 
     def children(self):
         return {"qkv": self.qkv, "out": self.out}
@@ -41,12 +38,12 @@ class CausalSelfAttention(Mixer):
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
-        lay = ctx.layout
-        qkv = self.qkv(ctx, h, out_dtype=self.kv.k.dtype)
+        lay, kv = ctx.layout, ctx.kv
+        qkv = self.qkv(ctx, h, out_dtype=kv.k.dtype)
         ctx.position.rotate(ctx, qkv, self)
-        if self.writes_cache:
+        if ctx.writes_cache:
             ctx.ops.kv_append(qkv, self.q_width, self.q_width + self.kv_width, lay.row_slot,
-                              lay.row_pos, self.kv, lay.n_rows)
+                              lay.row_pos, kv, lay.n_rows)
         attn = torch.empty((lay.n_rows, self.q_width), device=h.device, dtype=ctx.rt.act_dtype)
-        ctx.ops.attention(qkv, 0, lay, self.kv, self.n_heads, attn, self.scale, self.window)
+        ctx.ops.attention(qkv, 0, lay, kv, self.n_heads, attn, self.scale, self.window)
         self.out(ctx, attn, residual=residual)

@@ -13,7 +13,8 @@ family         interface
 ``mixer``      ``forward(ctx, h, residual)``: mixes tokens of a sequence; ``residual`` (the
                fp32 stream) receives ``+= mixer(h)``.  Declares what it keeps per sequence
                with ``cache_request()`` (growing keys/values) and ``state_request()``
-               (fixed size), and receives its storage through ``attach_cache``.
+               (fixed size); the storage of the running schedule entry is on the context
+               (``ctx.kv``, ``ctx.state``, ``ctx.writes_cache``).
 ``ffn``        ``forward(ctx, h, residual)``: per-token feed-forward, ``residual += ffn(h)``
 ``block``      ``forward(ctx, x, layer)``: the arrangement of norms, mixer and feed-forward
                around the residual stream of one layer
@@ -115,16 +116,11 @@ class Mixer(Part):
     def state_request(self) -> StateRequest | None:
         return None
 
-    def attach_cache(self, kv, state) -> None:
-        """``kv``: this layer's view of the paged key/value store (or that of the layer it
-        reads from); ``state``: fp32 tensor [n_slots, n_elements] or None."""
-        self.kv = kv
-        self.state = state
-
-    #: False for a mixer that only reads another layer's cache
-    writes_cache: bool = True
-
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
+        """``ctx.kv``: the paged key/value store of this schedule entry (or of the entry it
+        reads from, then ``ctx.writes_cache`` is False); ``ctx.state``: fp32 tensor
+        [n_slots, n_elements] or None.  Storage belongs to the schedule entry, not to the
+        layer: a layer that runs twice keeps two caches."""
         raise NotImplementedError
 
 

@@ -69,6 +69,26 @@ class WeightPlan:
     ignored: set[str] = field(default_factory=set)   # names in the file that are no weights
 
 
+class TensorDict:
+    """In-memory tensors with the reading interface of :class:`SafeTensorsFile`."""
+
+    def __init__(self, tensors: dict, path: str = "<memory>"):
+        self._t = dict(tensors)
+        self.path = path
+
+    def names(self):
+        return sorted(self._t)
+
+    def __contains__(self, name):
+        return name in self._t
+
+    def info(self, name):
+        return self._t[name]          # a tensor has .shape, which is all the loader asks for
+
+    def tensor(self, name):
+        return self._t[name]
+
+
 def find_weight_file(model_dir: str | Path) -> Path:
     d = Path(model_dir)
     for n in WEIGHT_FILE_NAMES:
@@ -115,7 +135,7 @@ def load_params(param_specs: dict[str, ParamSpec], plan: WeightPlan, file: SafeT
         ok = True
         for s in present:
             used.add(s.name)
-            got = file.info(s.name).shape
+            got = tuple(file.info(s.name).shape)
             if got not in s.shapes:
                 want = " or ".join(str(list(x)) for x in s.shapes)
                 wrong.append(f"{s.name} is {list(got)}, expected {want}")

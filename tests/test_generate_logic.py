@@ -1,0 +1,105 @@
+"""The generation loop's decisions, and the loop itself over the engine's host logic with the
+torch-CPU stand-in for the kernels."""
+import pytest
+import torch
+
+import plain_gpt2 as P
+from nimbus_infer_rs_b200 import Engine, SamplingParams
+from nimbus_infer_rs_b200.cache import CacheError
+from nimbus_infer_rs_b200.engine.generate import SequenceProgress, plan_batches, token_budget
+
+
+def test_token_budget():          # src/engine.rs:265-266
+    assert token_budget(10, 64, 1024) == 64
+    assert token_budget(1000, 64, 1024) == 24
+    assert token_budget(1024, 64, 1024) == 0
+    assert token_budget(2000, 64, 1024) == 0
+
+
+def test_sequence_progress_stop_rules():     # src/engine.rs:279-291
+    s = SequenceProgress(0, 5, 3, frozenset({9}))
+    assert s.record(4) and s.record(4) and not s.record(4)      # ends at its last step
+    assert s.generated == [4, 4, 4] and s.finished
+    s = SequenceProgress(0, 5, 8, frozenset({9}))
+    assert s.record(1) and not s.record(9)                        # the stop token is kept
+    assert s.generated == [1, 9]
+    assert SequenceProgress(0, 5, 0, frozenset()).finished        # nothing to generate
+
+
+def test_plan_batches():
+    # by count
+    assert plan_batches([5] * 5, [4] * 5, max_batch=2, cache_pages=100) == [[0, 1], [2, 3], [4]]
+    # by pages: 60+5-1 = 64 tokens -> one page each; 70 -> two pages
+    assert plan_batches([60, 60, 70, 10], [5, 5, 5, 5], max_batch=8, cache_pages=3) == \
+        [[0, 1], [2, 3]]
+    with pytest.raises(ValueError, match="needs"):
+        plan_batches([200], [10], max_batch=1, cache_pages=2)
+    assert plan_batches([], [], max_batch=3, cache_pages=3) == []
+
+
+@pytest.fixture()
+def engine_b(model_dirs, cpu_backend):
+    return Engine.load(model_dirs["B"], dtype="float32", device="cpu", cache_tokens=4 * 64,
+                       n_slots=3)
+
+
+def test_generate_matches_plain_greedy_over_several_batches(engine_b, model_dirs):
+    W = P.PlainWeights(model_dirs["B"])
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (1, 17, 5, 9, 13, 30, 2)]
+    seen = []
+    out = engine_b.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0),
+                            on_token=lambda i, t, s: seen.append((i, t, s)), max_batch=3)
+    want = [P.greedy_generate(W, p, 6) for p in prompts]
+    assert out == want
+    assert engine_b.cache.slots.n_free == 3                      # every slot came back
+    assert all(g_.pool.n_free == g_.pool.n_pages for g_ in engine_b.cache.groups)
+    for i, ids in enumerate(out):                                # callback: (request, token, step)
+        assert [(t, s) for j, t, s in seen if j == i] == [(t, s) for s, t in enumerate(ids)]
+
+
+def test_stop_tokens_end_a_sequence_early_and_the_rest_go_on(engine_b, model_dirs):
+    W = P.PlainWeights(model_dirs["B"])
+    prompts = [[3, 4, 5], [100, 200], [7]]
+    free_run = [P.greedy_generate(W, p, 8) for p in prompts]
+    stop = free_run[1][2]                                        # third token of request 1
+    out = engine_b.generate(prompts, SamplingParams(max_new_tokens=8, temperature=0.0,
+                                                    stop_tokens=[stop]))
+    want = [P.greedy_generate(W, p, 8, stop_tokens=(stop,)) for p in prompts]
+    assert out == want
+    assert len(out[1]) <= 3 and out[1][-1] == stop
+
+
+def test_budget_is_clipped_at_the_context_end(engine_b, model_dirs):
+    W = P.PlainWeights(model_dirs["B"])      # max_seq_len 64
+    prompt = list(range(1, 61))
+    out = engine_b.generate([prompt], SamplingParams(max_new_tokens=50, temperature=0.0))
+    assert len(out[0]) == 4 and out[0] == P.greedy_generate(W, prompt, 50)
+    assert engine_b.generate([list(range(64))], SamplingParams(max_new_tokens=5)) == [[]]
+
+
+def test_empty_prompt_and_bad_tokens_are_errors_before_any_launch(engine_b):
+    with pytest.raises(ValueError, match="empty token sequence"):    # src/engine.rs:261-263
+        engine_b.generate([[1], []])
+    s = engine_b.alloc_slot()
+    launches = engine_b.ops.launches
+    with pytest.raises(ValueError, match="token id outside"):
+        engine_b.step([(s, [1, 1000], None)])
+    with pytest.raises(ValueError, match="wanted place"):
+        engine_b.step([(s, [1, 2], [2])])
+    with pytest.raises(CacheError, match="exceeds the longest"):
+        engine_b.step([(s, list(range(65)), None)])
+    with pytest.raises(CacheError, match="not held"):
+        engine_b.step([(2, [1], None)])
+    assert engine_b.ops.launches == launches and engine_b.cache.lens[s] == 0
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_batch_mates(engine_b):
+    p = SamplingParams(max_new_tokens=5, temperature=0.7, seed=123)
+    a = engine_b.generate([[5, 6, 7], [9]], p)
+    b = engine_b.generate([[5, 6, 7], [9]], p)
+    assert a == b
+    alone = engine_b.generate([[5, 6, 7]], p)
+    assert alone[0] == a[0]                                       # same stream when run alone
+    c = engine_b.generate([[5, 6, 7]], SamplingParams(max_new_tokens=5, temperature=0.7, seed=124))
+    assert c != alone

@@ -1,0 +1,95 @@
+"""Generation through the entry points (Python API, command line) against the plain
+implementation's greedy loop."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_gpt2 as P
+from gpu_helpers import DTYPES, assert_greedy_matches
+from make_golden_lib import WORKLOADS, prompts_for
+from nimbus_infer_rs_b200 import Engine, SamplingParams
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_python_entry_point(model_dirs, name, dtype):
+    W = P.PlainWeights(model_dirs[name])
+    e = Engine.load(model_dirs[name], dtype=dtype, cache_tokens=1024)
+    key = name if name in WORKLOADS else "A"
+    prompts = prompts_for(key, e.spec.vocab_size)
+    n_new = WORKLOADS[key][1]
+    out = e.generate(prompts, SamplingParams(max_new_tokens=n_new, temperature=0.0))
+    assert [len(o) for o in out] == [n_new] * len(prompts)
+    for p, o in zip(prompts, out):
+        assert_greedy_matches(o, W, p, dtype)
+    again = e.generate(prompts, SamplingParams(max_new_tokens=n_new, temperature=0.0))
+    assert again == out                                     # tests/engine.rs:14-23
+    assert e.cache.slots.n_free == e.cache.n_slots
+
+
+def test_golden_greedy_ids_in_32bit(model_dirs):
+    golden = json.loads((ROOT / "tests" / "golden" / "tiny_A.json").read_text())
+    e = Engine.load(model_dirs["A"], dtype="float32", cache_tokens=1024)
+    out = e.generate(golden["prompts"], SamplingParams(max_new_tokens=8, temperature=0.0))
+    assert out == golden["greedy"]
+
+
+def test_more_requests_than_slots_run_as_batches_one_after_another(model_dirs):
+    W = P.PlainWeights(model_dirs["B"])
+    e = Engine.load(model_dirs["B"], dtype="float32", cache_tokens=3 * 64, n_slots=3)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (1, 17, 5, 9, 13, 30, 2)]
+    stop = P.greedy_generate(W, prompts[2], 10)[3]
+    out = e.generate(prompts, SamplingParams(max_new_tokens=10, temperature=0.0, stop_tokens=[stop]))
+    for p, o in zip(prompts, out):
+        assert o == P.greedy_generate(W, p, 10, stop_tokens=(stop,))
+    assert out[2][-1] == stop and len(out[2]) <= 4
+
+
+def test_temperature_top_k_top_p_and_penalty_run_and_are_seeded(model_dirs):
+    e = Engine.load(model_dirs["B"], dtype="float32", cache_tokens=1024)
+    prompts = [[1], list(range(2, 19))]
+    for kw in (dict(temperature=0.7), dict(temperature=0.7, repetition_penalty=1.3),
+               dict(temperature=0.9, top_k=5), dict(temperature=0.9, top_p=0.5),
+               dict(temperature=0.0, repetition_penalty=2.0)):
+        p = SamplingParams(max_new_tokens=12, seed=7, **kw)
+        a = e.generate(prompts, p)
+        assert a == e.generate(prompts, p) and [len(x) for x in a] == [12, 12]
+        assert e.generate(prompts[:1], p)[0] == a[0]       # independent of batch-mates
+    k1 = e.generate(prompts, SamplingParams(max_new_tokens=12, temperature=5.0, top_k=1, seed=3))
+    assert k1 == e.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0))
+
+
+def _cli(*args):
+    return subprocess.run([sys.executable, "-m", "nimbus_infer_rs_b200", *args], cwd=ROOT,
+                          capture_output=True, text=True, timeout=600)
+
+
+def test_command_line(model_dirs):
+    W = P.PlainWeights(model_dirs["A"])
+    r = _cli("generate", "--model", str(model_dirs["A"]), "--ids", "5,17,3", "--max-new-tokens", "6",
+             "--dtype", "float32", "--json")
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout)
+    assert out["prompt_tokens"] == 3 and out["generated_ids"] == P.greedy_generate(W, [5, 17, 3], 6)
+    assert "tok/s]" in r.stderr
+    r = _cli("logits", "--model", str(model_dirs["A"]), "--ids", "5,17,3", "--dtype", "float32")
+    probe = json.loads(r.stdout)
+    ref = P.forward_logits(W, [5, 17, 3])[-1]
+    assert probe["argmax"] == int(torch.argmax(ref))
+    assert abs(probe["sum"] - float(ref.sum())) < 1e-3
+    r = _cli("inspect", "--model", str(model_dirs["A"]))
+    info = json.loads(r.stdout)
+    assert info["layers"] == 2 and info["d_model"] == 64 and info["vocab"] == 512
+    r = _cli("generate", "--model", str(model_dirs["A"]), "--prompt", "hello")
+    assert r.returncode != 0 and "no tokenizer" in r.stderr
+    r = _cli("bench", "--model", str(model_dirs["A"]), "--prefill", "16", "--decode", "4", "--runs", "1")
+    assert r.returncode == 0, r.stderr
+    assert json.loads(r.stdout)["decode_tokens"] == 4

@@ -1,0 +1,281 @@
+"""Each kernel alone against a plain torch fp32 restatement of the same operation, at sizes
+other than the engine's tiny models (odd widths, tails, several pages, grouped heads)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from nimbus_infer_rs_b200.cache import PAGE, LayerKV
+from nimbus_infer_rs_b200.csrc import ops as ops_mod
+from nimbus_infer_rs_b200.engine.batch import build_layout
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return ops_mod.backend()
+
+
+def test_library_is_loaded_from_the_tree(ops):
+    from nimbus_infer_rs_b200.csrc import build
+    assert ops.lib.nb_abi_version() >= 1
+    assert build.build().name == "libnimbus_b200.so"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [48, 100, 768, 1600])
+def test_embed_pos(ops, dtype, d):
+    torch.manual_seed(0)
+    V, Pn, n = 301, 77, 19
+    wte = torch.randn(V, d, device=DEV).to(dtype)
+    wpe = torch.randn(Pn, d, device=DEV).to(dtype)
+    tok = torch.randint(0, V, (n,), device=DEV, dtype=torch.int32)
+    pos = torch.randint(0, Pn, (n,), device=DEV, dtype=torch.int32)
+    tok[5] = -1                                   # a padding row
+    out = torch.full((n, d), 9.0, device=DEV)
+    ops.embed_pos(tok, pos, wte, wpe, out)
+    ref = wte[tok.clamp(min=0).long()].float() + wpe[pos.long()].float()
+    ref[5] = 0
+    assert torch.equal(out, ref)
+    ops.embed_pos(tok, pos, wte, None, out)
+    ref = wte[tok.clamp(min=0).long()].float()
+    ref[5] = 0
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d, eps", [(17, 1e-5), (100, 1e-6), (768, 1e-5), (1600, 3e-5), (5000, 1e-5)])
+def test_layernorm(ops, out_dtype, d, eps):
+    torch.manual_seed(1)
+    n = 23
+    x = torch.randn(n, d, device=DEV) * 3 + 0.7
+    x[3] *= 1e3                                    # large mean and spread
+    g = torch.randn(d, device=DEV)
+    b = torch.randn(d, device=DEV)
+    out = torch.empty(n, d, device=DEV, dtype=out_dtype)
+    ops.layernorm(x, g, b, eps, out)
+    xd = x.double()
+    mean = xd.mean(-1, keepdim=True)
+    var = ((xd - mean) ** 2).mean(-1, keepdim=True)
+    ref = (xd - mean) / torch.sqrt(var + eps) * g.double() + b.double()
+    tol = 1e-5 if out_dtype == torch.float32 else 8e-3
+    assert ((out.double() - ref).abs() <= tol * (1 + ref.abs())).all()
+    # row selection, with a padding entry
+    rows = torch.tensor([4, -1, 0, 22], device=DEV, dtype=torch.int32)
+    sel = torch.empty(4, d, device=DEV, dtype=out_dtype)
+    ops.layernorm(x, g, b, eps, sel, rows)
+    assert torch.equal(sel[0], out[4]) and torch.equal(sel[2], out[0]) and torch.equal(sel[3], out[22])
+    assert (sel[1] == 0).all()
+
+
+def _gelu(y, act):
+    if act == 1:
+        return 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+    if act == 2:
+        return 0.5 * y * (1 + torch.erf(y / math.sqrt(2.0)))
+    return y
+
+
+LINEAR_SHAPES = [(1, 64, 64), (5, 1001, 96), (33, 130, 100), (130, 257, 72), (64, 768, 3072),
+                 (300, 2304, 768), (7, 50257, 64), (2048, 96, 320)]
+
+
+@pytest.mark.parametrize("M, N, K", LINEAR_SHAPES)
+@pytest.mark.parametrize("xdt, wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.float32)])
+def test_linear_against_float64(ops, M, N, K, xdt, wdt):
+    torch.manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device=DEV).to(xdt)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(wdt)
+    bias = torch.randn(N, device=DEV)
+    ref0 = x.double() @ w.double().t()
+    scale = float(ref0.abs().max())
+    tol = 3e-6 * scale * math.sqrt(K / 64)          # fp32 accumulation of K exact products
+    # plain product, fp32 out
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(x, w, None, out)
+    assert (out.double() - ref0).abs().max() <= tol
+    # bias + activation, output in the activation type
+    for act in (1, 2):
+        ref = _gelu(ref0 + bias.double(), act)
+        o = torch.empty(M, N, device=DEV, dtype=xdt)
+        ops.linear(x, w, bias, o, act)
+        t = tol if xdt == torch.float32 else tol + 8e-3 * float(ref.abs().max())
+        assert (o.double() - ref).abs().max() <= t
+    # bias + residual, in place on the fp32 stream
+    res = torch.randn(M, N, device=DEV)
+    ref = ref0 + bias.double() + res.double()
+    stream = res.clone()
+    ops.linear(x, w, bias, stream, 0, stream)
+    assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
+
+
+def _paged_cache(n_seqs, lens, Hk, hd, dtype, seed, extra_pages=3):
+    """A cache with shuffled pages, filled with random keys/values for the given lengths."""
+    g = torch.Generator().manual_seed(seed)
+    max_pages = max(-(-l // PAGE) for l in lens) + 1
+    n_pages = sum(-(-l // PAGE) for l in lens) + extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(n_seqs + 2, max_pages, dtype=torch.int32)
+    k = torch.randn(n_pages, Hk, PAGE, hd, generator=g).to(dtype)     # stale data everywhere
+    v = torch.randn(n_pages, Hk, PAGE, hd, generator=g).to(dtype)
+    dense_k, dense_v = [], []
+    it = iter(perm)
+    for s, l in enumerate(lens):
+        ks = torch.randn(l, Hk, hd, generator=g).to(dtype)
+        vs = torch.randn(l, Hk, hd, generator=g).to(dtype)
+        dense_k.append(ks)
+        dense_v.append(vs)
+        for p in range(-(-l // PAGE)):
+            page = next(it)
+            table[s + 1, p] = page                                      # slot = s + 1
+            n = min(PAGE, l - p * PAGE)
+            k[page, :, :n] = ks[p * PAGE:p * PAGE + n].transpose(0, 1)
+            v[page, :, :n] = vs[p * PAGE:p * PAGE + n].transpose(0, 1)
+    kv = LayerKV(k.to(DEV), v.to(DEV), table.to(DEV), PAGE, Hk, hd)
+    return kv, dense_k, dense_v
+
+
+def _attention_ref(q, ks, vs, pos, scale, group, window=0):
+    """q [H, hd] at position pos over dense keys/values [len, Hk, hd] (float64)."""
+    lo = max(0, pos + 1 - window) if window > 0 else 0
+    out = []
+    for h in range(q.shape[0]):
+        kk = ks[lo:pos + 1, h // group].double()
+        vv = vs[lo:pos + 1, h // group].double()
+        s = (kk @ q[h].double()) * scale
+        p = torch.softmax(s, 0)
+        out.append(p @ vv)
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, Hk, hd, window", [(4, 4, 16, 0), (6, 2, 48, 0), (12, 12, 64, 0),
+                                               (5, 1, 128, 0), (3, 3, 32, 70), (2, 2, 256, 0),
+                                               (25, 25, 64, 0)])
+def test_attention_over_paged_cache(ops, dtype, H, Hk, hd, window):
+    """Prefill-like chunks and single decode rows in one launch, sequences of unequal length
+    spanning several shuffled pages, with stale data in the unused part of every page."""
+    lens = [200, 1, 64, 65, 333]
+    new = [200, 1, 3, 1, 40]                     # rows of this step: the last `new` positions
+    kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H * 100 + hd)
+    entries = [(s + 1, [0] * n, []) for s, n in enumerate(new)]
+    pos0 = [l - n for l, n in zip(lens, new)]
+    lay = build_layout(entries, pos0, DEV, pad_rows_to=8)
+    torch.manual_seed(5)
+    width = (H + 2 * Hk) * hd
+    qkv = torch.randn(lay.n_rows, width, device=DEV).to(dtype)
+    out = torch.full((lay.n_rows, H * hd), 7.0, device=DEV, dtype=dtype)
+    scale = 0.37 / math.sqrt(hd)
+    ops.attention(qkv, 0, lay, kv, H, out, scale, window)
+    r = 0
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    for s, n in enumerate(new):
+        for i in range(n):
+            q = qkv[r, :H * hd].view(H, hd).cpu()
+            ref = _attention_ref(q, dk[s], dv[s], pos0[s] + i, scale, H // Hk, window)
+            got = out[r].view(H, hd).double().cpu()
+            assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (s, i)
+            r += 1
+    assert (out[r:] == 0).all()                  # padding rows give zeros
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_far_key_among_hundreds_is_found(ops, dtype):
+    """One key, hundreds of positions back and on another page, is made to dominate."""
+    H, hd, L = 2, 64, 700
+    kv, dk, dv = _paged_cache(1, [L], H, hd, dtype, seed=9)
+    lay = build_layout([(1, [0], [])], [L - 1], DEV)
+    q = torch.randn(1, 3 * H * hd).to(dtype)
+    far = 37
+    for h in range(H):
+        q[0, h * hd:(h + 1) * hd] = (dk[0][far, h].float() * 3.0).to(dtype)   # score stands out
+    out = torch.empty(1, H * hd, device=DEV, dtype=dtype)
+    ops.attention(q.to(DEV), 0, lay, kv, H, out, 1.0, 0)
+    ref = _attention_ref(q[0, :H * hd].view(H, hd), dk[0], dv[0], L - 1, 1.0, 1)
+    assert (ref - dv[0][far].double()).abs().max() < 1e-3          # the far value is the answer
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    assert (out.view(H, hd).double().cpu() - ref).abs().max() <= tol * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_append_writes_only_its_rows(ops, dtype):
+    Hk, hd = 3, 32
+    lens = [130, 5]
+    kv, dk, dv = _paged_cache(2, lens, Hk, hd, dtype, seed=2)
+    k_before, v_before = kv.k.clone(), kv.v.clone()
+    entries = [(1, [0] * 3, []), (2, [0] * 5, [])]       # positions 127..129 (two pages) and 0..4
+    lay = build_layout(entries, [127, 0], DEV, pad_rows_to=16)
+    width = 5 * hd + 2 * Hk * hd
+    src = torch.randn(lay.n_rows, width, device=DEV).to(dtype)
+    ops.kv_append(src, 5 * hd, 5 * hd + Hk * hd, lay.row_slot, lay.row_pos, kv, lay.n_rows)
+    expect_k, expect_v = k_before.clone(), v_before.clone()
+    r = 0
+    for slot, pos0, n in ((1, 127, 3), (2, 0, 5)):
+        for i in range(n):
+            pos = pos0 + i
+            page = int(kv.block_table[slot, pos // PAGE])
+            expect_k[page, :, pos % PAGE] = src[r, 5 * hd:5 * hd + Hk * hd].view(Hk, hd)
+            expect_v[page, :, pos % PAGE] = src[r, 5 * hd + Hk * hd:].view(Hk, hd)
+            r += 1
+    assert torch.equal(kv.k, expect_k) and torch.equal(kv.v, expect_v)
+
+
+def test_argmax_first_maximum(ops):
+    torch.manual_seed(3)
+    logits = torch.randn(9, 50257, device=DEV)
+    logits[0, 77] = logits[0, 40000] = 50.0          # a tie: the lower index wins
+    logits[1, 0] = 60.0
+    logits[2, 50256] = 60.0
+    logits[3, 5] = float("nan")
+    logits[4] = -float("inf")
+    logits[5, 0] = float("nan")                      # the scan starts from a NaN and stays there
+    out = torch.empty(9, device=DEV, dtype=torch.int32)
+    ops.argmax(logits, out)
+    got = out.cpu().tolist()
+    assert got[0] == 77 and got[1] == 0 and got[2] == 50256 and got[4] == 0 and got[5] == 0
+    row3 = logits[3].cpu()
+    row3[5] = -float("inf")
+    assert got[3] == int(torch.argmax(row3))
+    assert got[6:] == torch.argmax(logits[6:], dim=-1).cpu().tolist()
+    small = torch.tensor([[0.1, 5.0, 5.0, -1.0]], device=DEV)     # src/sampler.rs:223-228
+    o = torch.empty(1, device=DEV, dtype=torch.int32)
+    ops.argmax(small, o)
+    assert int(o) == 1
+
+
+def test_temperature_sampling_matches_the_host_sampler(ops):
+    from nimbus_infer_rs_b200.sampling import SamplingParams, Xoshiro256pp
+    from nimbus_infer_rs_b200.sampling import host as H
+    torch.manual_seed(4)
+    V, n = 1000, 64
+    logits = torch.randn(n, V, device=DEV) * 3
+    for temp in (0.7, 1.0, 1e-9):
+        rngs = [Xoshiro256pp(100 + i) for i in range(n)]
+        u = torch.tensor([r.next_f64() for r in rngs], dtype=torch.float64, device=DEV)
+        out = torch.empty(n, device=DEV, dtype=torch.int32)
+        ops.sample_temperature(logits, temp, u, out)
+        rngs = [Xoshiro256pp(100 + i) for i in range(n)]
+        want = [H.sample(logits[i].cpu().numpy(), SamplingParams(temperature=temp), [], rngs[i])
+                for i in range(n)]
+        assert out.cpu().tolist() == want
+    # edges of the cumulative sum
+    two = torch.tensor([[0.0, 0.0, -float("inf")]], device=DEV)
+    o = torch.empty(1, device=DEV, dtype=torch.int32)
+    for uu, w in ((0.0, 0), (0.49, 0), (0.51, 1), (0.999999, 1)):
+        ops.sample_temperature(two, 1.0, torch.tensor([uu], dtype=torch.float64, device=DEV), o)
+        assert int(o) == w
+    ops.sample_temperature(torch.full((1, 7), -float("inf"), device=DEV), 1.0,
+                           torch.tensor([0.3], dtype=torch.float64, device=DEV), o)
+    assert int(o) == 0
+
+
+def test_repetition_penalty(ops):
+    logits = torch.tensor([[2.0, -2.0, 1.0, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
+    hist = torch.tensor([[0, 1, 1, 0], [3, -1, -1, -1]], device=DEV, dtype=torch.int32)
+    lens = torch.tensor([4, 1], device=DEV, dtype=torch.int32)
+    ops.repetition_penalty(logits, hist, lens, 2.0)
+    assert logits.cpu().tolist() == [[1.0, -4.0, 1.0, 3.0], [1.0, 1.0, 1.0, 0.5]]

@@ -37,7 +37,7 @@ RECIPES = {
     "A": (TINY_A, 11, dict(std=0.02, bias_std=0.01, gamma_jitter=0.02, scheme="checkpoint",
                            dtype=torch.bfloat16)),
     "B": (TINY_B, 22, dict(std=0.05, bias_std=0.02, scheme="nimbus", dtype=torch.bfloat16)),
-    "C": (TINY_C, 33, dict(std=0.08, bias_std=0.02, gamma_jitter=0.05, beta_std=0.02,
+    "C": (TINY_C, 33, dict(std=0.05, bias_std=0.02, gamma_jitter=0.05, beta_std=0.02,
                            scheme="nimbus", dtype=torch.float32)),
 }
 
