@@ -144,6 +144,14 @@ class CudaBackend:
                    _ptr(out), c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
                    c_int(window), c_int(n_rows), self._stream())
 
+    def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
+        """tokens <- next_tokens, row_pos += 1 for live rows (between two decode steps)."""
+        for t, n in ((tokens, "tokens"), (next_tokens, "next"), (row_pos, "row_pos"),
+                     (row_slot, "row_slot")):
+            _check(t, n, torch.int32, 1)
+        self._call("nb_advance_decode", _ptr(tokens), _ptr(next_tokens), _ptr(row_pos),
+                   _ptr(row_slot), c_int(tokens.numel()), self._stream())
+
     # -- sampling ---------------------------------------------------------------------
     def argmax(self, logits, out):
         _check(logits, "logits", torch.float32, 2)

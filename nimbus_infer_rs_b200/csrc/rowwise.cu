@@ -178,3 +178,28 @@ NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col
   NB_CHECK_LAUNCH("kv_append");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// Between two decode steps on the device: the sampled token becomes the next input and the
+// position of every live row moves on by one.  Rows with a negative slot are padding.
+// ---------------------------------------------------------------------------------
+__global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ next,
+                                      int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                                      int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (row_slot[i] >= 0) {
+    tokens[i] = next[i];
+    row_pos[i] += 1;
+  } else {
+    tokens[i] = -1;
+  }
+}
+
+NB_EXPORT int nb_advance_decode(int* tokens, const int* next, int* row_pos, const int* row_slot,
+                                int n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, next, row_pos, row_slot, n);
+  NB_CHECK_LAUNCH("advance_decode");
+  return 0;
+}

@@ -1,0 +1,138 @@
+"""Decoding a batch token by token without leaving the device.
+
+A :class:`DecodeSession` holds a batch's decode state in fixed device buffers (the current
+token, position and slot of every row) and runs one step at a time: the model on one token
+per live sequence, token selection on the device, and the hand-over of the selected tokens
+to the next step.  Because every buffer keeps its address and no kernel's launch shape
+depends on the sequences' lengths, the whole step is captured once in a CUDA graph and then
+replayed: a decode step of a small model is bound by launch latency, not by arithmetic.
+
+It runs the same model, parts, cache and kernels as ``Engine.step``; the only additions are
+the in-place token hand-over and the graph.  A sequence that ends becomes a padding row
+(slot -1), which every kernel skips.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.paged import PAGE
+from ..sampling.params import SamplingParams
+from .batch import BatchLayout
+from .context import StepContext
+
+
+class DecodeSession:
+    def __init__(self, engine, slots: list[int], first_tokens: list[int],
+                 params: SamplingParams | None = None, seq_samplers=None, use_graph: bool = True):
+        """``slots``: the live sequences (already prefilled); ``first_tokens``: the token each
+        one runs next.  ``seq_samplers``: per-sequence sampling state (needed unless greedy)."""
+        self.engine = engine
+        self.params = params or SamplingParams(temperature=0.0)
+        self.seq_samplers = seq_samplers
+        self.n = len(slots)
+        self.slots = list(slots)
+        self.live = [True] * self.n
+        dev = engine.rt.device
+        self.use_graph = bool(use_graph) and dev.type == "cuda" and engine.graph_safe
+        n = self.n
+        host = np.zeros(3 * n, dtype=np.int32)
+        host[:n] = first_tokens
+        host[n:2 * n] = [engine.cache.lens[s] for s in slots]
+        host[2 * n:] = slots
+        buf = torch.from_numpy(host).to(dev)
+        self.tokens, self.row_pos, self.row_slot = buf[:n], buf[n:2 * n], buf[2 * n:]
+        self.next_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.want_rows = torch.arange(n, dtype=torch.int32, device=dev)
+        self.cu_rows = torch.arange(n + 1, dtype=torch.int32, device=dev)
+        self.u = torch.zeros(n, dtype=torch.float64, device=dev)
+        self.logits = None
+        self._graph = None
+        self._stage = None
+        self._steps = 0
+        if self.params.repetition_penalty != 1.0 or (
+                not self.params.greedy and (self.params.top_k > 0 or self.params.top_p < 1.0)):
+            raise ValueError("a decode session selects tokens greedily or by temperature only")
+
+    # ------------------------------------------------------------------ one step
+    def _layout(self) -> BatchLayout:
+        n = self.n
+        eng = self.engine
+        return BatchLayout(
+            n_rows=n, n_tokens=n, n_seqs=n, n_want=n, tokens=self.tokens, row_pos=self.row_pos,
+            row_slot=self.row_slot, want_rows=self.want_rows, cu_rows=self.cu_rows,
+            seq_slot=self.row_slot, seq_pos0=self.row_pos, seq_lens=[1] * n,
+            seq_pos0_host=[eng.cache.lens[s] for s in self.slots],
+            seq_slots_host=list(self.slots), max_q_len=1, max_kv_len=eng.spec.max_seq_len,
+            is_decode=True)
+
+    def _device_step(self) -> None:
+        eng = self.engine
+        ctx = StepContext(eng.rt, eng.ops, self._layout(), eng.model.position, eng.cache)
+        self.logits = eng.model.forward(ctx)
+        if self.params.greedy:
+            eng.ops.argmax(self.logits, self.next_tokens)
+        else:
+            eng.ops.sample_temperature(self.logits, float(self.params.temperature), self.u,
+                                       self.next_tokens)
+        eng.ops.advance_decode(self.tokens, self.next_tokens, self.row_pos, self.row_slot)
+
+    def step(self, tokens: list[int] | None = None) -> None:
+        """Run the current token of every live sequence and select its next token (left on the
+        device in ``next_tokens``; ``read_tokens`` brings them to the host).  ``tokens``: the
+        token each row runs in this step, from the host (one per row of the session, any value
+        for rows that have ended); without it the tokens selected by the previous step are
+        used as they lie on the device."""
+        eng = self.engine
+        cache = eng.cache
+        grow = [(s, 1) for s, alive in zip(self.slots, self.live) if alive]
+        if not grow:
+            return
+        if tokens is not None:
+            if self._stage is None:
+                self._stage = torch.empty(self.n, dtype=torch.int32,
+                                          pin_memory=eng.rt.device.type == "cuda")
+            self._stage.copy_(torch.as_tensor(tokens, dtype=torch.int32))
+            self.tokens.copy_(self._stage, non_blocking=True)
+        if any(cache.lens[s] % PAGE == 0 or cache.lens[s] + 1 > cache.max_seq_len for s, _ in grow):
+            cache.reserve(grow)            # a new page somewhere, or an error to raise
+        if not self.params.greedy:
+            us = [self.seq_samplers[i].rng.next_f64() if alive else 0.0
+                  for i, alive in enumerate(self.live)]
+            self.u.copy_(torch.tensor(us, dtype=torch.float64), non_blocking=False)
+        if not self.use_graph or self._steps == 0:
+            self._device_step()            # the first step runs plainly and warms the kernels
+        else:
+            if self._graph is None:
+                self._capture()            # records the step; nothing runs yet
+            launches = eng.ops.launches
+            self._graph.replay()
+            eng.ops.launches = launches + self._graph_launches
+        self._steps += 1
+        for s, _ in grow:
+            cache.advance(s, 1)
+
+    def _capture(self) -> None:
+        eng = self.engine
+        before = eng.ops.launches
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._device_step()
+        self._graph_launches = eng.ops.launches - before
+        eng.ops.launches = before
+        self._graph = graph
+
+    # ------------------------------------------------------------------ host side
+    def read_tokens(self) -> list[int]:
+        """The tokens selected by the last step, on the host (synchronises)."""
+        return self.next_tokens.to("cpu").tolist()
+
+    def retire(self, index: int) -> None:
+        """Sequence ``index`` of the session has ended: its row becomes padding."""
+        if self.live[index]:
+            self.live[index] = False
+            self.row_slot[index:index + 1].fill_(-1)
+
+    @property
+    def n_live(self) -> int:
+        return sum(self.live)

@@ -34,6 +34,7 @@ class Engine:
         self.config = config
         self.rt = model.rt
         self.ops = ops_mod.backend()
+        self.graph_safe = model.graph_safe()
         if cache_tokens is None:
             cache_tokens = 8 * self.spec.max_seq_len
         kv_req, st_req = model.storage_requests()

@@ -87,23 +87,48 @@ def run_batch(engine, prompts: list[list[int]], indices: list[int], params: Samp
     if not live:
         return results
     slots = {s.index: engine.alloc_slot() for s in live}
+
+    def take(seq_list, tokens):
+        """Record one sampled token per sequence; returns those that go on, with their token."""
+        nxt = []
+        for s, tok in zip(seq_list, tokens):
+            if on_token is not None:
+                on_token(s.index, tok, len(s.generated))
+            if s.record(tok):
+                nxt.append((s, tok))
+            else:
+                engine.free_slot(slots.pop(s.index))
+        return nxt
+
     try:
         # the prompts, in one step; logits of each last token
         logits = engine.step([(slots[s.index], prompts[s.index], [s.prompt_len - 1]) for s in live])
-        while True:
-            tokens = sampler.sample(logits, [seq_samplers[s.index] for s in live])
-            nxt = []
-            for s, tok in zip(live, tokens):
-                if on_token is not None:
-                    on_token(s.index, tok, len(s.generated))
-                if s.record(tok):
-                    nxt.append((s, tok))
-                else:
-                    engine.free_slot(slots.pop(s.index))
-            if not nxt:
-                break
-            live = [s for s, _ in nxt]
-            logits = engine.step([(slots[s.index], [tok], [0]) for s, tok in nxt])
+        nxt = take(live, sampler.sample(logits, [seq_samplers[s.index] for s in live]))
+        if nxt and not sampler.needs_host() and params.repetition_penalty == 1.0:
+            # token selection stays on the device: one captured step per token
+            from .decode import DecodeSession
+            members = [s for s, _ in nxt]
+            session = DecodeSession(engine, [slots[s.index] for s in members],
+                                    [tok for _, tok in nxt], params,
+                                    [seq_samplers[s.index] for s in members])
+            alive = list(range(len(members)))
+            tokens = [tok for _, tok in nxt]
+            while alive:
+                session.step(tokens)       # host tokens in ...
+                tokens = session.read_tokens()   # ... and out
+                for i in alive:
+                    seq_samplers[members[i].index].generated.append(tokens[i])
+                going = {s.index for s, _ in take([members[i] for i in alive],
+                                                  [tokens[i] for i in alive])}
+                for i in alive:
+                    if members[i].index not in going:
+                        session.retire(i)
+                alive = [i for i in alive if members[i].index in going]
+        else:
+            while nxt:
+                live = [s for s, _ in nxt]
+                logits = engine.step([(slots[s.index], [tok], [0]) for s, tok in nxt])
+                nxt = take(live, sampler.sample(logits, [seq_samplers[s.index] for s in live]))
     finally:
         for slot in slots.values():
             engine.free_slot(slot)

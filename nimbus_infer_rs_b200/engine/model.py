@@ -83,6 +83,13 @@ class Model:
         if self.spec.tie_head:
             self.head.tie(self.embedding.table)
 
+    def graph_safe(self) -> bool:
+        """True if every part of the model may run under CUDA-graph capture."""
+        parts = [self.embedding, self.position, self.final_norm, self.head]
+        for l in self.layers:
+            parts += [l.block, l.norm_mixer, l.mixer, l.norm_ffn, l.ffn]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def n_params(self) -> int:
         return sum(t.numel() for t in self.params.values() if t is not None)
 

@@ -73,6 +73,10 @@ class Part:
     """Base of all parts."""
     family: str = ""
     kind: str = ""
+    #: True if ``forward`` only launches work on the current CUDA stream from device-resident
+    #: data (no host reads of the batch, no synchronisation), so that a step can be captured
+    #: in a CUDA graph.  A part that does not say so keeps the engine on plain launches.
+    graph_safe: bool = False
 
     def param_specs(self) -> dict[str, ParamSpec]:
         return {}

@@ -8,6 +8,7 @@ from .base import Block, register_part
 class PreNormBlock(Block):
     """``x += mixer(norm_mixer(x)); x += ffn(norm_ffn(x))`` (src/model.rs:297-300 with
     :345-357, :437-439, :448-460, :485-487).  ``x`` is the fp32 residual stream."""
+    graph_safe = True
 
     def __init__(self):
         pass

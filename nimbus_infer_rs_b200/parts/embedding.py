@@ -9,6 +9,7 @@ from .base import MATRIX, TABLE, ParamSpec, Part
 class TokenEmbedding(Part):
     """``x[i] = table[token_i] (+ position_table[pos_i])`` into the fp32 residual stream
     (src/model.rs:285-295)."""
+    graph_safe = True
     family = "embedding"
     kind = "token_embedding"
 
@@ -30,6 +31,7 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     """``logits = h @ W.T`` without bias, fp32 result; ``W`` is the token embedding table when
     tied (src/model.rs:317-325)."""
+    graph_safe = True
     family = "head"
     kind = "lm_head"
 

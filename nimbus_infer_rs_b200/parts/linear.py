@@ -13,6 +13,7 @@ from .base import MATRIX, VECTOR, ParamSpec, Part
 
 
 class Linear(Part):
+    graph_safe = True
     family = "linear"
     kind = "linear"
 

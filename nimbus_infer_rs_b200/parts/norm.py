@@ -10,6 +10,7 @@ from .base import VECTOR, Norm, ParamSpec, register_part
 class LayerNorm(Norm):
     """``(x - mean) / sqrt(var + eps) * weight + bias`` per row with biased variance, statistics
     in fp32 (src/ops.rs:32-40).  Weight and bias are both required (src/engine.rs:141-152)."""
+    graph_safe = True
 
     def __init__(self, width: int, eps: float):
         self.width = int(width)

@@ -8,6 +8,7 @@ from .base import TABLE, ParamSpec, Position, register_part
 class LearnedAbsolute(Position):
     """A learned row per absolute position, added to the token embedding
     (src/model.rs:288-293).  Sequences cannot be longer than the table."""
+    graph_safe = True
 
     def __init__(self, max_positions: int, width: int):
         self.max_positions = int(max_positions)
@@ -21,6 +22,7 @@ class LearnedAbsolute(Position):
 @register_part("position", "none")
 class NoPosition(Position):
     """No position information is added anywhere."""
+    graph_safe = True
 
     def __init__(self, max_positions: int | None = None):
         self.max_positions = max_positions

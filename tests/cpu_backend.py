@@ -97,3 +97,8 @@ class CpuBackend:
                 if 0 <= tok < logits.shape[1]:
                     v = logits[r, tok]
                     logits[r, tok] = v / penalty if v > 0 else v * penalty
+
+    def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
+        live = row_slot >= 0
+        tokens.copy_(torch.where(live, next_tokens, torch.full_like(tokens, -1)))
+        row_pos.add_(live.to(row_pos.dtype))
