@@ -1,0 +1,345 @@
+// Matrix products with few rows (a decode step: one row per sequence, at most 64):
+// out[M,N] = act(norm?(X)[M,K] * W[N,K]^T + bias) (+ residual).
+//
+// With so few rows the product is bound by streaming W once from HBM, and for a small model
+// by latency.  Each CTA owns 8 output columns and all rows; its warps split K, every lane
+// fetches its part of the 8 weight rows with 16-byte loads straight into registers, all in
+// flight at once, and the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate) do the
+// arithmetic; partial sums of the warps are added through shared memory.  The LayerNorm that
+// precedes the product in a pre-norm block can be applied while the weights are in flight
+// (statistics in fp32, src/ops.rs:32-40), which saves a kernel and a round trip of the
+// normalised rows.  A second kernel does the same job with fp32 weights on the CUDA cores
+// (true 32-bit path).
+//
+// Reference analogue: Mat::gemv_into (src/model.rs:65-86), one dot product per output.
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Row statistics for a fused LayerNorm: stats[r] = (mean, 1/sqrt(var + eps)); one warp per row.
+template <typename TX>
+__device__ __forceinline__ void row_stats(const TX* __restrict__ X, float2* stats, int M, int K,
+                                          float eps, int warp, int lane, int n_warps) {
+  for (int r = warp; r < M; r += n_warps) {
+    const TX* src = X + (size_t)r * K;
+    float s = 0.0f;
+    for (int k = lane; k < K; k += 32) s += nb_to_f32(src[k]);
+    const float mean = nb_warp_sum(s) / (float)K;
+    float q = 0.0f;
+    for (int k = lane; k < K; k += 32) {
+      const float c = nb_to_f32(src[k]) - mean;
+      q += c * c;
+    }
+    const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
+    if (lane == 0) stats[r] = make_float2(mean, inv);
+  }
+}
+
+// Columns [k_lo, k_lo + width) of the rows of X into shared memory as bf16, optionally
+// normalised; rows M..rows_pad and columns at or beyond K are zero.
+template <typename TX, bool LN>
+__device__ __forceinline__ void stage_rows_bf16(const TX* __restrict__ X, bf16* xs, int stride,
+                                                int rows_pad, int M, int K, int k_lo, int width,
+                                                const float* __restrict__ gamma,
+                                                const float* __restrict__ beta,
+                                                const float2* stats, int tid, int n_threads) {
+  for (int idx = tid; idx < rows_pad * width; idx += n_threads) {
+    const int r = idx / width, kk = idx - r * width, k = k_lo + kk;
+    float y = 0.0f;
+    if (r < M && k < K) {
+      y = nb_to_f32(X[(size_t)r * K + k]);
+      if constexpr (LN) {
+        const float2 st = stats[r];
+        y = (y - st.x) * st.y * gamma[k];
+        if (beta) y += beta[k];
+      }
+    }
+    xs[(size_t)r * stride + kk] = __float2bfloat16_rn(y);
+  }
+}
+
+constexpr int CH = 8;  // 32-wide K chunks whose weights a warp holds in registers at a time
+
+// K is cut into segments of `kseg` columns (a multiple of 32 * WARPS) so that the staged rows
+// fit in shared memory; within a segment chunk c of 32 columns belongs to warp c % WARPS.
+template <int MT, int WARPS, typename TX, bool LN, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
+                        const float* __restrict__ beta, float eps, const bf16* __restrict__ W,
+                        const float* __restrict__ bias, const float* residual, TOut* out, int M,
+                        int N, int K, int act, int kseg) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int stride = kseg + 8;
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                           // [MT*16][stride]
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)MT * 16 * stride * sizeof(bf16));
+  float2* stats = reinterpret_cast<float2*>(red + WARPS * MT * 16 * 8);   // [MT*16]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 8;
+  const int n = n0 + g;
+  const bf16* wrow = W + (size_t)(n < N ? n : 0) * K;
+  const int rounds_per_seg = kseg / (32 * WARPS);
+  const int n_rounds = (K + 32 * WARPS - 1) / (32 * WARPS);   // round j: chunk j * WARPS + warp
+
+  uint4 wreg[CH];
+  auto load_batch = [&](int j0, int cnt) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int k = ((j0 + i) * WARPS + warp) * 32 + t * 8;
+      if (i < cnt && k < K && n < N)
+        wreg[i] = __ldg(reinterpret_cast<const uint4*>(wrow + k));
+      else
+        wreg[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  auto batch_len = [&](int j) {   // rounds from j to the end of j's segment, at most CH
+    const int seg_end = min(n_rounds, (j / rounds_per_seg + 1) * rounds_per_seg);
+    return max(0, min(CH, seg_end - j));
+  };
+  load_batch(0, batch_len(0));   // in flight while the rows are staged
+
+  if constexpr (LN) {
+    row_stats<TX>(X, stats, M, K, eps, warp, lane, WARPS);
+    __syncthreads();
+  }
+
+  float acc[MT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
+
+  for (int seg0 = 0; seg0 < n_rounds; seg0 += rounds_per_seg) {
+    const int seg_end = min(n_rounds, seg0 + rounds_per_seg);
+    const int k_lo = seg0 * 32 * WARPS;
+    if (seg0 > 0) __syncthreads();   // everyone is done reading the previous segment
+    stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, tid,
+                            WARPS * 32);
+    __syncthreads();
+    for (int j = seg0; j < seg_end; j += CH) {
+      const int cnt = min(CH, seg_end - j);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        if (i < cnt) {
+          const int kk = ((j + i) * WARPS + warp) * 32 + t * 8 - k_lo;   // column within xs
+          const uint4 w = wreg[i];
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const uint4 xa =
+                *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g) * stride + kk);
+            const uint4 xb =
+                *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g + 8) * stride + kk);
+            // K is permuted inside a chunk: lane group t owns elements 8t..8t+7 of both operands
+            mma_bf16_16816(acc[m], xa.x, xb.x, xa.y, xb.y, w.x, w.y);
+            mma_bf16_16816(acc[m], xa.z, xb.z, xa.w, xb.w, w.z, w.w);
+          }
+        }
+      }
+      load_batch(j + cnt, batch_len(j + cnt));   // the next batch, possibly of the next segment
+    }
+  }
+
+  // partial sums of the warps -> shared memory -> epilogue
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    float* r0 = red + ((size_t)warp * MT * 16 + m * 16 + g) * 8 + t * 2;
+    float* r1 = r0 + 8 * 8;
+    r0[0] = acc[m][0];
+    r0[1] = acc[m][1];
+    r1[0] = acc[m][2];
+    r1[1] = acc[m][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < MT * 16 * 8; idx += WARPS * 32) {
+    const int row = idx >> 3, col = idx & 7;
+    const int nn = n0 + col;
+    if (row >= M || nn >= N) continue;
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * MT * 16 + row) * 8 + col];
+    if (bias) v += bias[nn];
+    v = nb_apply_act(v, act);
+    if (residual) v += residual[(size_t)row * N + nn];
+    out[(size_t)row * N + nn] = nb_from_f32<TOut>(v);
+  }
+}
+
+// fp32 weights on the CUDA cores: one warp per output column, lanes along K, rows in chunks
+// of 8 held in shared memory.
+constexpr int F32_WARPS = 8;
+constexpr int F32_ROWS = 8;
+
+template <typename TX, bool LN, typename TOut>
+__global__ void __launch_bounds__(F32_WARPS * 32)
+gemm_skinny_f32_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, float eps, const float* __restrict__ W,
+                       const float* __restrict__ bias, const float* residual, TOut* out, int M,
+                       int N, int K, int act) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* xs = reinterpret_cast<float*>(smem_raw);  // [F32_ROWS][K]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.x * F32_WARPS + warp;
+  const float* wrow = W + (size_t)(n < N ? n : 0) * K;
+  const bool vec = (K % 4 == 0);
+
+  for (int m0 = 0; m0 < M; m0 += F32_ROWS) {
+    const int rows = min(F32_ROWS, M - m0);
+    __syncthreads();
+    for (int r = warp; r < F32_ROWS; r += F32_WARPS) {
+      float* dst = xs + (size_t)r * K;
+      if (r >= rows) {
+        for (int k = lane; k < K; k += 32) dst[k] = 0.0f;
+        continue;
+      }
+      const TX* src = X + (size_t)(m0 + r) * K;
+      if constexpr (LN) {
+        float s = 0.0f;
+        for (int k = lane; k < K; k += 32) s += nb_to_f32(src[k]);
+        const float mean = nb_warp_sum(s) / (float)K;
+        float q = 0.0f;
+        for (int k = lane; k < K; k += 32) {
+          const float c = nb_to_f32(src[k]) - mean;
+          q += c * c;
+        }
+        const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
+        for (int k = lane; k < K; k += 32) {
+          float y = (nb_to_f32(src[k]) - mean) * inv * gamma[k];
+          if (beta) y += beta[k];
+          dst[k] = y;
+        }
+      } else {
+        for (int k = lane; k < K; k += 32) dst[k] = nb_to_f32(src[k]);
+      }
+    }
+    __syncthreads();
+    float acc[F32_ROWS];
+#pragma unroll
+    for (int r = 0; r < F32_ROWS; ++r) acc[r] = 0.0f;
+    if (n < N) {
+      if (vec) {
+        for (int k = lane * 4; k < K; k += 128) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(wrow + k));
+#pragma unroll
+          for (int r = 0; r < F32_ROWS; ++r) {
+            const float4 x = *reinterpret_cast<const float4*>(xs + (size_t)r * K + k);
+            acc[r] = fmaf(x.x, w.x, acc[r]);
+            acc[r] = fmaf(x.y, w.y, acc[r]);
+            acc[r] = fmaf(x.z, w.z, acc[r]);
+            acc[r] = fmaf(x.w, w.w, acc[r]);
+          }
+        }
+      } else {
+        for (int k = lane; k < K; k += 32) {
+          const float w = __ldg(wrow + k);
+#pragma unroll
+          for (int r = 0; r < F32_ROWS; ++r) acc[r] = fmaf(xs[(size_t)r * K + k], w, acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < F32_ROWS; ++r) acc[r] = nb_warp_sum(acc[r]);
+    if (lane == 0 && n < N) {
+      for (int r = 0; r < rows; ++r) {
+        float v = acc[r];
+        if (bias) v += bias[n];
+        v = nb_apply_act(v, act);
+        const size_t o = (size_t)(m0 + r) * N + n;
+        if (residual) v += residual[o];
+        out[o] = nb_from_f32<TOut>(v);
+      }
+    }
+  }
+}
+
+template <int MT, int WARPS, typename TX, bool LN, typename TOut>
+int launch_bf16(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+                const float* bias, const float* residual, void* out, int M, int N, int K, int act,
+                cudaStream_t stream) {
+  // segment of K whose staged rows take about 96 KB at most (two CTAs per SM)
+  const int unit = 32 * WARPS;
+  const int cap = (96 * 1024) / (MT * 16 * (int)sizeof(bf16));
+  int kseg = ((K + unit - 1) / unit) * unit;
+  if (kseg > cap) kseg = (cap / unit) * unit;
+  if (kseg < unit) kseg = unit;
+  const size_t smem = (size_t)MT * 16 * (kseg + 8) * sizeof(bf16) +
+                      (size_t)WARPS * MT * 16 * 8 * sizeof(float) + (size_t)MT * 16 * sizeof(float2);
+  auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, LN, TOut>;
+  if (smem > 48 * 1024)
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(N + 7) / 8, WARPS * 32, smem, stream>>>((const TX*)X, gamma, beta, eps, (const bf16*)W,
+                                                  bias, residual, (TOut*)out, M, N, K, act, kseg);
+  return 0;
+}
+
+template <typename TX, bool LN, typename TOut>
+int dispatch_bf16(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+                  const float* bias, const float* residual, void* out, int M, int N, int K,
+                  int act, cudaStream_t stream) {
+  const bool wide = K > 1024;
+#define NB_GO(MT_, W_) \
+  return launch_bf16<MT_, W_, TX, LN, TOut>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream)
+  if (M <= 16) { if (wide) NB_GO(1, 8); else NB_GO(1, 4); }
+  if (M <= 32) { if (wide) NB_GO(2, 8); else NB_GO(2, 4); }
+  if (wide) NB_GO(4, 8); else NB_GO(4, 4);
+#undef NB_GO
+}
+
+template <typename TX, bool LN, typename TOut>
+int launch_f32(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+               const float* bias, const float* residual, void* out, int M, int N, int K, int act,
+               cudaStream_t stream) {
+  const size_t smem = (size_t)F32_ROWS * K * sizeof(float);
+  NB_REQUIRE(smem <= 220 * 1024, NB_ERR_UNSUPPORTED,
+             "gemm_skinny: width %d needs %zu bytes of shared memory", K, smem);
+  auto kern = gemm_skinny_f32_kernel<TX, LN, TOut>;
+  if (smem > 48 * 1024)
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(N + F32_WARPS - 1) / F32_WARPS, F32_WARPS * 32, smem, stream>>>(
+      (const TX*)X, gamma, beta, eps, (const float*)W, bias, residual, (TOut*)out, M, N, K, act);
+  return 0;
+}
+
+}  // namespace
+
+// M <= 64.  gamma != nullptr asks for LayerNorm of the rows first (X must then be fp32).
+// bf16 weights need K % 8 == 0 and 16-byte aligned rows; `residual` may alias `out` (fp32).
+NB_EXPORT int nb_gemm_skinny(const void* X, int x_dtype, const float* gamma, const float* beta,
+                             float eps, const void* W, int w_dtype, const float* bias,
+                             const float* residual, void* out, int out_dtype, int M, int N, int K,
+                             int act, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  NB_REQUIRE(M > 0 && M <= 64 && N > 0 && K > 0, NB_ERR_UNSUPPORTED,
+             "gemm_skinny: takes 1..64 rows, got M=%d N=%d K=%d", M, N, K);
+  const bool ln = gamma != nullptr;
+  NB_REQUIRE(!ln || x_dtype == NB_F32, NB_ERR_BAD_ARG, "gemm_skinny: a fused norm needs fp32 rows");
+  int rc = 0;
+#define NB_OUT(FN, TX_, LN_)                                                                  \
+  rc = (out_dtype == NB_F32)                                                                  \
+           ? FN<TX_, LN_, float>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream) \
+           : FN<TX_, LN_, bf16>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream)
+  if (w_dtype == NB_BF16) {
+    NB_REQUIRE(K % 8 == 0 && (uintptr_t)W % 16 == 0, NB_ERR_UNSUPPORTED,
+               "gemm_skinny: bf16 weights need a width that is a multiple of 8 (got %d)", K);
+    if (x_dtype == NB_F32) { if (ln) { NB_OUT(dispatch_bf16, float, true); } else { NB_OUT(dispatch_bf16, float, false); } }
+    else { NB_OUT(dispatch_bf16, bf16, false); }
+  } else {
+    NB_REQUIRE((uintptr_t)W % 16 == 0, NB_ERR_UNSUPPORTED, "gemm_skinny: unaligned weights");
+    if (x_dtype == NB_F32) { if (ln) { NB_OUT(launch_f32, float, true); } else { NB_OUT(launch_f32, float, false); } }
+    else { NB_OUT(launch_f32, bf16, false); }
+  }
+#undef NB_OUT
+  if (rc) return rc;
+  NB_CHECK_LAUNCH("gemm_skinny");
+  return 0;
+}

@@ -19,6 +19,7 @@ ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 
 
 class KernelError(RuntimeError):
@@ -98,8 +99,10 @@ class CudaBackend:
                    c_int(dtype_code(out.dtype)), c_int(n), c_int(d), c_float(eps), self._stream())
 
     # -- matrix products --------------------------------------------------------------
-    def linear(self, x, w, bias, out, act=ACT_NONE, residual=None):
-        """out = act(x @ w.T + bias) (+ residual).  x [M,K], w [N,K], out [M,N]."""
+    def linear(self, x, w, bias, out, act=ACT_NONE, residual=None, norm=None):
+        """out = act(norm(x) @ w.T + bias) (+ residual).  x [M,K], w [N,K], out [M,N].
+        ``norm``: ``(gamma, beta, eps, act_dtype)`` asks for LayerNorm of the fp32 rows ``x``
+        first; it is fused into the product where the kernel can, else run on its own."""
         _check(x, "x", None, 2)
         _check(w, "w", None, 2)
         _check(out, "out", None, 2)
@@ -116,6 +119,18 @@ class CudaBackend:
             _check(residual, "residual", torch.float32, 2)
             if residual.shape != out.shape:
                 raise KernelError("linear: residual shape does not match")
+        skinny = M <= SKINNY_MAX_ROWS and (w.dtype == torch.float32 or K % 8 == 0)
+        if skinny:
+            gamma, beta, eps = (norm[0], norm[1], norm[2]) if norm is not None else (None, None, 0.0)
+            self._call("nb_gemm_skinny", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(gamma),
+                       _ptr(beta), c_float(eps), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
+                       _ptr(residual), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N),
+                       c_int(K), c_int(act), self._stream())
+            return
+        if norm is not None:
+            h = torch.empty((M, K), device=x.device, dtype=norm[3])
+            self.layernorm(x, norm[0], norm[1], norm[2], h)
+            x = h
         self._call("nb_gemm_simt", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w),
                    c_int(dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
                    c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),

@@ -1,4 +1,4 @@
-from .base import (INDEX, MATRIX, TABLE, VECTOR, Block, FeedForward, KVRequest, Mixer, Norm,
+from .base import (INDEX, MATRIX, TABLE, VECTOR, Block, DeferredNorm, FeedForward, KVRequest, Mixer, Norm,
                    ParamSpec, Part, PartSpec, Position, StateRequest, bind_params, build_part,
                    collect_param_specs, register_part, registered_parts)
 from .linear import Linear

@@ -20,6 +20,7 @@ class CausalSelfAttention(Mixer):
     The output projection adds its result into the residual stream (src/model.rs:434-439).
     """
     graph_safe = True
+    accepts_deferred_norm = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  window: int = 0, bias: bool = True):

@@ -98,6 +98,25 @@ class Norm(Part):
                 n_rows: int | None = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def defer(self, ctx, x: torch.Tensor):
+        """The normalised rows, possibly not computed yet: a consumer that can fuse the norm
+        into its first kernel takes a :class:`DeferredNorm` apart, any other calls
+        ``.tensor()``.  The default computes right away."""
+        return self.forward(ctx, x)
+
+
+class DeferredNorm:
+    """``norm(x)`` that has not been computed: ``x`` fp32 rows, ``args`` what the fused kernel
+    needs.  ``tensor()`` computes it the plain way."""
+
+    def __init__(self, ctx, norm: Norm, x: torch.Tensor, args: tuple):
+        self.ctx, self.norm, self.x, self.args = ctx, norm, x, args
+        self.shape = x.shape
+        self.device = x.device
+
+    def tensor(self) -> torch.Tensor:
+        return self.norm.forward(self.ctx, self.x)
+
 
 class Position(Part):
     family = "position"
@@ -113,6 +132,9 @@ class Position(Part):
 
 class Mixer(Part):
     family = "mixer"
+    #: True if ``forward`` takes ``h`` as a :class:`DeferredNorm` (its first linear map fuses
+    #: the norm); otherwise it always gets a tensor
+    accepts_deferred_norm: bool = False
 
     def cache_request(self) -> KVRequest | None:
         return None
@@ -130,6 +152,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     family = "ffn"
+    accepts_deferred_norm: bool = False
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
         raise NotImplementedError

@@ -14,7 +14,10 @@ class PreNormBlock(Block):
         pass
 
     def forward(self, ctx, x, layer) -> None:
-        h = layer.norm_mixer.forward(ctx, x)
-        layer.mixer.forward(ctx, h, x)
-        h = layer.norm_ffn.forward(ctx, x)
-        layer.ffn.forward(ctx, h, x)
+        mixer, ffn = layer.mixer, layer.ffn
+        h = layer.norm_mixer.defer(ctx, x) if mixer.accepts_deferred_norm \
+            else layer.norm_mixer.forward(ctx, x)
+        mixer.forward(ctx, h, x)
+        h = layer.norm_ffn.defer(ctx, x) if ffn.accepts_deferred_norm \
+            else layer.norm_ffn.forward(ctx, x)
+        ffn.forward(ctx, h, x)

@@ -14,6 +14,7 @@ class DenseMLP(FeedForward):
     ``activation`` is ``gelu_tanh`` (src/ops.rs:21-24), ``gelu_erf`` or ``none``; ``hidden`` is
     a plain number, not derived from the width (src/config.rs:13)."""
     graph_safe = True
+    accepts_deferred_norm = True
 
     def __init__(self, width: int, hidden: int, activation: str, bias: bool = True):
         if activation not in ACTIVATIONS:

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import MATRIX, VECTOR, ParamSpec, Part
+from .base import MATRIX, VECTOR, DeferredNorm, ParamSpec, Part
 
 
 class Linear(Part):
@@ -35,10 +35,13 @@ class Linear(Part):
                  out_dtype: torch.dtype | None = None, act: int = 0,
                  residual: torch.Tensor | None = None) -> torch.Tensor:
         """``act(x @ W.T + b)``; with ``residual`` (fp32) the result is added into it in place."""
+        norm = None
+        if isinstance(x, DeferredNorm):       # the kernel applies the norm to the rows it loads
+            x, norm = x.x, x.args
         if residual is not None:
             out = residual
         elif out is None:
             out = torch.empty((x.shape[0], self.out_features), device=x.device,
                               dtype=out_dtype or ctx.rt.act_dtype)
-        ctx.ops.linear(x, self.weight, self.bias, out, act, residual)
+        ctx.ops.linear(x, self.weight, self.bias, out, act, residual, norm)
         return out

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import VECTOR, Norm, ParamSpec, register_part
+from .base import VECTOR, DeferredNorm, Norm, ParamSpec, register_part
 
 
 @register_part("norm", "layernorm")
@@ -21,6 +21,9 @@ class LayerNorm(Norm):
     def param_specs(self):
         return {"weight": ParamSpec((self.width,), VECTOR),
                 "bias": ParamSpec((self.width,), VECTOR)}
+
+    def defer(self, ctx, x):
+        return DeferredNorm(ctx, self, x, (self.weight, self.bias, self.eps, ctx.rt.act_dtype))
 
     def forward(self, ctx, x, rows=None, n_rows=None):
         n = x.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)

@@ -37,7 +37,11 @@ class CpuBackend:
             y = torch.where((rows[:n] >= 0)[:, None], y, torch.zeros_like(y))
         out.copy_(y.to(out.dtype))
 
-    def linear(self, x, w, bias, out, act=0, residual=None):
+    def linear(self, x, w, bias, out, act=0, residual=None, norm=None):
+        if norm is not None:
+            h = torch.empty(x.shape, dtype=norm[3])
+            self.layernorm(x, norm[0], norm[1], norm[2], h)
+            x = h
         y = x.float() @ w.float().t()
         if bias is not None:
             y = y + bias

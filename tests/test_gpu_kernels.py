@@ -279,3 +279,26 @@ def test_repetition_penalty(ops):
     lens = torch.tensor([4, 1], device=DEV, dtype=torch.int32)
     ops.repetition_penalty(logits, hist, lens, 2.0)
     assert logits.cpu().tolist() == [[1.0, -4.0, 1.0, 3.0], [1.0, 1.0, 1.0, 0.5]]
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 2304, 768), (17, 100, 96), (64, 768, 3072),
+                                     (40, 1001, 1600), (3, 77, 100), (130, 257, 72)])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
+    """LayerNorm fused into the product (few rows) or run before it (many rows) must both
+    equal norm-then-product in float64, up to the rounding of the normalised rows."""
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV) * 2 + 0.3
+    gamma, beta = torch.randn(K, device=DEV), torch.randn(K, device=DEV)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(wdt)
+    bias = torch.randn(N, device=DEV)
+    act_dtype = wdt
+    xd = x.double()
+    mean = xd.mean(-1, keepdim=True)
+    h = (xd - mean) / torch.sqrt(((xd - mean) ** 2).mean(-1, keepdim=True) + 1e-5) * gamma.double() \
+        + beta.double()
+    ref = _gelu(h @ w.double().t() + bias.double(), 1)
+    out = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    ops.linear(x, w, bias, out, 1, None, (gamma, beta, 1e-5, act_dtype))
+    tol = (2e-5 if wdt == torch.float32 else 1.5e-2) * float(ref.abs().max())
+    assert (out.double() - ref).abs().max() <= tol
