@@ -198,6 +198,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one phase only (for profiling); prints a reduced line")
+    ap.add_argument("--batch", type=int, default=BATCH, help="batch of the decode step")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -222,6 +225,18 @@ def main() -> int:
     cache_tokens = 64 * CONTEXT + 64
     engine = Engine.random(cfg, seed=0, dtype=dtype, cache_tokens=cache_tokens, std=0.02)
     elt = 2 if dtype == "bfloat16" else 4
+
+    if args.only == "prefill":
+        pre_ms = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT, reps=2)
+        print(json.dumps({"only": "prefill", "ms": round(pre_ms, 4),
+                          "tokens_per_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1)}))
+        return 0
+    if args.only == "decode":
+        ms, launches, mean_ctx = time_decode(engine, args.batch, CONTEXT, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
+                          "tokens_per_s": round(args.batch * 1000.0 / ms, 1),
+                          "gpu_launches": launches}))
+        return 0
 
     with ClockSampler() as clocks:
         ms, launches, mean_ctx = time_decode(engine, BATCH, CONTEXT, args.steps, args.warmup)

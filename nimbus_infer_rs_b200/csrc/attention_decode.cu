@@ -1,0 +1,362 @@
+// Decode attention: one query row per sequence over that sequence's paged keys and values.
+//
+// The work is reading the cache once, so the kernel is laid out for bandwidth: a CTA takes one
+// (row, key/value head, split of the sequence's pages), streams whole pages (64 keys x head_dim,
+// contiguous) into shared memory with 16-byte cp.async copies, two pages in flight, and all
+// query heads that share the key/value head are served from the same staged page.  Scores,
+// softmax and the weighted sum are fp32; every warp keeps a running (max, sum, accumulator)
+// for its quarter of each page, the warps are merged at the end of the split, and the splits
+// are merged by whichever CTA of the (row, head) finishes last (a counter in scratch memory
+// that it leaves at zero again).
+//
+// Scratch (caller-allocated): part_acc [rows][heads][splits][head_dim] fp32, part_ml
+// [rows][heads][splits][2] fp32, counters [rows][kv_heads] int32, zero before the first use.
+//
+// Reference: src/model.rs:401-422 (scores = dot(q,k)*scale over keys 0..pos, softmax,
+// weighted values), head h reads key/value head h / group (src/model.rs:390).
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int WARPS = 4;
+constexpr int PAGE_TOKENS = 64;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+template <typename T>
+struct Lane16;   // the 16 bytes a lane reads, as floats
+template <>
+struct Lane16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  }
+};
+template <>
+struct Lane16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __bfloat162float(h[i].x);
+      v[2 * i + 1] = __bfloat162float(h[i].y);
+    }
+  }
+};
+
+// G: query heads per key/value head served by one CTA (group <= G).
+template <typename T, int HD, int G, typename TOut>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
+                        const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                        NbPagedKV kv, int group, TOut* __restrict__ out, int out_stride,
+                        float scale, int window, int n_splits, float* __restrict__ part_acc,
+                        float* __restrict__ part_ml, int* __restrict__ counters) {
+  constexpr int EPL = Lane16<T>::N;           // elements per lane
+  constexpr int LPR = HD / EPL;               // lanes per key row
+  constexpr int RPW = 32 / LPR;               // key rows per warp iteration
+  constexpr int KEYS_PER_WARP = PAGE_TOKENS / WARPS;
+  constexpr int ITERS = KEYS_PER_WARP / RPW;
+  constexpr int TILE = PAGE_TOKENS * HD;      // elements of one page of one head
+  static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "head size not supported");
+  static_assert(ITERS >= 1, "head size not supported");
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* tiles = reinterpret_cast<T*>(smem_raw);                       // [2 stages][K tile | V tile]
+  float* q_s = reinterpret_cast<float*>(smem_raw + (size_t)4 * TILE * sizeof(T));  // [G][HD]
+  float* w_acc = q_s + G * HD;                                     // [WARPS][G][HD]
+  float* w_ml = w_acc + WARPS * G * HD;                            // [WARPS][G][2]
+  __shared__ int s_last;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub = lane / LPR, part = lane % LPR;
+  const int n_heads = kv.n_kv_heads * group;
+  const int slot = row_slot[r];
+  if (slot < 0) {   // padding row: zeros, written by split 0
+    if (split == 0)
+      for (int i = tid; i < group * HD; i += THREADS)
+        out[(size_t)r * out_stride + (size_t)kvh * group * HD + i] = nb_from_f32<TOut>(0.0f);
+    return;
+  }
+  const int pos = row_pos[r];
+  const int kv_len = pos + 1;
+  const int j_begin = (window > 0 && kv_len > window) ? kv_len - window : 0;
+  const int first_page = j_begin / PAGE_TOKENS;
+  const int n_pages = (kv_len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_page;
+  const int per_split = (n_pages + n_splits - 1) / n_splits;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(first_page + n_pages, p_begin + per_split);
+
+  // queries of the group, fp32
+  for (int i = tid; i < G * HD; i += THREADS) {
+    const int gh = i / HD, c = i - gh * HD;
+    q_s[i] = (gh < group)
+                 ? nb_to_f32(q[(size_t)r * q_stride + q_col + (size_t)(kvh * group + gh) * HD + c])
+                 : 0.0f;
+  }
+
+  const int* table = kv.block_table + (size_t)slot * kv.max_pages;
+  auto issue = [&](int page_idx, int stage) {
+    const int page_id = table[page_idx];
+    const T* ksrc = (const T*)kv.k + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE;
+    const T* vsrc = (const T*)kv.v + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE;
+    T* kdst = tiles + (size_t)stage * 2 * TILE;
+    T* vdst = kdst + TILE;
+    constexpr int VECS = TILE / EPL;   // 16-byte pieces per tile
+    for (int i = tid; i < VECS; i += THREADS) {
+      cp_async16(kdst + i * EPL, ksrc + i * EPL);
+      cp_async16(vdst + i * EPL, vsrc + i * EPL);
+    }
+    cp_async_commit();
+  };
+
+  float m_run[G], l_run[G], acc[G][EPL];
+#pragma unroll
+  for (int gh = 0; gh < G; ++gh) {
+    m_run[gh] = -INFINITY;
+    l_run[gh] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[gh][e] = 0.0f;
+  }
+
+  if (p_begin < p_end) issue(p_begin, 0);
+  __syncthreads();   // q_s is complete
+  float qreg[G][EPL];
+#pragma unroll
+  for (int gh = 0; gh < G; ++gh)
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qreg[gh][e] = q_s[gh * HD + part * EPL + e];
+
+  for (int p = p_begin; p < p_end; ++p) {
+    const int stage = (p - p_begin) & 1;
+    if (p + 1 < p_end) {
+      issue(p + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const T* kt = tiles + (size_t)stage * 2 * TILE;
+    const T* vt = kt + TILE;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int row = warp * KEYS_PER_WARP + it * RPW + sub;   // key within the page
+      const int j = p * PAGE_TOKENS + row;
+      const bool valid = (j >= j_begin) && (j < kv_len);
+      float kf[EPL], vf[EPL];
+      Lane16<T>::load(kt + (size_t)row * HD + part * EPL, kf);
+      Lane16<T>::load(vt + (size_t)row * HD + part * EPL, vf);
+      if (!valid) {   // whatever an unused cache row holds must not reach the sum
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) vf[e] = 0.0f;
+      }
+#pragma unroll
+      for (int gh = 0; gh < G; ++gh) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[gh][e], kf[e], dot);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float s = valid ? dot * scale : -INFINITY;
+        float mx = s;
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m_run[gh], mx);
+        if (m_new > -INFINITY) {   // warp-uniform
+          const float rescale = (m_run[gh] == -INFINITY) ? 0.0f : expf(m_run[gh] - m_new);
+          const float pr = valid ? expf(s - m_new) : 0.0f;
+          l_run[gh] = l_run[gh] * rescale + pr;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) acc[gh][e] = fmaf(pr, vf[e], acc[gh][e] * rescale);
+          m_run[gh] = m_new;
+        }
+      }
+    }
+    __syncthreads();   // the stage is free for the copy after next
+  }
+
+  // merge the key rows a warp handled side by side (lanes with equal `part`)
+#pragma unroll
+  for (int gh = 0; gh < G; ++gh) {
+    // l_run of a lane counts only its own rows; every lane of a row group holds the same value
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+      l_run[gh] += __shfl_xor_sync(0xffffffffu, l_run[gh], o);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[gh][e] += __shfl_xor_sync(0xffffffffu, acc[gh][e], o);
+    }
+    if (sub == 0) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) w_acc[(warp * G + gh) * HD + part * EPL + e] = acc[gh][e];
+      if (part == 0) {
+        w_ml[(warp * G + gh) * 2] = m_run[gh];
+        w_ml[(warp * G + gh) * 2 + 1] = l_run[gh];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps -> partial result of this split
+  for (int i = tid; i < group * HD; i += THREADS) {
+    const int gh = i / HD, c = i - gh * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, w_ml[(w * G + gh) * 2]);
+    float a = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = w_ml[(w * G + gh) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+      a += f * w_acc[(w * G + gh) * HD + c];
+      l += f * w_ml[(w * G + gh) * 2 + 1];
+    }
+    const int head = kvh * group + gh;
+    if (n_splits == 1) {   // nothing to merge with: this is the result
+      out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
+      continue;
+    }
+    const size_t pi = ((size_t)r * n_heads + head) * n_splits + split;
+    part_acc[pi * HD + c] = a;
+    if (c == 0) {
+      part_ml[pi * 2] = M;
+      part_ml[pi * 2 + 1] = l;
+    }
+  }
+  if (n_splits == 1) return;
+  // the CTA that finishes last for this (row, key/value head) merges the splits
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[r * kv.n_kv_heads + kvh], 1);
+    s_last = (old == n_splits - 1);
+    if (s_last) counters[r * kv.n_kv_heads + kvh] = 0;   // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = tid; i < group * HD; i += THREADS) {
+    const int gh = i / HD, c = i - gh * HD;
+    const int head = kvh * group + gh;
+    const size_t base = ((size_t)r * n_heads + head) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
+    float a = 0.0f, l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = __ldcg(&part_ml[(base + s) * 2]);
+      const float f = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+      a += f * __ldcg(&part_acc[(base + s) * HD + c]);
+      l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
+    }
+    out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
+  }
+}
+
+template <typename T, int HD, int G, typename TOut>
+int launch(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
+           const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+           int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters,
+           cudaStream_t stream) {
+  const size_t smem = (size_t)4 * PAGE_TOKENS * HD * sizeof(T) +
+                      (size_t)(G * HD + WARPS * G * HD + WARPS * G * 2) * sizeof(float);
+  auto kern = attention_decode_kernel<T, HD, G, TOut>;
+  if (smem > 48 * 1024)
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(n_splits, kv.n_kv_heads, n_rows);
+  kern<<<grid, THREADS, smem, stream>>>((const T*)q, q_stride, q_col, row_slot, row_pos, kv, group,
+                                        (TOut*)out, out_stride, scale, window, n_splits, part_acc,
+                                        part_ml, counters);
+  return 0;
+}
+
+template <typename T, int HD, typename TOut>
+int by_group(int group, const void* q, int q_stride, int q_col, const int* row_slot,
+             const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
+             int window, int n_rows, int n_splits, float* pa, float* pm, int* cn,
+             cudaStream_t st) {
+#define NB_G(G_) \
+  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, st)
+  if (group == 1) NB_G(1);
+  if (group == 2) NB_G(2);
+  if (group <= 4) NB_G(4);
+  NB_G(8);
+#undef NB_G
+}
+
+template <typename T, typename TOut>
+int by_head_dim(int hd, int group, const void* q, int q_stride, int q_col, const int* row_slot,
+                const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
+                int window, int n_rows, int n_splits, float* pa, float* pm, int* cn,
+                cudaStream_t st) {
+#define NB_HD(HD_) \
+  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, st)
+  switch (hd) {
+    case 16: NB_HD(16);
+    case 32: NB_HD(32);
+    case 64: NB_HD(64);
+    case 128: NB_HD(128);
+  }
+#undef NB_HD
+  return NB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// 1 if this kernel takes the shape (otherwise the caller uses the generic kernel).
+NB_EXPORT int nb_attention_decode_supported(int dtype, int head_dim, int n_heads, int n_kv_heads,
+                                            int page) {
+  if (page != PAGE_TOKENS || n_kv_heads < 1 || n_heads % n_kv_heads != 0) return 0;
+  if (n_heads / n_kv_heads > 8) return 0;
+  if (dtype != NB_F32 && dtype != NB_BF16) return 0;
+  return head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
+}
+
+// Floats of part_acc, floats of part_ml and ints of counters that a launch needs.
+NB_EXPORT void nb_attention_decode_scratch(int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                                           int n_splits, long long* acc_floats,
+                                           long long* ml_floats, long long* counter_ints) {
+  *acc_floats = (long long)n_rows * n_heads * n_splits * head_dim;
+  *ml_floats = (long long)n_rows * n_heads * n_splits * 2;
+  *counter_ints = (long long)n_rows * n_kv_heads;
+}
+
+NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_col,
+                                  const int* row_slot, const int* row_pos, const void* k_cache,
+                                  const void* v_cache, const int* block_table, int max_pages,
+                                  int page, int n_heads, int n_kv_heads, int head_dim, void* out,
+                                  int out_dtype, int out_stride, float scale, int window,
+                                  int n_rows, int n_splits, float* part_acc, float* part_ml,
+                                  int* counters, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(nb_attention_decode_supported(dtype, head_dim, n_heads, n_kv_heads, page),
+             NB_ERR_UNSUPPORTED,
+             "attention_decode: unsupported shape (head size %d, %d/%d heads, page %d)", head_dim,
+             n_heads, n_kv_heads, page);
+  NB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_rows <= 65535 && n_kv_heads <= 65535,
+             NB_ERR_UNSUPPORTED, "attention_decode: grid too large");
+  NB_REQUIRE(part_acc && part_ml && counters, NB_ERR_BAD_ARG, "attention_decode: scratch missing");
+  NbPagedKV kv{(void*)k_cache, (void*)v_cache, block_table, max_pages, page, n_kv_heads, head_dim};
+  const int group = n_heads / n_kv_heads;
+  typedef __nv_bfloat16 bf16;
+  int rc;
+#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, stream
+  if (dtype == NB_F32)
+    rc = out_dtype == NB_F32 ? by_head_dim<float, float>(NB_ARGS) : by_head_dim<float, bf16>(NB_ARGS);
+  else
+    rc = out_dtype == NB_F32 ? by_head_dim<bf16, float>(NB_ARGS) : by_head_dim<bf16, bf16>(NB_ARGS);
+#undef NB_ARGS
+  if (rc) return rc;
+  NB_CHECK_LAUNCH("attention_decode");
+  return 0;
+}

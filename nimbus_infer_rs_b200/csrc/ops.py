@@ -19,6 +19,7 @@ ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 
 
@@ -58,6 +59,7 @@ class CudaBackend:
         self.lib = build.load()
         self.lib.nb_last_error.restype = ctypes.c_char_p
         self.launches = 0  # kernels launched through this backend (for measurement reports)
+        self._scratch = {}
 
     # -- plumbing ---------------------------------------------------------------------
     def _stream(self) -> c_void_p:
@@ -137,6 +139,21 @@ class CudaBackend:
                    self._stream())
 
     # -- cache and attention ----------------------------------------------------------
+    def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
+        """Scratch of the split decode attention: partial sums per (row, head, split) and one
+        counter per (row, key/value head).  Kept and grown as needed; the counters start at
+        zero and every launch leaves them at zero."""
+        need_acc = n_rows * n_heads * n_splits * head_dim
+        need_ml = n_rows * n_heads * n_splits * 2
+        need_cnt = n_rows * n_kv_heads
+        s = self._scratch.get(device)
+        if s is None or s[0].numel() < need_acc or s[1].numel() < need_ml or s[2].numel() < need_cnt:
+            s = (torch.empty(max(need_acc, 1 << 16), dtype=torch.float32, device=device),
+                 torch.empty(max(need_ml, 1 << 12), dtype=torch.float32, device=device),
+                 torch.zeros(max(need_cnt, 1 << 12), dtype=torch.int32, device=device))
+            self._scratch[device] = s
+        return s
+
     def kv_append(self, src, k_col, v_col, row_slot, row_pos, kv, n_rows):
         _check(src, "src", kv.k.dtype, 2)
         self._call("nb_kv_append", _ptr(src), c_int(dtype_code(src.dtype)), c_int(src.shape[1]),
@@ -152,6 +169,22 @@ class CudaBackend:
         n_rows = layout.n_rows
         if out.shape[0] < n_rows or out.shape[1] != n_heads * kv.head_dim:
             raise KernelError("attention: output shape does not match")
+        if layout.is_decode and self.lib.nb_attention_decode_supported(
+                c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
+                c_int(kv.n_kv_heads), c_int(kv.page)):
+            pages = max(1, -(-layout.max_kv_len // kv.page))
+            n_splits = max(1, min(pages, -(-DECODE_TARGET_CTAS // (n_rows * kv.n_kv_heads))))
+            acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
+                                                     kv.head_dim, n_splits)
+            self._call("nb_attention_decode", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
+                       c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot),
+                       _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
+                       c_int(kv.block_table.shape[1]), c_int(kv.page), c_int(n_heads),
+                       c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
+                       c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
+                       c_int(window), c_int(n_rows), c_int(n_splits), _ptr(acc), _ptr(ml),
+                       _ptr(counters), self._stream())
+            return
         self._call("nb_attention_generic", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
                    c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
                    _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),

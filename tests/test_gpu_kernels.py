@@ -302,3 +302,38 @@ def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
     ops.linear(x, w, bias, out, 1, None, (gamma, beta, 1e-5, act_dtype))
     tol = (2e-5 if wdt == torch.float32 else 1.5e-2) * float(ref.abs().max())
     assert (out.double() - ref).abs().max() <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, Hk, hd, window", [(12, 12, 64, 0), (4, 4, 16, 0), (6, 2, 32, 0),
+                                               (8, 1, 128, 0), (6, 2, 64, 100), (3, 3, 48, 0),
+                                               (25, 25, 64, 0), (16, 1, 64, 0)])
+@pytest.mark.parametrize("max_kv", [64, 1024])
+def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
+    """One query row per sequence (a decode step): sequences of very unequal lengths, pages
+    shuffled, a padding row in the middle; run twice on the same scratch (the counters must be
+    left at zero); `max_kv` changes how many splits the launch uses."""
+    lens = [1, 64, 65, 700, 333, 1000, 129]
+    kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H + hd)
+    entries = [(s + 1, [0], []) for s in range(len(lens))]
+    lay = build_layout(entries, [l - 1 for l in lens], DEV, pad_rows_to=8)
+    assert lay.is_decode
+    lay.max_kv_len = max_kv if max_kv >= max(lens) else max(lens)
+    # a padding row between live rows
+    lay.row_slot[2] = -1
+    torch.manual_seed(6)
+    qkv = torch.randn(lay.n_rows, (H + 2 * Hk) * hd, device=DEV).to(dtype)
+    scale = 0.5 / math.sqrt(hd)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    for attempt in range(2):
+        out = torch.full((lay.n_rows, H * hd), 7.0, device=DEV, dtype=dtype)
+        ops.attention(qkv, 0, lay, kv, H, out, scale, window)
+        for s, l in enumerate(lens):
+            if s == 2:
+                assert (out[s] == 0).all()
+                continue
+            ref = _attention_ref(qkv[s, :H * hd].view(H, hd).cpu(), dk[s], dv[s], l - 1, scale,
+                                 H // Hk, window)
+            got = out[s].view(H, hd).double().cpu()
+            assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (attempt, s)
+        assert (out[len(lens):] == 0).all()
