@@ -27,19 +27,55 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Row statistics for a fused LayerNorm: stats[r] = (mean, 1/sqrt(var + eps)); one warp per row.
+// Eight consecutive elements of a row as floats (16-byte loads; the row start and k are
+// multiples of 8 elements).
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __bfloat162float(h[i].x);
+    v[2 * i + 1] = __bfloat162float(h[i].y);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
+// Row statistics for a fused LayerNorm: stats[r] = (mean, 1/sqrt(var + eps)); one warp per row,
+// two passes over the row (mean, then the squared deviations).  K is a multiple of 8.
 template <typename TX>
 __device__ __forceinline__ void row_stats(const TX* __restrict__ X, float2* stats, int M, int K,
                                           float eps, int warp, int lane, int n_warps) {
   for (int r = warp; r < M; r += n_warps) {
     const TX* src = X + (size_t)r * K;
     float s = 0.0f;
-    for (int k = lane; k < K; k += 32) s += nb_to_f32(src[k]);
+    for (int k = lane * 8; k < K; k += 256) {
+      float v[8];
+      load8(src + k, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += v[e];
+    }
     const float mean = nb_warp_sum(s) / (float)K;
     float q = 0.0f;
-    for (int k = lane; k < K; k += 32) {
-      const float c = nb_to_f32(src[k]) - mean;
-      q += c * c;
+    for (int k = lane * 8; k < K; k += 256) {
+      float v[8];
+      load8(src + k, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = v[e] - mean;
+        q = fmaf(c, c, q);
+      }
     }
     const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
     if (lane == 0) stats[r] = make_float2(mean, inv);
@@ -47,25 +83,44 @@ __device__ __forceinline__ void row_stats(const TX* __restrict__ X, float2* stat
 }
 
 // Columns [k_lo, k_lo + width) of the rows of X into shared memory as bf16, optionally
-// normalised; rows M..rows_pad and columns at or beyond K are zero.
+// normalised; rows M..rows_pad and columns at or beyond K are zero.  One warp per row, eight
+// elements per lane and step.
 template <typename TX, bool LN>
 __device__ __forceinline__ void stage_rows_bf16(const TX* __restrict__ X, bf16* xs, int stride,
                                                 int rows_pad, int M, int K, int k_lo, int width,
                                                 const float* __restrict__ gamma,
                                                 const float* __restrict__ beta,
-                                                const float2* stats, int tid, int n_threads) {
-  for (int idx = tid; idx < rows_pad * width; idx += n_threads) {
-    const int r = idx / width, kk = idx - r * width, k = k_lo + kk;
-    float y = 0.0f;
-    if (r < M && k < K) {
-      y = nb_to_f32(X[(size_t)r * K + k]);
-      if constexpr (LN) {
-        const float2 st = stats[r];
-        y = (y - st.x) * st.y * gamma[k];
-        if (beta) y += beta[k];
-      }
+                                                const float2* stats, int warp, int lane,
+                                                int n_warps) {
+  for (int r = warp; r < rows_pad; r += n_warps) {
+    bf16* dst = xs + (size_t)r * stride;
+    const TX* src = X + (size_t)r * K;
+    float2 st = make_float2(0.0f, 1.0f);
+    if constexpr (LN) {
+      if (r < M) st = stats[r];
     }
-    xs[(size_t)r * stride + kk] = __float2bfloat16_rn(y);
+    for (int kk = lane * 8; kk < width; kk += 256) {
+      const int k = k_lo + kk;
+      uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+      if (r < M && k < K) {
+        float v[8];
+        load8(src + k, v);
+        if constexpr (LN) {
+          float gm[8];
+          load8(gamma + k, gm);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = (v[e] - st.x) * st.y * gm[e];
+          if (beta) {
+            float bt[8];
+            load8(beta + k, bt);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += bt[e];
+          }
+        }
+        packed = pack8(v);
+      }
+      *reinterpret_cast<uint4*>(dst + kk) = packed;
+    }
   }
 }
 
@@ -124,8 +179,8 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
     const int seg_end = min(n_rounds, seg0 + rounds_per_seg);
     const int k_lo = seg0 * 32 * WARPS;
     if (seg0 > 0) __syncthreads();   // everyone is done reading the previous segment
-    stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, tid,
-                            WARPS * 32);
+    stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, warp,
+                            lane, WARPS);
     __syncthreads();
     for (int j = seg0; j < seg_end; j += CH) {
       const int cnt = min(CH, seg_end - j);
@@ -331,6 +386,8 @@ NB_EXPORT int nb_gemm_skinny(const void* X, int x_dtype, const float* gamma, con
   if (w_dtype == NB_BF16) {
     NB_REQUIRE(K % 8 == 0 && (uintptr_t)W % 16 == 0, NB_ERR_UNSUPPORTED,
                "gemm_skinny: bf16 weights need a width that is a multiple of 8 (got %d)", K);
+    NB_REQUIRE((uintptr_t)X % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0,
+               NB_ERR_UNSUPPORTED, "gemm_skinny: rows and norm vectors must be 16-byte aligned");
     if (x_dtype == NB_F32) { if (ln) { NB_OUT(dispatch_bf16, float, true); } else { NB_OUT(dispatch_bf16, float, false); } }
     else { NB_OUT(dispatch_bf16, bf16, false); }
   } else {
