@@ -1,0 +1,426 @@
+// Matrix product on the 5th-generation tensor cores (sm_100a): out[M,N] = act(X[M,K] *
+// W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
+//
+// One CTA computes a 128 x BN tile.  Warp 0 is the producer: one thread issues TMA loads of
+// 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
+// stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
+// allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
+// with shared-memory matrix descriptors; `tcgen05.commit` hands a stage back to the producer
+// and, after the last K block, signals the accumulator.  Warps 2..5 are the epilogue: each
+// reads its 32-lane quarter of the accumulator with `tcgen05.ld`, applies bias / GELU /
+// residual in fp32 and stores its rows.  Edges need no special code on the load side: TMA
+// zero-fills rows beyond M or N and columns beyond K.
+//
+// Every wait on an mbarrier is bounded by a clock budget; a wait that runs out raises an
+// error flag (nb_gemm_tcgen05_error), all roles leave their loops, the CTA lets its copies in
+// flight land, frees its tensor memory and returns.
+//
+// Requirements: K % 8 == 0 (16-byte row pitch for TMA), 16-byte aligned bases.
+// Reference analogue: Mat::gemm_into (src/model.rs:94-133).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int BM = 128;
+constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;         // producer warp, MMA warp, four epilogue warps
+constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
+
+__device__ int g_error_flag = 0;
+
+// ---------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the budget ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - start > WAIT_BUDGET) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc05_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc05_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16),
+// 128-byte swizzled, 1024-byte aligned: start address >> 4 in bits 0..13, leading byte
+// offset 1 (unused for swizzled K-major) in bits 16..29, stride byte offset (8 rows x 128 B =
+// 1024 B) >> 4 in bits 32..45, descriptor version 1 in bits 46..47, swizzle mode 2 (128 B) in
+// bits 61..63.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator (bits 4..5 = 1), bf16 A and B (bits
+// 7..9 and 10..12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17..22, M >> 4 in bits
+// 24..28.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
+  // after the tiles: full[STAGES], empty[STAGES], accumulator barrier, tmem base, abort flag
+  static constexpr int TOTAL = TILES_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024 /* alignment slack */;
+};
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
+                    int K, int act) {
+  using L = SmemLayout<BN>;
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment (swizzle atoms), computed on the shared-window address
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gen = smem_dyn + (base - raw);
+  const uint32_t bars = base + L::TILES_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (L::STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * L::STAGES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + (2 * L::STAGES + 1) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < L::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {   // the whole warp allocates BN columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc05_fence_before();
+  __syncthreads();
+  tc05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {   // ---------------------------------------------------- TMA producer
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % L::STAGES;
+        const uint32_t phase = (uint32_t)(kb / L::STAGES) & 1u;
+        if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag)) break;
+        mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+        const uint32_t a_dst = base + s * L::STAGE_BYTES;
+        tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
+        tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {   // ---------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % L::STAGES;
+        const uint32_t phase = (uint32_t)(kb / L::STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), phase, abort_flag);
+        if (!ok) break;
+        tc05_fence_after();
+        const uint32_t a_addr = base + s * L::STAGE_BYTES;
+        const uint64_t da = smem_desc_sw128(a_addr);
+        const uint64_t db = smem_desc_sw128(a_addr + L::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // advancing K by 16 elements inside the swizzle atom = 32 bytes = 2 address units
+          tc05_mma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tc05_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+      }
+      if (ok) tc05_commit(acc_bar);  // the accumulator is complete once all MMAs are done
+    }
+  } else {             // ------------------------------------------------------ epilogue
+    const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
+    const int m = m0 + quarter * 32 + lane;
+    // lane 0 decides for the warp: the tensor-memory loads below need all 32 lanes
+    const bool ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_bar, 0u, abort_flag), 0) != 0;
+    if (ready) {
+      tc05_fence_after();
+      const bool vec_f32 = (N % 4 == 0);
+      const bool vec_b16 = (N % 8 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+        tc05_wait_ld();
+        const int nb = n0 + c * 32;
+        if (m < M && nb < N) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = nb + j;
+            float x = __uint_as_float(v[j]);
+            if (n < N) {
+              if (bias) x += __ldg(bias + n);
+              x = nb_apply_act(x, act);
+            }
+            f[j] = x;
+          }
+          const size_t row = (size_t)m * N;
+          const bool full = nb + 32 <= N;
+          if constexpr (sizeof(TOut) == 4) {
+            float* o = reinterpret_cast<float*>(out) + row + nb;
+            const float* r = residual ? residual + row + nb : nullptr;
+            if (full && vec_f32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 y = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                if (r) {
+                  const float4 rr = *reinterpret_cast<const float4*>(r + j);
+                  y.x += rr.x; y.y += rr.y; y.z += rr.z; y.w += rr.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < N) o[j] = f[j] + (r ? r[j] : 0.0f);
+            }
+          } else {
+            bf16* o = reinterpret_cast<bf16*>(out) + row + nb;
+            const float* r = residual ? residual + row + nb : nullptr;
+            if (full && vec_b16) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  h[e] = __floats2bfloat162_rn(f[j + 2 * e] + (r ? r[j + 2 * e] : 0.0f),
+                                               f[j + 2 * e + 1] + (r ? r[j + 2 * e + 1] : 0.0f));
+                *reinterpret_cast<uint4*>(o + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < N) o[j] = __float2bfloat16_rn(f[j] + (r ? r[j] : 0.0f));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (tid == 0) {
+      atomicExch(&g_error_flag, 1);
+      // let TMA copies that are still in flight land before the shared memory goes away
+      const long long t0 = clock64();
+      while (clock64() - t0 < 4000000LL) {
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
+                 "r"((uint32_t)BN)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// A [rows, K] bf16 row-major matrix as a 2-D tensor map with boxes of `box_rows` x 64 elements.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  NB_REQUIRE(fn != nullptr, NB_ERR_UNSUPPORTED, "gemm_tcgen05: cuTensorMapEncodeTiled not found");
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NB_REQUIRE(r == CUDA_SUCCESS, NB_ERR_BAD_ARG, "gemm_tcgen05: cuTensorMapEncodeTiled failed (%d)",
+             (int)r);
+  return 0;
+}
+
+template <int BN, typename TOut>
+int launch(const void* X, const void* W, const float* bias, const float* residual, void* out, int M,
+           int N, int K, int act, cudaStream_t stream) {
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, X, M, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, BN);
+  if (rc) return rc;
+  auto kern = gemm_tcgen05_kernel<BN, TOut>;
+  const int smem = SmemLayout<BN>::TOTAL;
+  static bool configured = false;   // per instantiation
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kern<<<grid, THREADS, smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act);
+  return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernel takes this product.
+NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, int K) {
+  return x_dtype == NB_BF16 && w_dtype == NB_BF16 && K % 8 == 0 && M >= 1 && N >= 1 && K >= 8 &&
+         (M + BM - 1) / BM <= 65535;
+}
+
+// Reads (and clears) the error flag that a timed-out wait raises; synchronises the device.
+NB_EXPORT int nb_gemm_tcgen05_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_error_flag, &zero, sizeof(int));
+  }
+  return v;
+}
+
+NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, const float* residual,
+                              void* out, int out_dtype, int M, int N, int K, int act,
+                              cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  NB_REQUIRE(nb_gemm_tcgen05_supported(NB_BF16, NB_BF16, M, N, K), NB_ERR_UNSUPPORTED,
+             "gemm_tcgen05: needs bf16 operands and a width that is a multiple of 8 (M=%d N=%d K=%d)",
+             M, N, K);
+  NB_REQUIRE((uintptr_t)X % 16 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                 (uintptr_t)residual % 16 == 0,
+             NB_ERR_UNSUPPORTED, "gemm_tcgen05: operands must be 16-byte aligned");
+  // tile width: fill the 148 SMs first, then prefer wider tiles
+  const long long tiles_m = (M + BM - 1) / BM;
+  int bn = 256;
+  if (tiles_m * ((N + 255) / 256) < 2 * 148) bn = 128;
+  if (tiles_m * ((N + 127) / 128) < 148) bn = 64;
+  int rc;
+  if (out_dtype == NB_F32) {
+    rc = bn == 256 ? launch<256, float>(X, W, bias, residual, out, M, N, K, act, stream)
+       : bn == 128 ? launch<128, float>(X, W, bias, residual, out, M, N, K, act, stream)
+                   : launch<64, float>(X, W, bias, residual, out, M, N, K, act, stream);
+  } else if (out_dtype == NB_BF16) {
+    rc = bn == 256 ? launch<256, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+       : bn == 128 ? launch<128, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+                   : launch<64, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
+  } else {
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+  }
+  if (rc) return rc;
+  NB_CHECK_LAUNCH("gemm_tcgen05");
+  return 0;
+}

@@ -11,6 +11,7 @@ installs :class:`CudaBackend`.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_double, c_float, c_int, c_void_p
 
 import torch
@@ -60,6 +61,8 @@ class CudaBackend:
         self.lib.nb_last_error.restype = ctypes.c_char_p
         self.launches = 0  # kernels launched through this backend (for measurement reports)
         self._scratch = {}
+        # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
+        self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
 
     # -- plumbing ---------------------------------------------------------------------
     def _stream(self) -> c_void_p:
@@ -133,10 +136,22 @@ class CudaBackend:
             h = torch.empty((M, K), device=x.device, dtype=norm[3])
             self.layernorm(x, norm[0], norm[1], norm[2], h)
             x = h
+        if self.use_tcgen05 and self.lib.nb_gemm_tcgen05_supported(
+                c_int(dtype_code(x.dtype)), c_int(dtype_code(w.dtype)), c_int(M), c_int(N), c_int(K)):
+            self._call("nb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                       c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),
+                       self._stream())
+            return
         self._call("nb_gemm_simt", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w),
                    c_int(dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
                    c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),
                    self._stream())
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel reported a timed-out wait (synchronises the device)."""
+        if self.lib.nb_gemm_tcgen05_error() != 0:
+            raise KernelError("gemm_tcgen05: a wait on a shared-memory barrier ran out of time; "
+                              "the results of that product are not valid")
 
     # -- cache and attention ----------------------------------------------------------
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):

@@ -102,6 +102,9 @@ class CpuBackend:
                     v = logits[r, tok]
                     logits[r, tok] = v / penalty if v > 0 else v * penalty
 
+    def check_device_errors(self):
+        pass
+
     def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
         live = row_slot >= 0
         tokens.copy_(torch.where(live, next_tokens, torch.full_like(tokens, -1)))

@@ -337,3 +337,31 @@ def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
             got = out[s].view(H, hd).double().cpu()
             assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (attempt, s)
         assert (out[len(lens):] == 0).all()
+
+
+@pytest.mark.parametrize("M, N, K", [(65, 64, 8), (128, 128, 64), (129, 200, 72), (300, 2304, 768),
+                                     (2048, 768, 3072), (1000, 3072, 768), (256, 50257, 768),
+                                     (2048, 96, 320), (4096, 4096, 1600), (77, 1001, 2000)])
+def test_tensor_core_product(ops, M, N, K):
+    """The tcgen05 kernel (bf16, more than 64 rows) against float64: tile edges in M, N and K,
+    all three tile widths, every epilogue; and no wait may have timed out."""
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    ref0 = x.double() @ w.double().t()
+    tol = 3e-6 * float(ref0.abs().max()) * math.sqrt(K / 64)
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(x, w, None, out)
+    err = (out.double() - ref0).abs()
+    assert err.max() <= tol, f"worst element {err.argmax().item() // N, err.argmax().item() % N}"
+    ref = _gelu(ref0 + bias.double(), 1)
+    o = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.linear(x, w, bias, o, 1)
+    assert (o.double() - ref).abs().max() <= tol + 8e-3 * float(ref.abs().max())
+    res = torch.randn(M, N, device=DEV)
+    stream = res.clone()
+    ops.linear(x, w, bias, stream, 0, stream)
+    ref = ref0 + bias.double() + res.double()
+    assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
+    ops.check_device_errors()
