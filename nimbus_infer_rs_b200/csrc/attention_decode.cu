@@ -14,6 +14,8 @@
 //
 // Reference: src/model.rs:401-422 (scores = dot(q,k)*scale over keys 0..pos, softmax,
 // weighted values), head h reads key/value head h / group (src/model.rs:390).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -359,4 +361,74 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_decode");
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate device memory (see no_alloc.h).
+// Its scratch is this file-scope array: every GPU that loads the library holds these
+// NB_STATIC_SCRATCH_BYTES until the process exits.
+// ---------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_static_scratch[NB_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[MAX_DEVICES] = {nullptr};
+
+// The array's device address on the current device.  In host code the name
+// `g_static_scratch` is only a handle for the runtime, never an address a kernel may use.
+int static_scratch_address(unsigned char** out) {
+  int dev = -1;
+  NB_CUDA(cudaGetDevice(&dev));
+  NB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, NB_ERR_UNSUPPORTED,
+             "attention_decode_static: device index %d is beyond %d", dev, MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    NB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    NB_REQUIRE(p != nullptr, NB_ERR_UNSUPPORTED, "attention_decode_static: no symbol address");
+    g_static_ptr[dev] = p;
+  }
+  *out = static_cast<unsigned char*>(g_static_ptr[dev]);
+  return 0;
+}
+}  // namespace
+
+NB_EXPORT long long nb_attention_decode_static_capacity() { return NB_STATIC_SCRATCH_BYTES; }
+
+NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride, int q_col,
+                                         const int* row_slot, const int* row_pos,
+                                         const void* k_cache, const void* v_cache,
+                                         const int* block_table, int max_pages, int page,
+                                         int n_heads, int n_kv_heads, int head_dim, void* out,
+                                         int out_dtype, int out_stride, float scale, int window,
+                                         int n_rows, int n_splits, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && n_splits > 0,
+             NB_ERR_BAD_ARG, "attention_decode_static: sizes must be positive");
+  long long acc_f = 0, ml_f = 0, cnt_i = 0;
+  nb_attention_decode_scratch(n_rows, n_heads, n_kv_heads, head_dim, n_splits, &acc_f, &ml_f, &cnt_i);
+  // layout: [counters | (max,sum) pairs | partial sums], each part rounded up to 256 bytes
+  auto up = [](long long b) { return (b + 255) / 256 * 256; };
+  const long long cnt_b = up(cnt_i * 4), ml_b = up(ml_f * 4), acc_b = up(acc_f * 4);
+  NB_REQUIRE(cnt_b + ml_b + acc_b <= (long long)NB_STATIC_SCRATCH_BYTES, NB_ERR_UNSUPPORTED,
+             "attention_decode_static: %d rows x %d heads x %d splits x head size %d need %lld "
+             "bytes of scratch, the built-in array holds %lld; use fewer splits or "
+             "nb_attention_decode with scratch of your own",
+             n_rows, n_heads, n_splits, head_dim, cnt_b + ml_b + acc_b,
+             (long long)NB_STATIC_SCRATCH_BYTES);
+  unsigned char* base = nullptr;
+  const int rc = static_scratch_address(&base);
+  if (rc) return rc;
+  // the array keeps what the last call left; the counters are the only part that must start
+  // at zero (a launch that ran to its end leaves them so, an interrupted one may not)
+  NB_CUDA(cudaMemsetAsync(base, 0, (size_t)cnt_b, stream));
+  return nb_attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache,
+                             block_table, max_pages, page, n_heads, n_kv_heads, head_dim, out,
+                             out_dtype, out_stride, scale, window, n_rows, n_splits,
+                             reinterpret_cast<float*>(base + cnt_b + ml_b),
+                             reinterpret_cast<float*>(base + cnt_b),
+                             reinterpret_cast<int*>(base), stream);
 }

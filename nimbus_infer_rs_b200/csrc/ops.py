@@ -200,6 +200,19 @@ class CudaBackend:
                        c_int(window), c_int(n_rows), c_int(n_splits), _ptr(acc), _ptr(ml),
                        _ptr(counters), self._stream())
             return
+        if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
+                c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
+                c_int(kv.n_kv_heads), c_int(kv.page), c_int(q_src.shape[1]), c_int(q_col)):
+            if layout.n_rows > layout.n_tokens:
+                out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
+            self._call("nb_attention_prefill", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
+                       c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.cu_rows),
+                       _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
+                       _ptr(kv.block_table), c_int(kv.block_table.shape[1]), c_int(kv.page),
+                       c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
+                       c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
+                       c_int(window), c_int(layout.n_seqs), c_int(layout.max_q_len), self._stream())
+            return
         self._call("nb_attention_generic", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
                    c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
                    _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),
