@@ -124,10 +124,85 @@ __device__ __forceinline__ void stage_rows_bf16(const TX* __restrict__ X, bf16* 
   }
 }
 
-constexpr int CH = 8;  // 32-wide K chunks whose weights a warp holds in registers at a time
+constexpr int CH = 12;   // 32-wide K chunks whose weights a warp holds in registers at a time
+constexpr int VMAX = 8;  // 8-element vectors of a row a lane may hold (rows up to 2048 wide)
+
+// All of K at once: every warp brings whole rows through registers (one trip to memory per
+// row), takes mean and variance from the registers (two passes, src/ops.rs:32-40), and
+// writes the normalised bf16 row to shared memory.  Needs K <= 256 * VMAX.
+template <typename TX, bool LN>
+__device__ __forceinline__ void stage_rows_once(const TX* __restrict__ X, bf16* xs, int stride,
+                                                int rows_pad, int M, int K, int width,
+                                                const float* __restrict__ gamma,
+                                                const float* __restrict__ beta, float eps,
+                                                int warp, int lane, int n_warps) {
+  for (int r = warp; r < rows_pad; r += n_warps) {
+    bf16* dst = xs + (size_t)r * stride;
+    if (r >= M) {
+      for (int kk = lane * 8; kk < width; kk += 256)
+        *reinterpret_cast<uint4*>(dst + kk) = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const TX* src = X + (size_t)r * K;
+    float v[VMAX][8];
+#pragma unroll
+    for (int i = 0; i < VMAX; ++i) {
+      const int k = lane * 8 + i * 256;
+      if (k < K) {
+        load8(src + k, v[i]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = 0.0f;
+      }
+    }
+    if constexpr (LN) {
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VMAX; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += v[i][e];
+      const float mean = nb_warp_sum(s) / (float)K;
+      float q = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VMAX; ++i) {
+        if (lane * 8 + i * 256 < K) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float c = v[i][e] - mean;
+            q = fmaf(c, c, q);
+          }
+        }
+      }
+      const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
+#pragma unroll
+      for (int i = 0; i < VMAX; ++i) {
+        const int k = lane * 8 + i * 256;
+        if (k < K) {
+          float gm[8];
+          load8(gamma + k, gm);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] = (v[i][e] - mean) * inv * gm[e];
+          if (beta) {
+            float bt[8];
+            load8(beta + k, bt);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i][e] += bt[e];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VMAX; ++i) {
+      const int kk = lane * 8 + i * 256;
+      if (kk < width) *reinterpret_cast<uint4*>(dst + kk) = pack8(v[i]);
+    }
+  }
+}
 
 // K is cut into segments of `kseg` columns (a multiple of 32 * WARPS) so that the staged rows
 // fit in shared memory; within a segment chunk c of 32 columns belongs to warp c % WARPS.
+// With a single segment the rows are staged once and the CTA walks over column groups
+// blockIdx.x, blockIdx.x + gridDim.x, ... with the next group's weights already in flight.
 template <int MT, int WARPS, typename TX, bool LN, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
@@ -135,24 +210,27 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
                         const float* __restrict__ bias, const float* residual, TOut* out, int M,
                         int N, int K, int act, int kseg) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int NT = WARPS * 32;
+  constexpr int EPT = (MT * 16 * 8 + NT - 1) / NT;   // outputs per thread and column group
   const int stride = kseg + 8;
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);                           // [MT*16][stride]
   float* red = reinterpret_cast<float*>(smem_raw + (size_t)MT * 16 * stride * sizeof(bf16));
   float2* stats = reinterpret_cast<float2*>(red + WARPS * MT * 16 * 8);   // [MT*16]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 8;
-  const int n = n0 + g;
-  const bf16* wrow = W + (size_t)(n < N ? n : 0) * K;
+  const int n_groups = (N + 7) / 8;
   const int rounds_per_seg = kseg / (32 * WARPS);
   const int n_rounds = (K + 32 * WARPS - 1) / (32 * WARPS);   // round j: chunk j * WARPS + warp
+  const bool single = n_rounds <= rounds_per_seg;
 
   uint4 wreg[CH];
-  auto load_batch = [&](int j0, int cnt) {
+  auto load_batch = [&](int grp, int j0, int cnt) {
+    const int n = grp * 8 + g;
+    const bf16* wrow = W + (size_t)(n < N ? n : 0) * K;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       const int k = ((j0 + i) * WARPS + warp) * 32 + t * 8;
-      if (i < cnt && k < K && n < N)
+      if (i < cnt && k < K && n < N && grp < n_groups)
         wreg[i] = __ldg(reinterpret_cast<const uint4*>(wrow + k));
       else
         wreg[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -162,71 +240,103 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
     const int seg_end = min(n_rounds, (j / rounds_per_seg + 1) * rounds_per_seg);
     return max(0, min(CH, seg_end - j));
   };
-  load_batch(0, batch_len(0));   // in flight while the rows are staged
+  int grp = blockIdx.x;
+  load_batch(grp, 0, batch_len(0));   // in flight while the rows are staged
 
-  if constexpr (LN) {
-    row_stats<TX>(X, stats, M, K, eps, warp, lane, WARPS);
-    __syncthreads();
+  if (LN && single && K <= 256 * VMAX) {
+    stage_rows_once<TX, LN>(X, xs, stride, MT * 16, M, K, kseg, gamma, beta, eps, warp, lane, WARPS);
+  } else {
+    if constexpr (LN) {
+      row_stats<TX>(X, stats, M, K, eps, warp, lane, WARPS);
+      __syncthreads();
+    }
+    if (single)
+      stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, 0, kseg, gamma, beta, stats, warp,
+                              lane, WARPS);
   }
+  if (single) __syncthreads();
 
-  float acc[MT][4];
+  for (; grp < n_groups; grp += gridDim.x) {
+    const int n0 = grp * 8;
+    // what the epilogue will need, asked for now
+    float e_bias[EPT], e_res[EPT];
 #pragma unroll
-  for (int m = 0; m < MT; ++m)
+    for (int i = 0; i < EPT; ++i) {
+      const int idx = tid + i * NT;
+      const int row = idx >> 3, nn = n0 + (idx & 7);
+      const bool live = idx < MT * 16 * 8 && row < M && nn < N;
+      e_bias[i] = (live && bias) ? __ldg(bias + nn) : 0.0f;
+      e_res[i] = (live && residual) ? residual[(size_t)row * N + nn] : 0.0f;
+    }
+    float acc[MT][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
 
-  for (int seg0 = 0; seg0 < n_rounds; seg0 += rounds_per_seg) {
-    const int seg_end = min(n_rounds, seg0 + rounds_per_seg);
-    const int k_lo = seg0 * 32 * WARPS;
-    if (seg0 > 0) __syncthreads();   // everyone is done reading the previous segment
-    stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, warp,
-                            lane, WARPS);
-    __syncthreads();
-    for (int j = seg0; j < seg_end; j += CH) {
-      const int cnt = min(CH, seg_end - j);
+    for (int seg0 = 0; seg0 < n_rounds; seg0 += rounds_per_seg) {
+      const int seg_end = min(n_rounds, seg0 + rounds_per_seg);
+      const int k_lo = seg0 * 32 * WARPS;
+      if (!single) {
+        if (seg0 > 0) __syncthreads();   // everyone is done reading the previous segment
+        stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, warp,
+                                lane, WARPS);
+        __syncthreads();
+      }
+      for (int j = seg0; j < seg_end; j += CH) {
+        const int cnt = min(CH, seg_end - j);
 #pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        if (i < cnt) {
-          const int kk = ((j + i) * WARPS + warp) * 32 + t * 8 - k_lo;   // column within xs
-          const uint4 w = wreg[i];
+        for (int i = 0; i < CH; ++i) {
+          if (i < cnt) {
+            const int kk = ((j + i) * WARPS + warp) * 32 + t * 8 - k_lo;   // column within xs
+            const uint4 w = wreg[i];
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const uint4 xa =
-                *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g) * stride + kk);
-            const uint4 xb =
-                *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g + 8) * stride + kk);
-            // K is permuted inside a chunk: lane group t owns elements 8t..8t+7 of both operands
-            mma_bf16_16816(acc[m], xa.x, xb.x, xa.y, xb.y, w.x, w.y);
-            mma_bf16_16816(acc[m], xa.z, xb.z, xa.w, xb.w, w.z, w.w);
+            for (int m = 0; m < MT; ++m) {
+              const uint4 xa =
+                  *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g) * stride + kk);
+              const uint4 xb =
+                  *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g + 8) * stride + kk);
+              // K is permuted inside a chunk: lane group t owns elements 8t..8t+7 of both
+              // operands
+              mma_bf16_16816(acc[m], xa.x, xb.x, xa.y, xb.y, w.x, w.y);
+              mma_bf16_16816(acc[m], xa.z, xb.z, xa.w, xb.w, w.z, w.w);
+            }
           }
         }
+        // the next batch: of this group, or the first of the next group this CTA takes
+        if (j + cnt < n_rounds)
+          load_batch(grp, j + cnt, batch_len(j + cnt));
+        else
+          load_batch(grp + gridDim.x, 0, batch_len(0));
       }
-      load_batch(j + cnt, batch_len(j + cnt));   // the next batch, possibly of the next segment
     }
-  }
 
-  // partial sums of the warps -> shared memory -> epilogue
+    // partial sums of the warps -> shared memory -> epilogue
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
-    float* r0 = red + ((size_t)warp * MT * 16 + m * 16 + g) * 8 + t * 2;
-    float* r1 = r0 + 8 * 8;
-    r0[0] = acc[m][0];
-    r0[1] = acc[m][1];
-    r1[0] = acc[m][2];
-    r1[1] = acc[m][3];
-  }
-  __syncthreads();
-  for (int idx = tid; idx < MT * 16 * 8; idx += WARPS * 32) {
-    const int row = idx >> 3, col = idx & 7;
-    const int nn = n0 + col;
-    if (row >= M || nn >= N) continue;
-    float v = 0.0f;
+    for (int m = 0; m < MT; ++m) {
+      float* r0 = red + ((size_t)warp * MT * 16 + m * 16 + g) * 8 + t * 2;
+      float* r1 = r0 + 8 * 8;
+      r0[0] = acc[m][0];
+      r0[1] = acc[m][1];
+      r1[0] = acc[m][2];
+      r1[1] = acc[m][3];
+    }
+    __syncthreads();
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * MT * 16 + row) * 8 + col];
-    if (bias) v += bias[nn];
-    v = nb_apply_act(v, act);
-    if (residual) v += residual[(size_t)row * N + nn];
-    out[(size_t)row * N + nn] = nb_from_f32<TOut>(v);
+    for (int i = 0; i < EPT; ++i) {
+      const int idx = tid + i * NT;
+      const int row = idx >> 3, col = idx & 7;
+      const int nn = n0 + col;
+      if (idx >= MT * 16 * 8 || row >= M || nn >= N) continue;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * MT * 16 + row) * 8 + col];
+      v += e_bias[i];
+      v = nb_apply_act(v, act);
+      v += e_res[i];
+      out[(size_t)row * N + nn] = nb_from_f32<TOut>(v);
+    }
+    __syncthreads();   // `red` is rewritten for the next group
   }
 }
 
@@ -332,8 +442,22 @@ int launch_bf16(const void* X, const float* gamma, const float* beta, float eps,
   auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, LN, TOut>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(N + 7) / 8, WARPS * 32, smem, stream>>>((const TX*)X, gamma, beta, eps, (const bf16*)W,
-                                                  bias, residual, (TOut*)out, M, N, K, act, kseg);
+  const int n_groups = (N + 7) / 8;
+  const bool single = ((K + unit - 1) / unit) * unit <= kseg;
+  // with one segment the rows are staged once per CTA and the CTA walks over column groups
+  static int resident = 0;   // CTAs of this instantiation that fit on the GPU at once
+  static size_t resident_smem = 0;
+  if (resident == 0 || resident_smem != smem) {
+    int per_sm = 0, dev = 0, sms = 0;
+    NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, WARPS * 32, smem));
+    NB_CUDA(cudaGetDevice(&dev));
+    NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    resident = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
+    resident_smem = smem;
+  }
+  const int grid = (single && n_groups > resident) ? resident : n_groups;
+  kern<<<grid, WARPS * 32, smem, stream>>>((const TX*)X, gamma, beta, eps, (const bf16*)W, bias,
+                                           residual, (TOut*)out, M, N, K, act, kseg);
   return 0;
 }
 
@@ -345,8 +469,13 @@ int dispatch_bf16(const void* X, const float* gamma, const float* beta, float ep
 #define NB_GO(MT_, W_) \
   return launch_bf16<MT_, W_, TX, LN, TOut>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream)
   if (M <= 16) { if (wide) NB_GO(1, 8); else NB_GO(1, 4); }
-  if (M <= 32) { if (wide) NB_GO(2, 8); else NB_GO(2, 4); }
-  if (wide) NB_GO(4, 8); else NB_GO(4, 4);
+  if constexpr (LN) {
+    NB_REQUIRE(false, NB_ERR_UNSUPPORTED,
+               "gemm_skinny: the fused norm takes at most 16 rows (got %d)", M);
+  } else {
+    if (M <= 32) { if (wide) NB_GO(2, 8); else NB_GO(2, 4); }
+    if (wide) NB_GO(4, 8); else NB_GO(4, 4);
+  }
 #undef NB_GO
 }
 

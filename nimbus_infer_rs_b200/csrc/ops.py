@@ -21,6 +21,7 @@ ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GEL
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
+FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to this many rows
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 
 
@@ -126,6 +127,10 @@ class CudaBackend:
                 raise KernelError("linear: residual shape does not match")
         skinny = M <= SKINNY_MAX_ROWS and (w.dtype == torch.float32 or K % 8 == 0)
         if skinny:
+            if norm is not None and (M > FUSED_NORM_MAX_ROWS or w.dtype != torch.bfloat16):
+                h = torch.empty((M, K), device=x.device, dtype=norm[3])
+                self.layernorm(x, norm[0], norm[1], norm[2], h)
+                x, norm = h, None
             gamma, beta, eps = (norm[0], norm[1], norm[2]) if norm is not None else (None, None, 0.0)
             self._call("nb_gemm_skinny", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(gamma),
                        _ptr(beta), c_float(eps), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
