@@ -65,7 +65,8 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
                         const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                         NbPagedKV kv, int group, TOut* __restrict__ out, int out_stride,
                         float scale, int window, int n_splits, float* __restrict__ part_acc,
-                        float* __restrict__ part_ml, int* __restrict__ counters) {
+                        float* __restrict__ part_ml, int* __restrict__ counters, int append,
+                        int k_col, int v_col) {
   constexpr int EPL = Lane16<T>::N;           // elements per lane
   constexpr int LPR = HD / EPL;               // lanes per key row
   constexpr int RPW = 32 / LPR;               // key rows per warp iteration
@@ -151,8 +152,25 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
       cp_async_wait<0>();
     }
     __syncthreads();
-    const T* kt = tiles + (size_t)stage * 2 * TILE;
-    const T* vt = kt + TILE;
+    T* kt = tiles + (size_t)stage * 2 * TILE;
+    T* vt = kt + TILE;
+    if (append && p == pos / PAGE_TOKENS) {
+      // this step's own key and value (row r of the projection output) belong at token `pos`
+      // of this page: put them into the staged tile and into the cache
+      const int in_page = pos % PAGE_TOKENS;
+      const int page_id = table[p];
+      for (int i = tid; i < 2 * LPR; i += THREADS) {
+        const bool is_v = i >= LPR;
+        const int c = (is_v ? i - LPR : i) * EPL;
+        const uint4 val = *reinterpret_cast<const uint4*>(
+            q + (size_t)r * q_stride + (is_v ? v_col : k_col) + (size_t)kvh * HD + c);
+        *reinterpret_cast<uint4*>((is_v ? vt : kt) + in_page * HD + c) = val;
+        T* cache = (T*)(is_v ? kv.v : kv.k);
+        *reinterpret_cast<uint4*>(cache + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE +
+                                  in_page * HD + c) = val;
+      }
+      __syncthreads();
+    }
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int row = warp * KEYS_PER_WARP + it * RPW + sub;   // key within the page
@@ -268,8 +286,8 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
 template <typename T, int HD, int G, typename TOut>
 int launch(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
            const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
-           int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters,
-           cudaStream_t stream) {
+           int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
+           int k_col, int v_col, cudaStream_t stream) {
   const size_t smem = (size_t)4 * PAGE_TOKENS * HD * sizeof(T) +
                       (size_t)(G * HD + WARPS * G * HD + WARPS * G * 2) * sizeof(float);
   auto kern = attention_decode_kernel<T, HD, G, TOut>;
@@ -278,17 +296,17 @@ int launch(const void* q, int q_stride, int q_col, const int* row_slot, const in
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
   kern<<<grid, THREADS, smem, stream>>>((const T*)q, q_stride, q_col, row_slot, row_pos, kv, group,
                                         (TOut*)out, out_stride, scale, window, n_splits, part_acc,
-                                        part_ml, counters);
+                                        part_ml, counters, append, k_col, v_col);
   return 0;
 }
 
 template <typename T, int HD, typename TOut>
 int by_group(int group, const void* q, int q_stride, int q_col, const int* row_slot,
              const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
-             int window, int n_rows, int n_splits, float* pa, float* pm, int* cn,
-             cudaStream_t st) {
+             int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+             int kc, int vc, cudaStream_t st) {
 #define NB_G(G_) \
-  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, st)
+  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   if (group == 1) NB_G(1);
   if (group == 2) NB_G(2);
   if (group <= 4) NB_G(4);
@@ -299,10 +317,10 @@ int by_group(int group, const void* q, int q_stride, int q_col, const int* row_s
 template <typename T, typename TOut>
 int by_head_dim(int hd, int group, const void* q, int q_stride, int q_col, const int* row_slot,
                 const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
-                int window, int n_rows, int n_splits, float* pa, float* pm, int* cn,
-                cudaStream_t st) {
+                int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+                int kc, int vc, cudaStream_t st) {
 #define NB_HD(HD_) \
-  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, st)
+  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   switch (hd) {
     case 16: NB_HD(16);
     case 32: NB_HD(32);
@@ -333,13 +351,17 @@ NB_EXPORT void nb_attention_decode_scratch(int n_rows, int n_heads, int n_kv_hea
   *counter_ints = (long long)n_rows * n_kv_heads;
 }
 
+// append != 0: row r of `q` also holds this step's key and value at columns k_col / v_col;
+// the kernel writes them to the cache at token row_pos[r] and attends to them as well, so no
+// separate append pass is needed.
 NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_col,
                                   const int* row_slot, const int* row_pos, const void* k_cache,
                                   const void* v_cache, const int* block_table, int max_pages,
                                   int page, int n_heads, int n_kv_heads, int head_dim, void* out,
                                   int out_dtype, int out_stride, float scale, int window,
                                   int n_rows, int n_splits, float* part_acc, float* part_ml,
-                                  int* counters, cudaStream_t stream) {
+                                  int* counters, int append, int k_col, int v_col,
+                                  cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(nb_attention_decode_supported(dtype, head_dim, n_heads, n_kv_heads, page),
              NB_ERR_UNSUPPORTED,
@@ -348,11 +370,16 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
   NB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_rows <= 65535 && n_kv_heads <= 65535,
              NB_ERR_UNSUPPORTED, "attention_decode: grid too large");
   NB_REQUIRE(part_acc && part_ml && counters, NB_ERR_BAD_ARG, "attention_decode: scratch missing");
+  if (append) {
+    const int epl = dtype == NB_F32 ? 4 : 8;
+    NB_REQUIRE(q_stride % epl == 0 && k_col % epl == 0 && v_col % epl == 0 && (uintptr_t)q % 16 == 0,
+               NB_ERR_UNSUPPORTED, "attention_decode: keys/values to append must be 16-byte aligned");
+  }
   NbPagedKV kv{(void*)k_cache, (void*)v_cache, block_table, max_pages, page, n_kv_heads, head_dim};
   const int group = n_heads / n_kv_heads;
   typedef __nv_bfloat16 bf16;
   int rc;
-#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, stream
+#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
   if (dtype == NB_F32)
     rc = out_dtype == NB_F32 ? by_head_dim<float, float>(NB_ARGS) : by_head_dim<float, bf16>(NB_ARGS);
   else
@@ -430,5 +457,5 @@ NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride,
                              out_dtype, out_stride, scale, window, n_rows, n_splits,
                              reinterpret_cast<float*>(base + cnt_b + ml_b),
                              reinterpret_cast<float*>(base + cnt_b),
-                             reinterpret_cast<int*>(base), stream);
+                             reinterpret_cast<int*>(base), /*append=*/0, 0, 0, stream);
 }

@@ -182,8 +182,11 @@ class CudaBackend:
                    c_int(kv.page), c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(n_rows),
                    self._stream())
 
-    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0):
-        """Causal attention of the packed rows of ``layout`` over the cache ``kv``."""
+    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
+        """Causal attention of the packed rows of ``layout`` over the cache ``kv``.
+        ``append=(k_col, v_col)``: the rows of ``q_src`` also hold this step's keys and values
+        at those columns; they are written to the cache first (inside the decode kernel, or by
+        a pass of their own before the other kernels)."""
         _check(q_src, "q", kv.k.dtype, 2)
         _check(out, "out", None, 2)
         n_rows = layout.n_rows
@@ -203,8 +206,12 @@ class CudaBackend:
                        c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
                        c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
                        c_int(window), c_int(n_rows), c_int(n_splits), _ptr(acc), _ptr(ml),
-                       _ptr(counters), self._stream())
+                       _ptr(counters), c_int(1 if append else 0),
+                       c_int(append[0] if append else 0), c_int(append[1] if append else 0),
+                       self._stream())
             return
+        if append:
+            self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
         if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
                 c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
                 c_int(kv.n_kv_heads), c_int(kv.page), c_int(q_src.shape[1]), c_int(q_col)):

@@ -43,9 +43,7 @@ class CausalSelfAttention(Mixer):
         lay, kv = ctx.layout, ctx.kv
         qkv = self.qkv(ctx, h, out_dtype=kv.k.dtype)
         ctx.position.rotate(ctx, qkv, self)
-        if ctx.writes_cache:
-            ctx.ops.kv_append(qkv, self.q_width, self.q_width + self.kv_width, lay.row_slot,
-                              lay.row_pos, kv, lay.n_rows)
+        append = (self.q_width, self.q_width + self.kv_width) if ctx.writes_cache else None
         attn = torch.empty((lay.n_rows, self.q_width), device=h.device, dtype=ctx.rt.act_dtype)
-        ctx.ops.attention(qkv, 0, lay, kv, self.n_heads, attn, self.scale, self.window)
+        ctx.ops.attention(qkv, 0, lay, kv, self.n_heads, attn, self.scale, self.window, append)
         self.out(ctx, attn, residual=residual)

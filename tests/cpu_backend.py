@@ -64,7 +64,10 @@ class CpuBackend:
             kv.k[page, :, pos % kv.page, :] = src[r, k_col:k_col + w].view(kv.n_kv_heads, kv.head_dim)
             kv.v[page, :, pos % kv.page, :] = src[r, v_col:v_col + w].view(kv.n_kv_heads, kv.head_dim)
 
-    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0):
+    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
+        if append:
+            self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv,
+                           layout.n_rows)
         hd, group = kv.head_dim, n_heads // kv.n_kv_heads
         for r in range(layout.n_rows):
             slot = int(layout.row_slot[r])

@@ -365,3 +365,25 @@ def test_tensor_core_product(ops, M, N, K):
     ref = ref0 + bias.double() + res.double()
     assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
     ops.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, Hk, hd", [(12, 12, 64), (6, 2, 32), (4, 1, 128), (4, 4, 16)])
+def test_decode_attention_appends_its_own_key_and_value(ops, dtype, H, Hk, hd):
+    """With `append`, the decode kernel must give what append-then-attend gives, and leave the
+    same cache behind; positions at a page start, a page end and mid-page."""
+    lens = [1, 64, 65, 128, 300, 449]               # the new token is the last of each
+    kv_a, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=3 * H + hd)
+    kv_b = LayerKV(kv_a.k.clone(), kv_a.v.clone(), kv_a.block_table, PAGE, Hk, hd)
+    lay = build_layout([(s + 1, [0], []) for s in range(len(lens))], [l - 1 for l in lens], DEV)
+    lay.max_kv_len = 512
+    torch.manual_seed(8)
+    qkv = torch.randn(lay.n_rows, (H + 2 * Hk) * hd, device=DEV).to(dtype)
+    kc, vc = H * hd, (H + Hk) * hd
+    want = torch.empty(lay.n_rows, H * hd, device=DEV, dtype=dtype)
+    ops.kv_append(qkv, kc, vc, lay.row_slot, lay.row_pos, kv_a, lay.n_rows)
+    ops.attention(qkv, 0, lay, kv_a, H, want, 0.2)
+    got = torch.empty_like(want)
+    ops.attention(qkv, 0, lay, kv_b, H, got, 0.2, 0, (kc, vc))
+    assert torch.equal(kv_a.k, kv_b.k) and torch.equal(kv_a.v, kv_b.v)
+    assert torch.equal(got, want)

@@ -78,7 +78,7 @@ def test_static_scratch_variant_matches_the_usual_entry_point(dtype, H, Hk, hd, 
     counters = torch.zeros(n_rows * Hk, dtype=torch.int32, device=DEV)
     want = torch.full((n_rows, H * hd), 3.0, dtype=dtype, device=DEV)
     rc = lib.nb_attention_decode(*common(want), c_void_p(acc.data_ptr()), c_void_p(ml.data_ptr()),
-                                 c_void_p(counters.data_ptr()), stream)
+                                 c_void_p(counters.data_ptr()), c_int(0), c_int(0), c_int(0), stream)
     assert rc == 0, lib.nb_last_error()
     torch.cuda.synchronize()
     assert torch.isfinite(want.float()).all() and (want[1] == 0).all()
