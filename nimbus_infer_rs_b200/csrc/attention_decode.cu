@@ -83,6 +83,8 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
   float* w_ml = w_acc + WARPS * G * HD;                            // [WARPS][G][2]
   __shared__ int s_last;
 
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int sub = lane / LPR, part = lane % LPR;
@@ -294,9 +296,9 @@ int launch(const void* q, int q_stride, int q_col, const int* row_slot, const in
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
-  kern<<<grid, THREADS, smem, stream>>>((const T*)q, q_stride, q_col, row_slot, row_pos, kv, group,
-                                        (TOut*)out, out_stride, scale, window, n_splits, part_acc,
-                                        part_ml, counters, append, k_col, v_col);
+  NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const T*)q, q_stride, q_col, row_slot,
+                    row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits, part_acc,
+                    part_ml, counters, append, k_col, v_col));
   return 0;
 }
 

@@ -52,6 +52,39 @@ void nb_set_error(const char* fmt, ...);
   } while (0)
 
 // ---------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through nb_launch with overlap enabled
+// may start while the kernel before it in the stream is still running; it must execute
+// nb_grid_dependency_wait() before it reads anything an earlier kernel wrote or writes
+// anything at all (before that point it may only fetch constants: weights, biases).  Every
+// kernel calls nb_launch_dependents() early so that its successor can be set up meanwhile.
+// Without the launch attribute both instructions do nothing.
+// ---------------------------------------------------------------------------------
+bool nb_overlap_enabled();
+
+__device__ __forceinline__ void nb_grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+__device__ __forceinline__ void nb_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t nb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = nb_overlap_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------
 // device helpers
 // ---------------------------------------------------------------------------------
 __device__ __forceinline__ float nb_to_f32(float v) { return v; }

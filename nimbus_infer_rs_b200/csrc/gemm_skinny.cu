@@ -241,7 +241,10 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
     return max(0, min(CH, seg_end - j));
   };
   int grp = blockIdx.x;
-  load_batch(grp, 0, batch_len(0));   // in flight while the rows are staged
+  nb_launch_dependents();
+  load_batch(grp, 0, batch_len(0));   // weights: in flight while the predecessor finishes and
+                                      // the rows are staged
+  nb_grid_dependency_wait();
 
   if (LN && single && K <= 256 * VMAX) {
     stage_rows_once<TX, LN>(X, xs, stride, MT * 16, M, K, kseg, gamma, beta, eps, warp, lane, WARPS);
@@ -353,6 +356,8 @@ gemm_skinny_f32_kernel(const TX* __restrict__ X, const float* __restrict__ gamma
                        int N, int K, int act) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);  // [F32_ROWS][K]
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.x * F32_WARPS + warp;
   const float* wrow = W + (size_t)(n < N ? n : 0) * K;
@@ -456,8 +461,8 @@ int launch_bf16(const void* X, const float* gamma, const float* beta, float eps,
     resident_smem = smem;
   }
   const int grid = (single && n_groups > resident) ? resident : n_groups;
-  kern<<<grid, WARPS * 32, smem, stream>>>((const TX*)X, gamma, beta, eps, (const bf16*)W, bias,
-                                           residual, (TOut*)out, M, N, K, act, kseg);
+  NB_CUDA(nb_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, (const TX*)X, gamma, beta, eps,
+                    (const bf16*)W, bias, residual, (TOut*)out, M, N, K, act, kseg));
   return 0;
 }
 
@@ -489,8 +494,9 @@ int launch_f32(const void* X, const float* gamma, const float* beta, float eps, 
   auto kern = gemm_skinny_f32_kernel<TX, LN, TOut>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(N + F32_WARPS - 1) / F32_WARPS, F32_WARPS * 32, smem, stream>>>(
-      (const TX*)X, gamma, beta, eps, (const float*)W, bias, residual, (TOut*)out, M, N, K, act);
+  NB_CUDA(nb_launch(kern, dim3((N + F32_WARPS - 1) / F32_WARPS), dim3(F32_WARPS * 32), smem, stream,
+                    (const TX*)X, gamma, beta, eps, (const float*)W, bias, residual, (TOut*)out, M,
+                    N, K, act));
   return 0;
 }
 

@@ -1,7 +1,7 @@
 // Matrix product on the 5th-generation tensor cores (sm_100a): out[M,N] = act(X[M,K] *
 // W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
 //
-// One CTA computes a 128 x BN tile.  Warp 0 is the producer: one thread issues TMA loads of
+// One CTA computes a 128 x BN tile (BN = 64 or 128).  Warp 0 is the producer: one thread issues TMA loads of
 // 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
 // stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
@@ -136,23 +136,26 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
          ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN>
+// STAGES_ is chosen by the launcher: few stages (about 96 KB) let two CTAs share an SM, so
+// that one CTA's epilogue overlaps the other's main loop; many stages keep more bytes in
+// flight when a few CTAs stream a weight matrix for a handful of rows.
+template <int BN, int STAGES_>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = STAGES_;
   static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
   // after the tiles: full[STAGES], empty[STAGES], accumulator barrier, tmem base, abort flag
   static constexpr int TOTAL = TILES_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024 /* alignment slack */;
 };
 
-template <int BN, typename TOut>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int BN, int STAGES_, typename TOut>
+__global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
                     int K, int act) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, STAGES_>;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment (swizzle atoms), computed on the shared-window address
   const uint32_t raw = smem_u32(smem_dyn);
@@ -354,7 +357,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
   return 0;
 }
 
-template <int BN, typename TOut>
+template <int BN, int STAGES_, typename TOut>
 int launch(const void* X, const void* W, const float* bias, const float* residual, void* out, int M,
            int N, int K, int act, cudaStream_t stream) {
   CUtensorMap mx, mw;
@@ -362,8 +365,8 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   if (rc) return rc;
   rc = make_map(&mw, W, N, K, BN);
   if (rc) return rc;
-  auto kern = gemm_tcgen05_kernel<BN, TOut>;
-  const int smem = SmemLayout<BN>::TOTAL;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES_, TOut>;
+  const int smem = SmemLayout<BN, STAGES_>::TOTAL;
   static bool configured = false;   // per instantiation
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -403,23 +406,24 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   NB_REQUIRE((uintptr_t)X % 16 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                  (uintptr_t)residual % 16 == 0,
              NB_ERR_UNSUPPORTED, "gemm_tcgen05: operands must be 16-byte aligned");
-  // tile width: fill the 148 SMs first, then prefer wider tiles
+  // tile shape: one row tile streaming a weight matrix -> narrow tiles, deep pipeline;
+  // otherwise fill the 148 SMs twice over (two CTAs per SM) before going to wider tiles
   const long long tiles_m = (M + BM - 1) / BM;
-  int bn = 256;
-  if (tiles_m * ((N + 255) / 256) < 2 * 148) bn = 128;
-  if (tiles_m * ((N + 127) / 128) < 148) bn = 64;
+  int shape = 0;   // 0: 64 wide, 8 stages; 1: 64 wide, 4 stages; 2: 128 wide, 3 stages
+  if (tiles_m > 1) shape = (tiles_m * ((N + 127) / 128) >= 2 * 148) ? 2 : 1;
   int rc;
+#define NB_SHAPES(T_)                                                                  \
+  rc = shape == 2 ? launch<128, 3, T_>(X, W, bias, residual, out, M, N, K, act, stream) \
+     : shape == 1 ? launch<64, 4, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
+                  : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
-    rc = bn == 256 ? launch<256, float>(X, W, bias, residual, out, M, N, K, act, stream)
-       : bn == 128 ? launch<128, float>(X, W, bias, residual, out, M, N, K, act, stream)
-                   : launch<64, float>(X, W, bias, residual, out, M, N, K, act, stream);
+    NB_SHAPES(float);
   } else if (out_dtype == NB_BF16) {
-    rc = bn == 256 ? launch<256, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-       : bn == 128 ? launch<128, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-                   : launch<64, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
+    NB_SHAPES(bf16);
   } else {
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
   }
+#undef NB_SHAPES
   if (rc) return rc;
   NB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;

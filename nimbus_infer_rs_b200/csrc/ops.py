@@ -125,7 +125,12 @@ class CudaBackend:
             _check(residual, "residual", torch.float32, 2)
             if residual.shape != out.shape:
                 raise KernelError("linear: residual shape does not match")
-        skinny = M <= SKINNY_MAX_ROWS and (w.dtype == torch.float32 or K % 8 == 0)
+        tensor_core = (x.dtype == torch.bfloat16 or norm is not None and norm[3] == torch.bfloat16) \
+            and w.dtype == torch.bfloat16 and K % 8 == 0 and self.use_tcgen05
+        # few rows: the weight-streaming kernel; from 17 rows on the tensor-core kernel streams
+        # weights faster (TMA ring), where it applies
+        skinny = (M <= FUSED_NORM_MAX_ROWS or (M <= SKINNY_MAX_ROWS and not tensor_core)) \
+            and (w.dtype == torch.float32 or K % 8 == 0)
         if skinny:
             if norm is not None and (M > FUSED_NORM_MAX_ROWS or w.dtype != torch.bfloat16):
                 h = torch.empty((M, K), device=x.device, dtype=norm[3])

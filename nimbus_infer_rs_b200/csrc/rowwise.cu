@@ -18,7 +18,13 @@ void nb_set_error(const char* fmt, ...) {
 
 NB_EXPORT const char* nb_last_error() { return g_error; }
 
-NB_EXPORT int nb_abi_version() { return 1; }
+NB_EXPORT int nb_abi_version() { return 2; }
+
+// Whether kernels are launched so that they may overlap the tail of their predecessor.
+static int g_overlap = 0;
+bool nb_overlap_enabled() { return g_overlap != 0; }
+NB_EXPORT void nb_set_overlap(int on) { g_overlap = on; }
+NB_EXPORT int nb_get_overlap() { return g_overlap; }
 
 // ---------------------------------------------------------------------------------
 // x[r] = wte[token[r]] + wpe[pos[r]]   (src/model.rs:285-295), fp32 result.
@@ -28,6 +34,8 @@ template <typename T>
 __global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
                                  float* __restrict__ out, int d) {
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int r = blockIdx.x;
   const int tok = tokens[r];
   float* o = out + (size_t)r * d;
@@ -50,11 +58,11 @@ NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, c
   NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "embed_pos: bad sizes rows=%d d=%d", n_rows, d);
   const int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_dtype == NB_F32)
-    embed_pos_kernel<float><<<n_rows, threads, 0, stream>>>(tokens, pos, (const float*)wte,
-                                                            (const float*)wpe, out, d);
+    NB_CUDA(nb_launch(embed_pos_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, tokens, pos,
+                      (const float*)wte, (const float*)wpe, out, d));
   else if (table_dtype == NB_BF16)
-    embed_pos_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-        tokens, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d);
+    NB_CUDA(nb_launch(embed_pos_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+                      tokens, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d));
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "embed_pos: unknown table dtype %d", table_dtype);
   NB_CHECK_LAUNCH("embed_pos");
@@ -73,6 +81,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  TOut* __restrict__ out, int d, float eps) {
   extern __shared__ float row[];
   __shared__ float red[32];
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   TOut* o = out + (size_t)r * d;
@@ -102,11 +112,99 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// The same, one warp per row with the row held in registers (one trip to memory): widths that
+// are a multiple of 4 up to 128 * VN.
+template <typename TOut, int VN>
+__global__ void __launch_bounds__(128)
+layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                      TOut* __restrict__ out, int n_rows, int d, float eps) {
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const int src = rows ? rows[r] : r;
+  TOut* o = out + (size_t)r * d;
+  float4 v[VN];
+  const float* xr = x + (size_t)(src < 0 ? 0 : src) * d;
+#pragma unroll
+  for (int i = 0; i < VN; ++i) {
+    const int k = lane * 4 + i * 128;
+    v[i] = (src >= 0 && k < d) ? *reinterpret_cast<const float4*>(xr + k)
+                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VN; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  const float mean = nb_warp_sum(s) / (float)d;
+  float q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VN; ++i) {
+    if (lane * 4 + i * 128 < d) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+      q += (a * a + b * b) + (c * c + e * e);
+    }
+  }
+  const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)d + eps);
+#pragma unroll
+  for (int i = 0; i < VN; ++i) {
+    const int k = lane * 4 + i * 128;
+    if (k >= d) continue;
+    float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (src >= 0) {
+      const float4 gm = *reinterpret_cast<const float4*>(gamma + k);
+      y.x = (v[i].x - mean) * inv * gm.x;
+      y.y = (v[i].y - mean) * inv * gm.y;
+      y.z = (v[i].z - mean) * inv * gm.z;
+      y.w = (v[i].w - mean) * inv * gm.w;
+      if (beta) {
+        const float4 bt = *reinterpret_cast<const float4*>(beta + k);
+        y.x += bt.x; y.y += bt.y; y.z += bt.z; y.w += bt.w;
+      }
+    }
+    if constexpr (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(o + k) = y;
+    } else {
+      uint2 pk;
+      *reinterpret_cast<__nv_bfloat162*>(&pk.x) = __floats2bfloat162_rn(y.x, y.y);
+      *reinterpret_cast<__nv_bfloat162*>(&pk.y) = __floats2bfloat162_rn(y.z, y.w);
+      *reinterpret_cast<uint2*>(o + k) = pk;
+    }
+  }
+}
+
+template <typename TOut>
+int launch_layernorm_warp(const float* x, const int* rows, const float* gamma, const float* beta,
+                          void* out, int n_rows, int d, float eps, cudaStream_t stream) {
+  const dim3 grid((n_rows + 3) / 4), block(128);
+  if (d <= 128 * 2)
+    NB_CUDA(nb_launch(layernorm_warp_kernel<TOut, 2>, grid, block, 0, stream, x, rows, gamma, beta,
+                      (TOut*)out, n_rows, d, eps));
+  else if (d <= 128 * 8)
+    NB_CUDA(nb_launch(layernorm_warp_kernel<TOut, 8>, grid, block, 0, stream, x, rows, gamma, beta,
+                      (TOut*)out, n_rows, d, eps));
+  else
+    NB_CUDA(nb_launch(layernorm_warp_kernel<TOut, 16>, grid, block, 0, stream, x, rows, gamma, beta,
+                      (TOut*)out, n_rows, d, eps));
+  return 0;
+}
+
 NB_EXPORT int nb_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
                            void* out, int out_dtype, int n_rows, int d, float eps,
                            cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "layernorm: bad sizes rows=%d d=%d", n_rows, d);
+  if (d % 4 == 0 && d <= 128 * 16 && (uintptr_t)x % 16 == 0 && (uintptr_t)gamma % 16 == 0 &&
+      (uintptr_t)beta % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+      (out_dtype == NB_F32 || out_dtype == NB_BF16)) {
+    const int rc = out_dtype == NB_F32
+                       ? launch_layernorm_warp<float>(x, rows, gamma, beta, out, n_rows, d, eps, stream)
+                       : launch_layernorm_warp<__nv_bfloat16>(x, rows, gamma, beta, out, n_rows, d,
+                                                              eps, stream);
+    if (rc) return rc;
+    NB_CHECK_LAUNCH("layernorm");
+    return 0;
+  }
   const size_t smem = (size_t)d * sizeof(float);
   NB_REQUIRE(smem <= 200 * 1024, NB_ERR_UNSUPPORTED,
              "layernorm: width %d needs %zu bytes of shared memory (limit 204800)", d, smem);
@@ -115,14 +213,14 @@ NB_EXPORT int nb_layernorm(const float* x, const int* rows, const float* gamma, 
     if (smem > 48 * 1024)
       NB_CUDA(cudaFuncSetAttribute(layernorm_kernel<float>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (float*)out,
-                                                               d, eps);
+    NB_CUDA(nb_launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows,
+                      gamma, beta, (float*)out, d, eps));
   } else if (out_dtype == NB_BF16) {
     if (smem > 48 * 1024)
       NB_CUDA(cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(
-        x, rows, gamma, beta, (__nv_bfloat16*)out, d, eps);
+    NB_CUDA(nb_launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, x,
+                      rows, gamma, beta, (__nv_bfloat16*)out, d, eps));
   } else {
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "layernorm: unknown output dtype %d", out_dtype);
   }
@@ -186,6 +284,8 @@ NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col
 __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ next,
                                       int* __restrict__ row_pos, const int* __restrict__ row_slot,
                                       int n) {
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (row_slot[i] >= 0) {
@@ -199,7 +299,8 @@ __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __res
 NB_EXPORT int nb_advance_decode(int* tokens, const int* next, int* row_pos, const int* row_slot,
                                 int n, cudaStream_t stream) {
   if (n == 0) return 0;
-  advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, next, row_pos, row_slot, n);
+  NB_CUDA(nb_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, next,
+                    row_pos, row_slot, n));
   NB_CHECK_LAUNCH("advance_decode");
   return 0;
 }

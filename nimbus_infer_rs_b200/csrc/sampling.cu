@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
   __shared__ float s_val[THREADS];
   __shared__ int s_idx[THREADS];
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   // every thread starts from element 0, as the reference's scan does
@@ -73,6 +75,8 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, float tem
                           const double* __restrict__ u, int* __restrict__ out) {
   __shared__ double s_red[THREADS];
   __shared__ int s_choice;
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const double temp = fmax((double)temperature, 1e-6);
@@ -145,7 +149,7 @@ NB_EXPORT int nb_repetition_penalty(float* logits, int n_rows, int vocab, const 
 NB_EXPORT int nb_argmax(const float* logits, int n_rows, int vocab, int* out, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(vocab > 0, NB_ERR_BAD_ARG, "argmax: empty vocabulary");
-  argmax_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, out);
+  NB_CUDA(nb_launch(argmax_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, vocab, out));
   NB_CHECK_LAUNCH("argmax");
   return 0;
 }
@@ -154,7 +158,8 @@ NB_EXPORT int nb_sample_temperature(const float* logits, int n_rows, int vocab, 
                                     const double* u, int* out, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(vocab > 0, NB_ERR_BAD_ARG, "sample_temperature: empty vocabulary");
-  sample_temperature_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, temperature, u, out);
+  NB_CUDA(nb_launch(sample_temperature_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, vocab,
+                    temperature, u, out));
   NB_CHECK_LAUNCH("sample_temperature");
   return 0;
 }
