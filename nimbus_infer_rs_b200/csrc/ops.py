@@ -64,6 +64,13 @@ class CudaBackend:
         self._scratch = {}
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
+        # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
+        # the kernel before it (programmatic dependent launch)
+        self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "0") == "1")
+
+    def set_overlap(self, on: bool) -> None:
+        self.lib.nb_set_overlap(c_int(1 if on else 0))
+        self.overlap = bool(on)
 
     # -- plumbing ---------------------------------------------------------------------
     def _stream(self) -> c_void_p:
