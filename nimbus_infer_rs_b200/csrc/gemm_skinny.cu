@@ -145,11 +145,22 @@ __device__ __forceinline__ void stage_rows_once(const TX* __restrict__ X, bf16* 
     }
     const TX* src = X + (size_t)r * K;
     float v[VMAX][8];
+    // the row, and right behind it (not after the reductions) the norm's weight and bias, so
+    // that all of them are one trip to memory
+    uint4 gm_raw[LN ? VMAX : 1][2], bt_raw[LN ? VMAX : 1][2];
 #pragma unroll
     for (int i = 0; i < VMAX; ++i) {
       const int k = lane * 8 + i * 256;
       if (k < K) {
         load8(src + k, v[i]);
+        if constexpr (LN) {
+          gm_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(gamma + k));
+          gm_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(gamma + k + 4));
+          if (beta) {
+            bt_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(beta + k));
+            bt_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(beta + k + 4));
+          }
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[i][e] = 0.0f;
@@ -178,13 +189,11 @@ __device__ __forceinline__ void stage_rows_once(const TX* __restrict__ X, bf16* 
       for (int i = 0; i < VMAX; ++i) {
         const int k = lane * 8 + i * 256;
         if (k < K) {
-          float gm[8];
-          load8(gamma + k, gm);
+          const float* gm = reinterpret_cast<const float*>(&gm_raw[i][0]);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[i][e] = (v[i][e] - mean) * inv * gm[e];
           if (beta) {
-            float bt[8];
-            load8(beta + k, bt);
+            const float* bt = reinterpret_cast<const float*>(&bt_raw[i][0]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[i][e] += bt[e];
           }
@@ -246,6 +255,20 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
                                       // the rows are staged
   nb_grid_dependency_wait();
 
+  // what the epilogue of a column group needs, asked for ahead of time
+  float e_bias[EPT], e_res[EPT];
+  auto load_epilogue = [&](int grp_) {
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      const int idx = tid + i * NT;
+      const int row = idx >> 3, nn = grp_ * 8 + (idx & 7);
+      const bool live = idx < MT * 16 * 8 && row < M && nn < N && grp_ < n_groups;
+      e_bias[i] = (live && bias) ? __ldg(bias + nn) : 0.0f;
+      e_res[i] = (live && residual) ? residual[(size_t)row * N + nn] : 0.0f;
+    }
+  };
+  load_epilogue(grp);
+
   if (LN && single && K <= 256 * VMAX) {
     stage_rows_once<TX, LN>(X, xs, stride, MT * 16, M, K, kseg, gamma, beta, eps, warp, lane, WARPS);
   } else {
@@ -261,16 +284,6 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
 
   for (; grp < n_groups; grp += gridDim.x) {
     const int n0 = grp * 8;
-    // what the epilogue will need, asked for now
-    float e_bias[EPT], e_res[EPT];
-#pragma unroll
-    for (int i = 0; i < EPT; ++i) {
-      const int idx = tid + i * NT;
-      const int row = idx >> 3, nn = n0 + (idx & 7);
-      const bool live = idx < MT * 16 * 8 && row < M && nn < N;
-      e_bias[i] = (live && bias) ? __ldg(bias + nn) : 0.0f;
-      e_res[i] = (live && residual) ? residual[(size_t)row * N + nn] : 0.0f;
-    }
     float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -339,6 +352,7 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
       v += e_res[i];
       out[(size_t)row * N + nn] = nb_from_f32<TOut>(v);
     }
+    load_epilogue(grp + gridDim.x);   // for the next group this CTA takes
     __syncthreads();   // `red` is rewritten for the next group
   }
 }
@@ -473,7 +487,8 @@ int dispatch_bf16(const void* X, const float* gamma, const float* beta, float ep
   const bool wide = K > 1024;
 #define NB_GO(MT_, W_) \
   return launch_bf16<MT_, W_, TX, LN, TOut>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream)
-  if (M <= 16) { if (wide) NB_GO(1, 8); else NB_GO(1, 4); }
+  // eight warps when K is long, or when a fused norm has more than four rows to bring in
+  if (M <= 16) { if (wide || (LN && M > 4)) NB_GO(1, 8); else NB_GO(1, 4); }
   if constexpr (LN) {
     NB_REQUIRE(false, NB_ERR_UNSUPPORTED,
                "gemm_skinny: the fused norm takes at most 16 rows (got %d)", M);

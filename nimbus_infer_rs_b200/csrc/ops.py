@@ -62,6 +62,7 @@ class CudaBackend:
         self.lib.nb_last_error.restype = ctypes.c_char_p
         self.launches = 0  # kernels launched through this backend (for measurement reports)
         self._scratch = {}
+        self._argmax_scratch = {}
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
@@ -257,6 +258,16 @@ class CudaBackend:
         _check(logits, "logits", torch.float32, 2)
         _check(out, "out", torch.int32, 1)
         n, v = logits.shape
+        n_ctas = min(32, max(1, v // 2048))
+        if n_ctas > 1 and n * n_ctas <= 4096:
+            s = self._argmax_scratch.get(logits.device)
+            if s is None or s[0].numel() < n:
+                s = (torch.zeros(max(n, 256), dtype=torch.int64, device=logits.device),
+                     torch.zeros(max(n, 256), dtype=torch.int32, device=logits.device))
+                self._argmax_scratch[logits.device] = s
+            self._call("nb_argmax_split", _ptr(logits), c_int(n), c_int(v), _ptr(out), _ptr(s[0]),
+                       _ptr(s[1]), c_int(n_ctas), self._stream())
+            return
         self._call("nb_argmax", _ptr(logits), c_int(n), c_int(v), _ptr(out), self._stream())
 
     def sample_temperature(self, logits, temperature, u, out):

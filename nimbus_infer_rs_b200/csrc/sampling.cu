@@ -67,6 +67,64 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   if (tid == 0) out[r] = s_idx[0];
 }
 
+// The same over several CTAs per row (a large vocabulary scanned by one CTA is bound by
+// latency).  Each CTA reduces its slice to one (value, index) pair, packs it into a 64-bit key
+// whose unsigned order is "greater value first, then lower index", and merges it into the
+// row's key with atomicMax; the CTA that arrives last for a row unpacks the winner and leaves
+// key and counter at zero for the next launch.  NaN maps to the lowest key, so it never wins;
+// if nothing beats it the answer is index 0, as in the single-CTA scan.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+  if (v == 0.0f) v = 0.0f;                              // -0 and +0 tie, as they compare equal
+  unsigned int b = __float_as_uint(v);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);       // order-preserving map of finite floats
+  if (v != v) b = 0u;                                    // NaN: lowest
+  return ((unsigned long long)b << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)idx);
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_split_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out,
+                    unsigned long long* __restrict__ keys, int* __restrict__ counters) {
+  __shared__ unsigned long long s_key[THREADS / 32];
+  __shared__ int s_last;
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int r = blockIdx.y, tid = threadIdx.x;
+  const int per = (vocab + gridDim.x - 1) / gridDim.x;
+  const int i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
+  const float* row = logits + (size_t)r * vocab;
+  unsigned long long best = 0ull;
+  for (int i = i0 + tid; i < i1; i += THREADS) {
+    const unsigned long long k = argmax_key(row[i], i);
+    best = k > best ? k : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((tid & 31) == 0) s_key[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < THREADS / 32; ++w) best = s_key[w] > best ? s_key[w] : best;
+    atomicMax(&keys[r], best);
+    __threadfence();
+    const int old = atomicAdd(&counters[r], 1);
+    s_last = (old == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_last && tid == 0) {
+    __threadfence();
+    const unsigned long long k = atomicExch(&keys[r], 0ull);
+    counters[r] = 0;
+    // The sequential scan starts from element 0 and replaces it only by something strictly
+    // greater: if element 0 is NaN nothing ever is, and the answer is 0.  Key 0 means every
+    // element was NaN: index 0 as well.
+    const float first = row[0];
+    out[r] = ((k >> 32) == 0ull || first != first)
+                 ? 0 : (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull));
+  }
+}
+
 // Temperature sampling by inverse CDF in f64.  u[r] in [0,1) comes from the sequence's own
 // generator on the host.  Each thread owns a contiguous segment of the vocabulary, so the
 // walk over the cumulative sum visits the tokens in index order as the reference does.
@@ -143,6 +201,21 @@ NB_EXPORT int nb_repetition_penalty(float* logits, int n_rows, int vocab, const 
   repetition_penalty_kernel<<<n_rows, 128, 0, stream>>>(logits, vocab, history, history_stride,
                                                         history_len, penalty);
   NB_CHECK_LAUNCH("repetition_penalty");
+  return 0;
+}
+
+// Scratch: `keys` (8 bytes per row) and `counters` (4 bytes per row), zero before the first
+// use; every launch leaves them at zero.  n_ctas CTAs scan each row.
+NB_EXPORT int nb_argmax_split(const float* logits, int n_rows, int vocab, int* out,
+                              unsigned long long* keys, int* counters, int n_ctas,
+                              cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0 && n_ctas >= 1 && n_rows <= 65535, NB_ERR_BAD_ARG,
+             "argmax_split: bad sizes rows=%d vocab=%d ctas=%d", n_rows, vocab, n_ctas);
+  NB_REQUIRE(keys && counters, NB_ERR_BAD_ARG, "argmax_split: scratch missing");
+  NB_CUDA(nb_launch(argmax_split_kernel, dim3(n_ctas, n_rows), dim3(THREADS), 0, stream, logits,
+                    vocab, out, keys, counters));
+  NB_CHECK_LAUNCH("argmax_split");
   return 0;
 }
 
