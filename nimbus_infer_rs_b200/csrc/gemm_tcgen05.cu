@@ -1,14 +1,15 @@
 // Matrix product on the 5th-generation tensor cores (sm_100a): out[M,N] = act(X[M,K] *
 // W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
 //
-// One CTA computes a 128 x BN tile (BN = 64 or 128).  Warp 0 is the producer: one thread issues TMA loads of
+// A CTA computes 128 x BN tiles (BN = 64 or 128), one after another.  Warp 0 is the producer: one thread issues TMA loads of
 // 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
 // stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
 // with shared-memory matrix descriptors; `tcgen05.commit` hands a stage back to the producer
-// and, after the last K block, signals the accumulator.  Warps 2..5 are the epilogue: each
-// reads its 32-lane quarter of the accumulator with `tcgen05.ld`, applies bias / GELU /
-// residual in fp32 and stores its rows.  Edges need no special code on the load side: TMA
+// and, after the last K block of a tile, signals that tile's accumulator (there are two, used
+// in turn).  Warps 2..5 are the epilogue: each reads its 32-lane quarter of the accumulator
+// with `tcgen05.ld`, hands the accumulator back, applies bias / GELU / residual in fp32 and
+// stores its rows while the MMAs of the next tile already run.  Edges need no special code on the load side: TMA
 // zero-fills rows beyond M or N and columns beyond K.
 //
 // Every wait on an mbarrier is bounded by a clock budget; a wait that runs out raises an
@@ -136,9 +137,8 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
          ((uint32_t)(m >> 4) << 24);
 }
 
-// STAGES_ is chosen by the launcher: few stages (about 96 KB) let two CTAs share an SM, so
-// that one CTA's epilogue overlaps the other's main loop; many stages keep more bytes in
-// flight when a few CTAs stream a weight matrix for a handful of rows.
+// One CTA per SM (about 192 KB of stages) walks over tiles; two accumulators in tensor memory
+// let the epilogue of one tile overlap the main loop of the next.
 template <int BN, int STAGES_>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -146,15 +146,17 @@ struct SmemLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = STAGES_;
   static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
-  // after the tiles: full[STAGES], empty[STAGES], accumulator barrier, tmem base, abort flag
-  static constexpr int TOTAL = TILES_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024 /* alignment slack */;
+  // after the tiles: full[STAGES], empty[STAGES], accumulator full[2] / empty[2], then the
+  // tensor-memory base address and the abort flag
+  static constexpr int N_BARRIERS = 2 * STAGES + 4;
+  static constexpr int TOTAL = TILES_BYTES + N_BARRIERS * 8 + 16 + 1024 /* alignment slack */;
 };
 
 template <int BN, int STAGES_, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
-                    int K, int act) {
+                    int K, int act, int tiles_n, int num_tiles) {
   using L = SmemLayout<BN, STAGES_>;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment (swizzle atoms), computed on the shared-window address
@@ -164,12 +166,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const uint32_t bars = base + L::TILES_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (L::STAGES + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * L::STAGES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + (2 * L::STAGES + 1) * 8);
+  auto acc_full = [&](int b) { return bars + 8u * (2 * L::STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * L::STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + L::N_BARRIERS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int num_kb = (K + BK - 1) / BK;
 
   if (tid == 0) {
@@ -177,15 +179,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);   // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  if (warp == 1) {   // the whole warp allocates BN columns of tensor memory
+  if (warp == 1) {   // the whole warp allocates two accumulators of BN columns each
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)(2 * BN))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -194,55 +199,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   tc05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the shared-memory
+  // ring runs on across tiles, and while the epilogue drains one accumulator the MMAs of the
+  // next tile fill the other.
   if (warp == 0) {
     if (lane == 0) {   // ---------------------------------------------------- TMA producer
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % L::STAGES;
-        const uint32_t phase = (uint32_t)(kb / L::STAGES) & 1u;
-        if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag)) break;
-        mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
-        const uint32_t a_dst = base + s * L::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
-        tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t phase = (it / L::STAGES) & 1u;
+          ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          const uint32_t a_dst = base + s * L::STAGE_BYTES;
+          tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
+          tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // ---------------------------------------------------- MMA issuer
       constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % L::STAGES;
-        const uint32_t phase = (uint32_t)(kb / L::STAGES) & 1u;
-        ok = mbar_wait(full_bar(s), phase, abort_flag);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
+        ok = mbar_wait(acc_empty(ab), aphase ^ 1u, abort_flag);   // the epilogue has drained it
         if (!ok) break;
         tc05_fence_after();
-        const uint32_t a_addr = base + s * L::STAGE_BYTES;
-        const uint64_t da = smem_desc_sw128(a_addr);
-        const uint64_t db = smem_desc_sw128(a_addr + L::A_BYTES);
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t phase = (it / L::STAGES) & 1u;
+          ok = mbar_wait(full_bar(s), phase, abort_flag);
+          if (!ok) break;
+          tc05_fence_after();
+          const uint32_t a_addr = base + s * L::STAGE_BYTES;
+          const uint64_t da = smem_desc_sw128(a_addr);
+          const uint64_t db = smem_desc_sw128(a_addr + L::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing K by 16 elements inside the swizzle atom = 32 bytes = 2 address units
-          tc05_mma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                        (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 elements inside the swizzle atom = 32 bytes = 2 address units
+            tc05_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                          (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc05_commit(empty_bar(s));   // the stage is free once these MMAs have read it
         }
-        tc05_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+        if (ok) tc05_commit(acc_full(ab));   // complete once all MMAs issued so far are done
       }
-      if (ok) tc05_commit(acc_bar);  // the accumulator is complete once all MMAs are done
     }
   } else {             // ------------------------------------------------------ epilogue
     const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
-    const int m = m0 + quarter * 32 + lane;
-    // lane 0 decides for the warp: the tensor-memory loads below need all 32 lanes
-    const bool ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_bar, 0u, abort_flag), 0) != 0;
-    if (ready) {
+    const bool vec_f32 = (N % 4 == 0);
+    const bool vec_b16 = (N % 8 == 0);
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int m = m0 + quarter * 32 + lane;
+      const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
+      // lane 0 decides for the warp: the tensor-memory loads below need all 32 lanes
+      const bool ready =
+          __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
+      if (!ready) break;
       tc05_fence_after();
-      const bool vec_f32 = (N % 4 == 0);
-      const bool vec_b16 = (N % 8 == 0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
-        tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+        tc05_ld_32x32b_x32(
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + (uint32_t)(c * 32), v);
         tc05_wait_ld();
+        if (c == BN / 32 - 1) {   // this warp has read all of the accumulator: hand it back
+          tc05_fence_before();
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
+        }
         const int nb = n0 + c * 32;
         if (m < M && nb < N) {
           float f[32];
@@ -316,7 +350,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 1) {
     tc05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)(2 * BN))
                  : "memory");
   }
 }
@@ -372,8 +406,18 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kern<<<grid, THREADS, smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act);
+  const int tiles_n = (N + BN - 1) / BN;
+  const long long num_tiles = (long long)tiles_n * ((M + BM - 1) / BM);
+  NB_REQUIRE(num_tiles < (1ll << 31), NB_ERR_UNSUPPORTED, "gemm_tcgen05: too many tiles");
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    NB_CUDA(cudaGetDevice(&dev));
+    NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
+  kern<<<grid, THREADS, smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
+                                        (int)num_tiles);
   return 0;
 }
 
@@ -409,13 +453,12 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   // tile shape: one row tile streaming a weight matrix -> narrow tiles, deep pipeline;
   // otherwise fill the 148 SMs twice over (two CTAs per SM) before going to wider tiles
   const long long tiles_m = (M + BM - 1) / BM;
-  int shape = 0;   // 0: 64 wide, 8 stages; 1: 64 wide, 4 stages; 2: 128 wide, 3 stages
-  if (tiles_m > 1) shape = (tiles_m * ((N + 127) / 128) >= 2 * 148) ? 2 : 1;
+  // narrow tiles until there are enough of them for every SM to have two
+  const bool wide = tiles_m * ((N + 127) / 128) >= 2 * 148;
   int rc;
-#define NB_SHAPES(T_)                                                                  \
-  rc = shape == 2 ? launch<128, 3, T_>(X, W, bias, residual, out, M, N, K, act, stream) \
-     : shape == 1 ? launch<64, 4, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
-                  : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
+#define NB_SHAPES(T_)                                                              \
+  rc = wide ? launch<128, 6, T_>(X, W, bias, residual, out, M, N, K, act, stream) \
+            : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
     NB_SHAPES(float);
   } else if (out_dtype == NB_BF16) {
