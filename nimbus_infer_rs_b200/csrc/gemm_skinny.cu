@@ -52,159 +52,114 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return u;
 }
 
-// Row statistics for a fused LayerNorm: stats[r] = (mean, 1/sqrt(var + eps)); one warp per row,
-// two passes over the row (mean, then the squared deviations).  K is a multiple of 8.
-template <typename TX>
-__device__ __forceinline__ void row_stats(const TX* __restrict__ X, float2* stats, int M, int K,
-                                          float eps, int warp, int lane, int n_warps) {
-  for (int r = warp; r < M; r += n_warps) {
-    const TX* src = X + (size_t)r * K;
-    float s = 0.0f;
-    for (int k = lane * 8; k < K; k += 256) {
-      float v[8];
-      load8(src + k, v);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s += v[e];
-    }
-    const float mean = nb_warp_sum(s) / (float)K;
-    float q = 0.0f;
-    for (int k = lane * 8; k < K; k += 256) {
-      float v[8];
-      load8(src + k, v);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float c = v[e] - mean;
-        q = fmaf(c, c, q);
-      }
-    }
-    const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
-    if (lane == 0) stats[r] = make_float2(mean, inv);
-  }
-}
-
-// Columns [k_lo, k_lo + width) of the rows of X into shared memory as bf16, optionally
-// normalised; rows M..rows_pad and columns at or beyond K are zero.  One warp per row, eight
-// elements per lane and step.
-template <typename TX, bool LN>
-__device__ __forceinline__ void stage_rows_bf16(const TX* __restrict__ X, bf16* xs, int stride,
-                                                int rows_pad, int M, int K, int k_lo, int width,
-                                                const float* __restrict__ gamma,
-                                                const float* __restrict__ beta,
-                                                const float2* stats, int warp, int lane,
-                                                int n_warps) {
-  for (int r = warp; r < rows_pad; r += n_warps) {
-    bf16* dst = xs + (size_t)r * stride;
-    const TX* src = X + (size_t)r * K;
-    float2 st = make_float2(0.0f, 1.0f);
-    if constexpr (LN) {
-      if (r < M) st = stats[r];
-    }
-    for (int kk = lane * 8; kk < width; kk += 256) {
-      const int k = k_lo + kk;
-      uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-      if (r < M && k < K) {
-        float v[8];
-        load8(src + k, v);
-        if constexpr (LN) {
-          float gm[8];
-          load8(gamma + k, gm);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = (v[e] - st.x) * st.y * gm[e];
-          if (beta) {
-            float bt[8];
-            load8(beta + k, bt);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += bt[e];
-          }
-        }
-        packed = pack8(v);
-      }
-      *reinterpret_cast<uint4*>(dst + kk) = packed;
-    }
-  }
-}
-
 constexpr int CH = 12;   // 32-wide K chunks whose weights a warp holds in registers at a time
-constexpr int VMAX = 8;  // 8-element vectors of a row a lane may hold (rows up to 2048 wide)
+constexpr int VMAX = 8;  // most 8-element vectors of a row a thread may hold while it is normalised
 
-// All of K at once: every warp brings whole rows through registers (one trip to memory per
-// row), takes mean and variance from the registers (two passes, src/ops.rs:32-40), and
-// writes the normalised bf16 row to shared memory.  Needs K <= 256 * VMAX.
-template <typename TX, bool LN>
-__device__ __forceinline__ void stage_rows_once(const TX* __restrict__ X, bf16* xs, int stride,
-                                                int rows_pad, int M, int K, int width,
+// Sum of `v` over the `tpr` consecutive threads that share a row (tpr is a multiple of 32 and
+// divides the block).  `part` holds one float per warp.  Every thread of the block calls it.
+__device__ __forceinline__ float row_group_sum(float v, float* part, int tid, int tpr) {
+  v = nb_warp_sum(v);
+  if (tpr == 32) return v;
+  __syncthreads();
+  if ((tid & 31) == 0) part[tid >> 5] = v;
+  __syncthreads();
+  const int first = (tid / tpr) * (tpr >> 5);
+  float s = 0.0f;
+  for (int w = 0; w < (tpr >> 5); ++w) s += part[first + w];
+  return s;
+}
+
+// Rows of X, LayerNorm applied, into shared memory as bf16 -- all threads of the block share
+// the work of every row: a row belongs to `tpr` consecutive threads, each thread holds its
+// vectors of the row in registers (one trip to memory for the row, the norm's weight and its
+// bias together), mean and variance are reduced over the row's threads (two passes over the
+// registers, src/ops.rs:32-40).  Needs K <= 8 * tpr * VPT; only the M real rows are written.
+template <int NT, int VPT>
+__device__ __forceinline__ void stage_rows_norm(const float* __restrict__ X, bf16* xs, int stride,
+                                                int M, int K, int width,
                                                 const float* __restrict__ gamma,
                                                 const float* __restrict__ beta, float eps,
-                                                int warp, int lane, int n_warps) {
-  for (int r = warp; r < rows_pad; r += n_warps) {
-    bf16* dst = xs + (size_t)r * stride;
-    if (r >= M) {
-      for (int kk = lane * 8; kk < width; kk += 256)
-        *reinterpret_cast<uint4*>(dst + kk) = make_uint4(0u, 0u, 0u, 0u);
-      continue;
-    }
-    const TX* src = X + (size_t)r * K;
-    float v[VMAX][8];
-    // the row, and right behind it (not after the reductions) the norm's weight and bias, so
-    // that all of them are one trip to memory
-    uint4 gm_raw[LN ? VMAX : 1][2], bt_raw[LN ? VMAX : 1][2];
+                                                float* part, int tid, int tpr) {
+  const int rows_per_pass = NT / tpr;
+  const int tr = tid % tpr;
+  for (int r0 = 0; r0 < M; r0 += rows_per_pass) {
+    const int r = r0 + tid / tpr;
+    const bool live = r < M;
+    const float* src = X + (size_t)(live ? r : 0) * K;
+    float v[VPT][8];
+    uint4 gm_raw[VPT][2], bt_raw[VPT][2];
 #pragma unroll
-    for (int i = 0; i < VMAX; ++i) {
-      const int k = lane * 8 + i * 256;
-      if (k < K) {
+    for (int i = 0; i < VPT; ++i) {
+      const int k = (tr + i * tpr) * 8;
+      if (live && k < K) {
         load8(src + k, v[i]);
-        if constexpr (LN) {
-          gm_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(gamma + k));
-          gm_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(gamma + k + 4));
-          if (beta) {
-            bt_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(beta + k));
-            bt_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(beta + k + 4));
-          }
+        gm_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(gamma + k));
+        gm_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(gamma + k + 4));
+        if (beta) {
+          bt_raw[i][0] = __ldg(reinterpret_cast<const uint4*>(beta + k));
+          bt_raw[i][1] = __ldg(reinterpret_cast<const uint4*>(beta + k + 4));
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[i][e] = 0.0f;
       }
     }
-    if constexpr (LN) {
-      float s = 0.0f;
+    float s = 0.0f;
 #pragma unroll
-      for (int i = 0; i < VMAX; ++i)
+    for (int i = 0; i < VPT; ++i)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s += v[i][e];
-      const float mean = nb_warp_sum(s) / (float)K;
-      float q = 0.0f;
+      for (int e = 0; e < 8; ++e) s += v[i][e];
+    const float mean = row_group_sum(s, part, tid, tpr) / (float)K;
+    float q = 0.0f;
 #pragma unroll
-      for (int i = 0; i < VMAX; ++i) {
-        if (lane * 8 + i * 256 < K) {
+    for (int i = 0; i < VPT; ++i) {
+      if (live && (tr + i * tpr) * 8 < K) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float c = v[i][e] - mean;
-            q = fmaf(c, c, q);
-          }
-        }
-      }
-      const float inv = 1.0f / sqrtf(nb_warp_sum(q) / (float)K + eps);
-#pragma unroll
-      for (int i = 0; i < VMAX; ++i) {
-        const int k = lane * 8 + i * 256;
-        if (k < K) {
-          const float* gm = reinterpret_cast<const float*>(&gm_raw[i][0]);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[i][e] = (v[i][e] - mean) * inv * gm[e];
-          if (beta) {
-            const float* bt = reinterpret_cast<const float*>(&bt_raw[i][0]);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[i][e] += bt[e];
-          }
+        for (int e = 0; e < 8; ++e) {
+          const float c = v[i][e] - mean;
+          q = fmaf(c, c, q);
         }
       }
     }
+    const float inv = 1.0f / sqrtf(row_group_sum(q, part, tid, tpr) / (float)K + eps);
 #pragma unroll
-    for (int i = 0; i < VMAX; ++i) {
-      const int kk = lane * 8 + i * 256;
-      if (kk < width) *reinterpret_cast<uint4*>(dst + kk) = pack8(v[i]);
+    for (int i = 0; i < VPT; ++i) {
+      const int k = (tr + i * tpr) * 8;
+      if (!live || k >= width) continue;
+      if (k < K) {
+        const float* gm = reinterpret_cast<const float*>(&gm_raw[i][0]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = (v[i][e] - mean) * inv * gm[e];
+        if (beta) {
+          const float* bt = reinterpret_cast<const float*>(&bt_raw[i][0]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += bt[e];
+        }
+      }
+      *reinterpret_cast<uint4*>(xs + (size_t)r * stride + k) = pack8(v[i]);
     }
+    // columns of the staged width that lie beyond the vectors held in registers: zero
+    for (int k = (tr + VPT * tpr) * 8; live && k < width; k += tpr * 8)
+      *reinterpret_cast<uint4*>(xs + (size_t)r * stride + k) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Columns [k_lo, k_lo + width) of the M rows of X into shared memory as bf16 (no norm); columns
+// at or beyond K are zero.  The vectors are spread over all threads of the block.
+template <typename TX>
+__device__ __forceinline__ void stage_rows_copy(const TX* __restrict__ X, bf16* xs, int stride,
+                                                int M, int K, int k_lo, int width, int tid,
+                                                int n_threads) {
+  const int vpr = width >> 3;   // vectors per row
+  for (int idx = tid; idx < M * vpr; idx += n_threads) {
+    const int r = idx / vpr, kk = (idx - r * vpr) * 8, k = k_lo + kk;
+    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+    if (k < K) {
+      float v[8];
+      load8(X + (size_t)r * K + k, v);
+      packed = pack8(v);
+    }
+    *reinterpret_cast<uint4*>(xs + (size_t)r * stride + kk) = packed;
   }
 }
 
@@ -212,19 +167,22 @@ __device__ __forceinline__ void stage_rows_once(const TX* __restrict__ X, bf16* 
 // fit in shared memory; within a segment chunk c of 32 columns belongs to warp c % WARPS.
 // With a single segment the rows are staged once and the CTA walks over column groups
 // blockIdx.x, blockIdx.x + gridDim.x, ... with the next group's weights already in flight.
-template <int MT, int WARPS, typename TX, bool LN, typename TOut>
+// Only the M real rows live in shared memory; the other rows of the 16-row MMA tile are zero
+// registers.  A fused norm needs a single segment (the launcher sees to it).
+template <int MT, int WARPS, typename TX, int VPT, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
                         const float* __restrict__ beta, float eps, const bf16* __restrict__ W,
                         const float* __restrict__ bias, const float* residual, TOut* out, int M,
-                        int N, int K, int act, int kseg) {
+                        int N, int K, int act, int kseg, int tpr) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr bool LN = VPT > 0;   // VPT: vectors of a row per thread for the fused norm; 0 = none
   constexpr int NT = WARPS * 32;
   constexpr int EPT = (MT * 16 * 8 + NT - 1) / NT;   // outputs per thread and column group
   const int stride = kseg + 8;
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                           // [MT*16][stride]
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)MT * 16 * stride * sizeof(bf16));
-  float2* stats = reinterpret_cast<float2*>(red + WARPS * MT * 16 * 8);   // [MT*16]
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                           // [M][stride]
+  float* red = reinterpret_cast<float*>(smem_raw + (((size_t)M * stride * sizeof(bf16) + 15) & ~(size_t)15));
+  float* part = red + WARPS * MT * 16 * 8;                                // [WARPS]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_groups = (N + 7) / 8;
@@ -233,13 +191,13 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
   const bool single = n_rounds <= rounds_per_seg;
 
   uint4 wreg[CH];
-  auto load_batch = [&](int grp, int j0, int cnt) {
-    const int n = grp * 8 + g;
+  auto load_batch = [&](int grp_, int j0, int cnt) {
+    const int n = grp_ * 8 + g;
     const bf16* wrow = W + (size_t)(n < N ? n : 0) * K;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       const int k = ((j0 + i) * WARPS + warp) * 32 + t * 8;
-      if (i < cnt && k < K && n < N && grp < n_groups)
+      if (i < cnt && k < K && n < N && grp_ < n_groups)
         wreg[i] = __ldg(reinterpret_cast<const uint4*>(wrow + k));
       else
         wreg[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -269,18 +227,21 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
   };
   load_epilogue(grp);
 
-  if (LN && single && K <= 256 * VMAX) {
-    stage_rows_once<TX, LN>(X, xs, stride, MT * 16, M, K, kseg, gamma, beta, eps, warp, lane, WARPS);
+  if constexpr (LN) {
+    stage_rows_norm<NT, (VPT > 0 ? VPT : 1)>(reinterpret_cast<const float*>(X), xs, stride, M, K,
+                                             kseg, gamma, beta, eps, part, tid, tpr);
   } else {
-    if constexpr (LN) {
-      row_stats<TX>(X, stats, M, K, eps, warp, lane, WARPS);
-      __syncthreads();
-    }
-    if (single)
-      stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, 0, kseg, gamma, beta, stats, warp,
-                              lane, WARPS);
+    if (single) stage_rows_copy<TX>(X, xs, stride, M, K, 0, kseg, tid, NT);
   }
   if (single) __syncthreads();
+
+  // rows of the MMA tile that exist
+  bool row_a[MT], row_b[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    row_a[m] = m * 16 + g < M;
+    row_b[m] = m * 16 + g + 8 < M;
+  }
 
   for (; grp < n_groups; grp += gridDim.x) {
     const int n0 = grp * 8;
@@ -295,8 +256,7 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
       const int k_lo = seg0 * 32 * WARPS;
       if (!single) {
         if (seg0 > 0) __syncthreads();   // everyone is done reading the previous segment
-        stage_rows_bf16<TX, LN>(X, xs, stride, MT * 16, M, K, k_lo, kseg, gamma, beta, stats, warp,
-                                lane, WARPS);
+        stage_rows_copy<TX>(X, xs, stride, M, K, k_lo, kseg, tid, NT);
         __syncthreads();
       }
       for (int j = seg0; j < seg_end; j += CH) {
@@ -308,10 +268,11 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
             const uint4 w = wreg[i];
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              const uint4 xa =
-                  *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g) * stride + kk);
-              const uint4 xb =
-                  *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g + 8) * stride + kk);
+              uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
+              if (row_a[m])
+                xa = *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g) * stride + kk);
+              if (row_b[m])
+                xb = *reinterpret_cast<const uint4*>(xs + (size_t)(m * 16 + g + 8) * stride + kk);
               // K is permuted inside a chunk: lane group t owns elements 8t..8t+7 of both
               // operands
               mma_bf16_16816(acc[m], xa.x, xb.x, xa.y, xb.y, w.x, w.y);
@@ -446,38 +407,74 @@ gemm_skinny_f32_kernel(const TX* __restrict__ X, const float* __restrict__ gamma
   }
 }
 
-template <int MT, int WARPS, typename TX, bool LN, typename TOut>
-int launch_bf16(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+// Threads that share a row while it is normalised: the block divided by the rows (rounded up
+// to a power of two), at least a warp.
+inline int norm_threads_per_row(int n_threads, int M) {
+  int mp = 1;
+  while (mp < M) mp <<= 1;
+  return n_threads / mp < 32 ? 32 : n_threads / mp;
+}
+
+template <int MT, int WARPS, typename TX, int VPT, typename TOut>
+int launch_bf16_v(const void* X, const float* gamma, const float* beta, float eps, const void* W,
                 const float* bias, const float* residual, void* out, int M, int N, int K, int act,
                 cudaStream_t stream) {
   // segment of K whose staged rows take about 96 KB at most (two CTAs per SM)
+  constexpr int NT = WARPS * 32;
   const int unit = 32 * WARPS;
-  const int cap = (96 * 1024) / (MT * 16 * (int)sizeof(bf16));
+  const int cap = (96 * 1024) / (M * (int)sizeof(bf16));
   int kseg = ((K + unit - 1) / unit) * unit;
-  if (kseg > cap) kseg = (cap / unit) * unit;
+  const bool single = kseg <= cap;
+  if (!single) kseg = (cap / unit) * unit;
   if (kseg < unit) kseg = unit;
-  const size_t smem = (size_t)MT * 16 * (kseg + 8) * sizeof(bf16) +
-                      (size_t)WARPS * MT * 16 * 8 * sizeof(float) + (size_t)MT * 16 * sizeof(float2);
-  auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, LN, TOut>;
+  constexpr bool LN = VPT > 0;
+  const int tpr = norm_threads_per_row(NT, M);
+  if (LN) {
+    NB_REQUIRE(single && K <= 8 * tpr * VPT, NB_ERR_UNSUPPORTED,
+               "gemm_skinny: a fused norm takes rows up to %d wide for %d rows (got %d)",
+               8 * tpr * VPT, M, K);
+  }
+  const size_t xs_bytes = (((size_t)M * (kseg + 8) * sizeof(bf16)) + 15) & ~(size_t)15;
+  const size_t smem = xs_bytes + (size_t)WARPS * MT * 16 * 8 * sizeof(float) + WARPS * sizeof(float);
+  auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, VPT, TOut>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int n_groups = (N + 7) / 8;
-  const bool single = ((K + unit - 1) / unit) * unit <= kseg;
-  // with one segment the rows are staged once per CTA and the CTA walks over column groups
   static int resident = 0;   // CTAs of this instantiation that fit on the GPU at once
   static size_t resident_smem = 0;
   if (resident == 0 || resident_smem != smem) {
     int per_sm = 0, dev = 0, sms = 0;
-    NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, WARPS * 32, smem));
+    NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
     NB_CUDA(cudaGetDevice(&dev));
     NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     resident = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
     resident_smem = smem;
   }
+  // with one segment the rows are staged once per CTA and the CTA walks over column groups
   const int grid = (single && n_groups > resident) ? resident : n_groups;
-  NB_CUDA(nb_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, (const TX*)X, gamma, beta, eps,
-                    (const bf16*)W, bias, residual, (TOut*)out, M, N, K, act, kseg));
+  NB_CUDA(nb_launch(kern, dim3(grid), dim3(NT), smem, stream, (const TX*)X, gamma, beta, eps,
+                    (const bf16*)W, bias, residual, (TOut*)out, M, N, K, act, kseg, tpr));
   return 0;
+}
+
+// Picks the number of row vectors per thread for the fused norm (0 without a norm).
+template <int MT, int WARPS, typename TX, bool LN, typename TOut>
+int launch_bf16(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+                const float* bias, const float* residual, void* out, int M, int N, int K, int act,
+                cudaStream_t stream) {
+#define NB_V(V_) \
+  return launch_bf16_v<MT, WARPS, TX, V_, TOut>(X, gamma, beta, eps, W, bias, residual, out, M, N, K, act, stream)
+  if constexpr (!LN) {
+    NB_V(0);
+  } else {
+    const int tpr = norm_threads_per_row(WARPS * 32, M);
+    const int vpt = (K / 8 + tpr - 1) / tpr;
+    if (vpt <= 1) NB_V(1);
+    if (vpt <= 2) NB_V(2);
+    if (vpt <= 4) NB_V(4);
+    NB_V(8);
+  }
+#undef NB_V
 }
 
 template <typename TX, bool LN, typename TOut>

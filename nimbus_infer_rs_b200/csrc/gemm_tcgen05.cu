@@ -7,8 +7,8 @@
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
 // with shared-memory matrix descriptors; `tcgen05.commit` hands a stage back to the producer
 // and, after the last K block of a tile, signals that tile's accumulator (there are two, used
-// in turn).  Warps 2..5 are the epilogue: each reads its 32-lane quarter of the accumulator
-// with `tcgen05.ld`, hands the accumulator back, applies bias / GELU / residual in fp32 and
+// in turn).  Warps 2..9 are the epilogue: each reads half the columns of its 32-lane quarter of
+// the accumulator with `tcgen05.ld`, hands the accumulator back, applies bias / GELU / residual in fp32 and
 // stores its rows while the MMAs of the next tile already run.  Edges need no special code on the load side: TMA
 // zero-fills rows beyond M or N and columns beyond K.
 //
@@ -32,7 +32,8 @@ typedef __nv_bfloat16 bf16;
 constexpr int BM = 128;
 constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;         // producer warp, MMA warp, four epilogue warps
+constexpr int EPI_WARPS = 8;         // two per 32-lane quarter of tensor memory, half the columns each
+constexpr int THREADS = 64 + 32 * EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
 
 __device__ int g_error_flag = 0;
@@ -181,7 +182,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);   // one arrival per epilogue warp
+      mbar_init(acc_empty(b), EPI_WARPS);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -253,6 +254,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   } else {             // ------------------------------------------------------ epilogue
     const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns it takes
+    constexpr int CHUNKS = BN / 32 / 2; // 32-column chunks per warp
     const bool vec_f32 = (N % 4 == 0);
     const bool vec_b16 = (N % 8 == 0);
     uint32_t t = 0;
@@ -266,12 +269,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (!ready) break;
       tc05_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
         uint32_t v[32];
         tc05_ld_32x32b_x32(
             tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + (uint32_t)(c * 32), v);
         tc05_wait_ld();
-        if (c == BN / 32 - 1) {   // this warp has read all of the accumulator: hand it back
+        if (c == (half + 1) * CHUNKS - 1) {   // this warp has read its share: hand it back
           tc05_fence_before();
           __syncwarp();
           if (lane == 0)
