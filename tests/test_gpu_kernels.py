@@ -308,11 +308,12 @@ def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
 @pytest.mark.parametrize("H, Hk, hd, window", [(12, 12, 64, 0), (4, 4, 16, 0), (6, 2, 32, 0),
                                                (8, 1, 128, 0), (6, 2, 64, 100), (3, 3, 48, 0),
                                                (25, 25, 64, 0), (16, 1, 64, 0)])
-@pytest.mark.parametrize("max_kv", [64, 1024])
+@pytest.mark.parametrize("max_kv", [64, 1024, 4096])
 def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
     """One query row per sequence (a decode step): sequences of very unequal lengths, pages
     shuffled, a padding row in the middle; run twice on the same scratch (the counters must be
-    left at zero); `max_kv` changes how many splits the launch uses."""
+    left at zero).  `max_kv` (the longest context the launch is sized for) selects the kernel:
+    up to 32 pages one CTA per (row, head), beyond that a sequence split over several CTAs."""
     lens = [1, 64, 65, 700, 333, 1000, 129]
     kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H + hd)
     entries = [(s + 1, [0], []) for s in range(len(lens))]
@@ -369,14 +370,15 @@ def test_tensor_core_product(ops, M, N, K):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H, Hk, hd", [(12, 12, 64), (6, 2, 32), (4, 1, 128), (4, 4, 16)])
-def test_decode_attention_appends_its_own_key_and_value(ops, dtype, H, Hk, hd):
+@pytest.mark.parametrize("max_kv", [512, 4096])
+def test_decode_attention_appends_its_own_key_and_value(ops, dtype, H, Hk, hd, max_kv):
     """With `append`, the decode kernel must give what append-then-attend gives, and leave the
     same cache behind; positions at a page start, a page end and mid-page."""
     lens = [1, 64, 65, 128, 300, 449]               # the new token is the last of each
     kv_a, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=3 * H + hd)
     kv_b = LayerKV(kv_a.k.clone(), kv_a.v.clone(), kv_a.block_table, PAGE, Hk, hd)
     lay = build_layout([(s + 1, [0], []) for s in range(len(lens))], [l - 1 for l in lens], DEV)
-    lay.max_kv_len = 512
+    lay.max_kv_len = max_kv
     torch.manual_seed(8)
     qkv = torch.randn(lay.n_rows, (H + 2 * Hk) * hd, device=DEV).to(dtype)
     kc, vc = H * hd, (H + Hk) * hd
