@@ -20,7 +20,6 @@ ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
-WIDE_DECODE_MAX_PAGES = 32     # contexts up to this many pages take the one-CTA decode attention
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
 FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to this many rows
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
@@ -210,21 +209,7 @@ class CudaBackend:
                 c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
                 c_int(kv.n_kv_heads), c_int(kv.page)):
             pages = max(1, -(-layout.max_kv_len // kv.page))
-            n_splits = max(1, min(pages, -(-DECODE_TARGET_CTAS // (n_rows * kv.n_kv_heads))))
-            align = 4 if q_src.dtype == torch.float32 else 8
-            if (n_splits == 1 or pages <= WIDE_DECODE_MAX_PAGES) and q_src.shape[1] % align == 0 \
-                    and q_col % align == 0:
-                # one CTA per (row, key/value head), a warp per page: no scratch, no merge pass
-                self._call("nb_attention_decode_wide", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
-                           c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot),
-                           _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
-                           c_int(kv.block_table.shape[1]), c_int(kv.page), c_int(n_heads),
-                           c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
-                           c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
-                           c_int(window), c_int(n_rows), c_int(1 if append else 0),
-                           c_int(append[0] if append else 0), c_int(append[1] if append else 0),
-                           self._stream())
-                return
+            n_splits = max(1, min(pages, DECODE_TARGET_CTAS // (n_rows * kv.n_kv_heads)))
             acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
                                                      kv.head_dim, n_splits)
             self._call("nb_attention_decode", _ptr(q_src), c_int(dtype_code(q_src.dtype)),

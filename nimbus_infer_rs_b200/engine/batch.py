@@ -31,6 +31,7 @@ class BatchLayout:
     max_q_len: int
     max_kv_len: int             # longest sequence after this step
     is_decode: bool             # one token per sequence
+    want_all_rows: bool = False  # want_rows is 0, 1, ..., n_rows - 1
 
 
 def build_layout(entries, pos0: list[int], device, pad_rows_to: int = 1) -> BatchLayout:
@@ -77,4 +78,5 @@ def build_layout(entries, pos0: list[int], device, pad_rows_to: int = 1) -> Batc
         seq_lens=lens, seq_pos0_host=list(pos0), seq_slots_host=[int(e[0]) for e in entries],
         max_q_len=max(lens) if lens else 0,
         max_kv_len=max((p + t for p, t in zip(pos0, lens)), default=0),
-        is_decode=all(t == 1 for t in lens))
+        is_decode=all(t == 1 for t in lens),
+        want_all_rows=(n_want == n_rows and bool((want == np.arange(n_rows, dtype=np.int32)).all())))

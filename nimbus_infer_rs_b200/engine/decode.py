@@ -64,7 +64,7 @@ class DecodeSession:
             seq_slot=self.row_slot, seq_pos0=self.row_pos, seq_lens=[1] * n,
             seq_pos0_host=[eng.cache.lens[s] for s in self.slots],
             seq_slots_host=list(self.slots), max_q_len=1, max_kv_len=eng.spec.max_seq_len,
-            is_decode=True)
+            is_decode=True, want_all_rows=True)
 
     def _device_step(self) -> None:
         eng = self.engine

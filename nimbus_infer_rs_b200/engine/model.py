@@ -149,6 +149,10 @@ class Model:
 
     def logits(self, ctx, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
         """Final norm and head on the selected rows → fp32 [n_rows, vocab]."""
+        if ctx.layout.want_all_rows and n_rows == x.shape[0]:
+            # every row is wanted, in order (a decode step): no gather, and the norm may be
+            # folded into the head's product
+            return self.head.forward(ctx, self.final_norm.defer(ctx, x))
         h = self.final_norm.forward(ctx, x, rows, n_rows)
         return self.head.forward(ctx, h)
 

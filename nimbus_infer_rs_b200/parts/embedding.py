@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import MATRIX, TABLE, ParamSpec, Part
+from .base import MATRIX, TABLE, DeferredNorm, ParamSpec, Part
 
 
 class TokenEmbedding(Part):
@@ -49,7 +49,11 @@ class LMHead(Part):
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, h) -> torch.Tensor:
+        """``h``: activation rows, or a :class:`DeferredNorm` of fp32 rows."""
+        norm = None
+        if isinstance(h, DeferredNorm):
+            h, norm = h.x, h.args
         logits = torch.empty((h.shape[0], self.vocab_size), device=h.device, dtype=torch.float32)
-        ctx.ops.linear(h, self.weight, None, logits, 0, None)
+        ctx.ops.linear(h, self.weight, None, logits, 0, None, norm)
         return logits

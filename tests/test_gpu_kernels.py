@@ -312,8 +312,8 @@ def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
 def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
     """One query row per sequence (a decode step): sequences of very unequal lengths, pages
     shuffled, a padding row in the middle; run twice on the same scratch (the counters must be
-    left at zero).  `max_kv` (the longest context the launch is sized for) selects the kernel:
-    up to 32 pages one CTA per (row, head), beyond that a sequence split over several CTAs."""
+    left at zero).  `max_kv` (the longest context the launch is sized for) changes the number
+    of splits a sequence's pages are spread over."""
     lens = [1, 64, 65, 700, 333, 1000, 129]
     kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H + hd)
     entries = [(s + 1, [0], []) for s in range(len(lens))]
