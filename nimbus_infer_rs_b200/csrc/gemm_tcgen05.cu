@@ -1,7 +1,7 @@
 // Matrix product on the 5th-generation tensor cores (sm_100a): out[M,N] = act(X[M,K] *
 // W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
 //
-// A CTA computes 128 x BN tiles (BN = 64 or 128), one after another.  Warp 0 is the producer: one thread issues TMA loads of
+// A CTA computes 128 x BN tiles (BN = 64, 128 or 256), one after another.  Warp 0 is the producer: one thread issues TMA loads of
 // 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
 // stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
@@ -456,12 +456,16 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   // tile shape: one row tile streaming a weight matrix -> narrow tiles, deep pipeline;
   // otherwise fill the 148 SMs twice over (two CTAs per SM) before going to wider tiles
   const long long tiles_m = (M + BM - 1) / BM;
-  // narrow tiles until there are enough of them for every SM to have two
-  const bool wide = tiles_m * ((N + 127) / 128) >= 2 * 148;
+  // Tile width.  Every tile re-reads its 128 rows of X and its BN rows of W from L2, so wide
+  // tiles (more flops per byte brought in) win as soon as there is more than one row tile,
+  // even when they leave some SMs without a tile; a single row tile (at most 128 rows) is a
+  // weight stream, for which many narrow tiles with a deep ring are best.
+  const int bn = tiles_m == 1 ? 64 : (N >= 1024 ? 256 : (N >= 256 ? 128 : 64));
   int rc;
-#define NB_SHAPES(T_)                                                              \
-  rc = wide ? launch<128, 6, T_>(X, W, bias, residual, out, M, N, K, act, stream) \
-            : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
+#define NB_SHAPES(T_)                                                                   \
+  rc = bn == 256 ? launch<256, 4, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
+     : bn == 128 ? launch<128, 6, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
+                 : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
     NB_SHAPES(float);
   } else if (out_dtype == NB_BF16) {
