@@ -252,6 +252,315 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same job on the tensor cores, for a bf16 cache.  The CUDA-core kernel above spends its
+// time on instructions (widening every key and value, shuffles, a running softmax per four
+// keys); here a warp's 16 keys of a page are one mma.sync operand: scores = K (16 keys x
+// head_dim) times Q^T (head_dim x 8 query heads of the group, unused columns zero), then the
+// value product out^T (head_dim x 8 heads) += V^T (head_dim x 16 keys) times P (16 keys x 8
+// heads).  Softmax statistics stay fp32 per head (in units of log2 e); probabilities are
+// rounded to bf16 only as the operand of the value product, as in the prefill kernel.  Pages
+// are staged with padded rows so that ldmatrix runs without bank conflicts.  Any head size
+// that is a multiple of 16 up to 128; up to 8 query heads per key/value head at no extra cost.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int HD, typename TOut>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, int q_col,
+                            const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                            NbPagedKV kv, int group, TOut* __restrict__ out, int out_stride,
+                            float scale, int window, int n_splits, float* __restrict__ part_acc,
+                            float* __restrict__ part_ml, int* __restrict__ counters, int append,
+                            int k_col, int v_col) {
+  typedef __nv_bfloat16 bf16;
+  constexpr int ROW = HD + 8;          // padded row of a staged page (elements)
+  constexpr int KS = HD / 16;          // k-steps of the score product = row tiles of the value product
+  constexpr int GH = 8;                // query heads an MMA column block holds
+  constexpr int TILE = PAGE_TOKENS * HD;
+  constexpr int STILE = PAGE_TOKENS * ROW;
+  static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size not supported");
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                   // [2 stages][K | V][64][ROW]
+  float* w_acc = reinterpret_cast<float*>(smem_raw + (size_t)4 * STILE * sizeof(bf16));  // [WARPS][GH][HD]
+  float* w_ml = w_acc + WARPS * GH * HD;                             // [WARPS][GH][2]
+  __shared__ int s_last;
+
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_heads = kv.n_kv_heads * group;
+  const int slot = row_slot[r];
+  if (slot < 0) {   // padding row: zeros, written by split 0
+    if (split == 0)
+      for (int i = tid; i < group * HD; i += THREADS)
+        out[(size_t)r * out_stride + (size_t)kvh * group * HD + i] = nb_from_f32<TOut>(0.0f);
+    return;
+  }
+  const int pos = row_pos[r];
+  const int kv_len = pos + 1;
+  const int j_begin = (window > 0 && kv_len > window) ? kv_len - window : 0;
+  const int first_page = j_begin / PAGE_TOKENS;
+  const int n_pages = (kv_len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_page;
+  const int per_split = (n_pages + n_splits - 1) / n_splits;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(first_page + n_pages, p_begin + per_split);
+  const int* table = kv.block_table + (size_t)slot * kv.max_pages;
+  const bf16* qrow = q + (size_t)r * q_stride;
+
+  auto issue = [&](int page_idx, int stage) {
+    const int page_id = table[page_idx];
+    const bf16* ksrc = (const bf16*)kv.k + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE;
+    const bf16* vsrc = (const bf16*)kv.v + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE;
+    bf16* kdst = tiles + (size_t)stage * 2 * STILE;
+    bf16* vdst = kdst + STILE;
+    constexpr int CPR = HD / 8;   // 16-byte pieces per row
+    for (int i = tid; i < PAGE_TOKENS * CPR; i += THREADS) {
+      const int row = i / CPR, c = i - row * CPR;
+      cp_async16(kdst + row * ROW + c * 8, ksrc + row * HD + c * 8);
+      cp_async16(vdst + row * ROW + c * 8, vsrc + row * HD + c * 8);
+    }
+    cp_async_commit();
+  };
+  if (p_begin < p_end) issue(p_begin, 0);
+
+  // Q^T as the B operand of the score product: column g of the block is query head g of the
+  // group (zero beyond the group); this thread holds rows 2t, 2t+1 and 2t+8, 2t+9 of each k-step
+  uint32_t qb[KS][2];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qb[ks][0] = qb[ks][1] = 0u;
+    if (g < group) {
+      const bf16* p = qrow + q_col + (size_t)(kvh * group + g) * HD + ks * 16 + 2 * t;
+      qb[ks][0] = *reinterpret_cast<const uint32_t*>(p);
+      qb[ks][1] = *reinterpret_cast<const uint32_t*>(p + 8);
+    }
+  }
+
+  // this thread's share: heads 2t and 2t+1; keys g and g+8 of the warp's 16; rows g, g+8 of
+  // every 16-row tile of the output
+  float o[KS][4];
+#pragma unroll
+  for (int i = 0; i < KS; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const float sl2 = scale * 1.4426950408889634f;
+
+  for (int p = p_begin; p < p_end; ++p) {
+    const int stage = (p - p_begin) & 1;
+    if (p + 1 < p_end) {
+      issue(p + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    bf16* kt = tiles + (size_t)stage * 2 * STILE;
+    bf16* vt = kt + STILE;
+    if (append && p == pos / PAGE_TOKENS) {
+      // this step's own key and value belong at token `pos` of this page: into the staged
+      // tile and into the cache
+      const int in_page = pos % PAGE_TOKENS;
+      const int page_id = table[p];
+      constexpr int CPR = HD / 8;
+      for (int i = tid; i < 2 * CPR; i += THREADS) {
+        const bool is_v = i >= CPR;
+        const int c = (is_v ? i - CPR : i) * 8;
+        const uint4 val = *reinterpret_cast<const uint4*>(
+            qrow + (is_v ? v_col : k_col) + (size_t)kvh * HD + c);
+        *reinterpret_cast<uint4*>((is_v ? vt : kt) + in_page * ROW + c) = val;
+        bf16* cache = (bf16*)(is_v ? kv.v : kv.k);
+        *reinterpret_cast<uint4*>(cache + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE +
+                                  in_page * HD + c) = val;
+      }
+      __syncthreads();
+    }
+    const int key0 = p * PAGE_TOKENS + warp * 16;     // first key of this warp's 16
+    if (key0 < kv_len && key0 + 16 > j_begin) {       // warp-uniform: something to attend to
+      float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t ka[4];
+        ldsm_x4(ka, kt + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
+        mma_16816(sc, ka, qb[ks][0], qb[ks][1]);
+      }
+      const int ja = key0 + g, jb = ja + 8;
+      const bool va = ja >= j_begin && ja < kv_len, vb = jb >= j_begin && jb < kv_len;
+      const float s0 = va ? sc[0] * sl2 : -INFINITY, s1 = va ? sc[1] * sl2 : -INFINITY;
+      const float s2 = vb ? sc[2] * sl2 : -INFINITY, s3 = vb ? sc[3] * sl2 : -INFINITY;
+      float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);   // finite: a key is valid
+      const float r0 = (m_run[0] == -INFINITY) ? 0.0f : exp2f(m_run[0] - mn0);
+      const float r1 = (m_run[1] == -INFINITY) ? 0.0f : exp2f(m_run[1] - mn1);
+      m_run[0] = mn0;
+      m_run[1] = mn1;
+      const float p0 = exp2f(s0 - mn0), p1 = exp2f(s1 - mn1);
+      const float p2 = exp2f(s2 - mn0), p3 = exp2f(s3 - mn1);
+      l_run[0] = l_run[0] * r0 + p0 + p2;
+      l_run[1] = l_run[1] * r1 + p1 + p3;
+#pragma unroll
+      for (int i = 0; i < KS; ++i) {
+        o[i][0] *= r0; o[i][1] *= r1; o[i][2] *= r0; o[i][3] *= r1;
+      }
+      // P as the B operand of the value product: this thread needs keys 2t, 2t+1 (and +8) of
+      // head g; they sit in lanes (g' = 2t, t' = g/2) and (g' = 2t+1, t' = g/2)
+      const uint32_t pe = pack2_bf16(p0, p2);   // head 2t:   keys g, g+8
+      const uint32_t po = pack2_bf16(p1, p3);   // head 2t+1: keys g, g+8
+      const int src1 = (2 * t) * 4 + (g >> 1), src2 = src1 + 4;
+      const uint32_t e1 = __shfl_sync(0xffffffffu, pe, src1), o1 = __shfl_sync(0xffffffffu, po, src1);
+      const uint32_t e2 = __shfl_sync(0xffffffffu, pe, src2), o2 = __shfl_sync(0xffffffffu, po, src2);
+      const uint32_t x1 = (g & 1) ? o1 : e1, x2 = (g & 1) ? o2 : e2;
+      const uint32_t pb0 = __byte_perm(x1, x2, 0x5410);   // keys 2t, 2t+1
+      const uint32_t pb1 = __byte_perm(x1, x2, 0x7632);   // keys 2t+8, 2t+9
+#pragma unroll
+      for (int i = 0; i < KS; ++i) {
+        uint32_t va4[4];
+        ldsm_x4_trans(va4, vt + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * ROW + i * 16 +
+                               ((lane >> 3) & 1) * 8);
+        mma_16816(o[i], va4, pb0, pb1);
+      }
+    }
+    __syncthreads();   // the stage is free for the copy after next
+  }
+
+  // row sums over the lanes that share a head (different keys), then the warps
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
+  }
+#pragma unroll
+  for (int i = 0; i < KS; ++i) {
+    float* base = w_acc + (size_t)warp * GH * HD;
+    base[(2 * t) * HD + i * 16 + g] = o[i][0];
+    base[(2 * t + 1) * HD + i * 16 + g] = o[i][1];
+    base[(2 * t) * HD + i * 16 + g + 8] = o[i][2];
+    base[(2 * t + 1) * HD + i * 16 + g + 8] = o[i][3];
+  }
+  if (g == 0) {
+    w_ml[(warp * GH + 2 * t) * 2] = m_run[0];
+    w_ml[(warp * GH + 2 * t) * 2 + 1] = l_run[0];
+    w_ml[(warp * GH + 2 * t + 1) * 2] = m_run[1];
+    w_ml[(warp * GH + 2 * t + 1) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  // merge the warps -> partial result of this split (maxima in units of log2 e)
+  for (int i = tid; i < group * HD; i += THREADS) {
+    const int gh = i / HD, c = i - gh * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, w_ml[(w * GH + gh) * 2]);
+    float a = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = w_ml[(w * GH + gh) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+      a += f * w_acc[(w * GH + gh) * HD + c];
+      l += f * w_ml[(w * GH + gh) * 2 + 1];
+    }
+    const int head = kvh * group + gh;
+    if (n_splits == 1) {
+      out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
+      continue;
+    }
+    const size_t pi = ((size_t)r * n_heads + head) * n_splits + split;
+    part_acc[pi * HD + c] = a;
+    if (c == 0) {
+      part_ml[pi * 2] = M;
+      part_ml[pi * 2 + 1] = l;
+    }
+  }
+  if (n_splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[r * kv.n_kv_heads + kvh], 1);
+    s_last = (old == n_splits - 1);
+    if (s_last) counters[r * kv.n_kv_heads + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = tid; i < group * HD; i += THREADS) {
+    const int gh = i / HD, c = i - gh * HD;
+    const int head = kvh * group + gh;
+    const size_t base = ((size_t)r * n_heads + head) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
+    float a = 0.0f, l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = __ldcg(&part_ml[(base + s) * 2]);
+      const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+      a += f * __ldcg(&part_acc[(base + s) * HD + c]);
+      l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
+    }
+    out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
+  }
+}
+
+template <int HD, typename TOut>
+int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
+               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+               int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
+               int k_col, int v_col, cudaStream_t stream) {
+  const size_t smem = (size_t)4 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16) +
+                      (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
+  auto kern = attention_decode_mma_kernel<HD, TOut>;
+  if (smem > 48 * 1024)
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(n_splits, kv.n_kv_heads, n_rows);
+  NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride, q_col,
+                    row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits,
+                    part_acc, part_ml, counters, append, k_col, v_col));
+  return 0;
+}
+
+template <typename TOut>
+int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* row_slot,
+                    const int* row_pos, const NbPagedKV& kv, int group, void* out, int out_stride,
+                    float scale, int window, int n_rows, int n_splits, float* pa, float* pm,
+                    int* cn, int ap, int kc, int vc, cudaStream_t st) {
+#define NB_HD(HD_) \
+  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  switch (hd) {
+    NB_HD(16); NB_HD(32); NB_HD(48); NB_HD(64); NB_HD(80); NB_HD(96); NB_HD(112); NB_HD(128);
+  }
+#undef NB_HD
+  return NB_ERR_UNSUPPORTED;
+}
+
 template <typename T, int HD, int G, typename TOut>
 int launch(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
            const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
@@ -307,7 +616,8 @@ NB_EXPORT int nb_attention_decode_supported(int dtype, int head_dim, int n_heads
                                             int page) {
   if (page != PAGE_TOKENS || n_kv_heads < 1 || n_heads % n_kv_heads != 0) return 0;
   if (n_heads / n_kv_heads > 8) return 0;
-  if (dtype != NB_F32 && dtype != NB_BF16) return 0;
+  if (dtype == NB_BF16) return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128;
+  if (dtype != NB_F32) return 0;
   return head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
 }
 
@@ -349,10 +659,16 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
   typedef __nv_bfloat16 bf16;
   int rc;
 #define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
-  if (dtype == NB_F32)
+  if (dtype == NB_F32) {
     rc = out_dtype == NB_F32 ? by_head_dim<float, float>(NB_ARGS) : by_head_dim<float, bf16>(NB_ARGS);
-  else
-    rc = out_dtype == NB_F32 ? by_head_dim<bf16, float>(NB_ARGS) : by_head_dim<bf16, bf16>(NB_ARGS);
+  } else {
+    // bf16 cache: tensor cores (needs 16-byte aligned rows and 4-byte aligned query columns)
+    NB_REQUIRE(q_stride % 8 == 0 && q_col % 2 == 0 && (uintptr_t)q % 16 == 0, NB_ERR_UNSUPPORTED,
+               "attention_decode: query rows must be 16-byte aligned");
+    rc = out_dtype == NB_F32
+             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream)
+             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream);
+  }
 #undef NB_ARGS
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_decode");
