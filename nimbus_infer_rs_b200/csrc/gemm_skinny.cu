@@ -309,7 +309,7 @@ gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamm
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * MT * 16 + row) * 8 + col];
       v += e_bias[i];
-      v = nb_apply_act(v, act);
+      v = nb_apply_act_fast(v, act);
       v += e_res[i];
       out[(size_t)row * N + nn] = nb_from_f32<TOut>(v);
     }

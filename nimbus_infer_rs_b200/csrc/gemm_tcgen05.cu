@@ -7,8 +7,8 @@
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
 // with shared-memory matrix descriptors; `tcgen05.commit` hands a stage back to the producer
 // and, after the last K block of a tile, signals that tile's accumulator (there are two, used
-// in turn).  Warps 2..9 are the epilogue: each reads half the columns of its 32-lane quarter of
-// the accumulator with `tcgen05.ld`, hands the accumulator back, applies bias / GELU / residual in fp32 and
+// in turn).  The other 8 or 16 warps are the epilogue: each reads its share of the columns of
+// its 32-lane quarter of the accumulator with `tcgen05.ld`, hands the accumulator back, applies bias / GELU / residual in fp32 and
 // stores its rows while the MMAs of the next tile already run.  Edges need no special code on the load side: TMA
 // zero-fills rows beyond M or N and columns beyond K.
 //
@@ -32,8 +32,10 @@ typedef __nv_bfloat16 bf16;
 constexpr int BM = 128;
 constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
-constexpr int EPI_WARPS = 8;         // two per 32-lane quarter of tensor memory, half the columns each
-constexpr int THREADS = 64 + 32 * EPI_WARPS;   // producer warp, MMA warp, epilogue warps
+// Epilogue warps per CTA: a warp may read only the 32 tensor-memory lanes of its quarter
+// (warp index mod 4), so the warps of a quarter share the tile's columns among them.
+__host__ __device__ constexpr int epi_warps(int bn) { return bn >= 128 ? 16 : 8; }
+__host__ __device__ constexpr int cta_threads(int bn) { return 64 + 32 * epi_warps(bn); }
 constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
 
 __device__ int g_error_flag = 0;
@@ -154,7 +156,7 @@ struct SmemLayout {
 };
 
 template <int BN, int STAGES_, typename TOut>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(cta_threads(BN))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
                     int K, int act, int tiles_n, int num_tiles) {
@@ -182,7 +184,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), EPI_WARPS);   // one arrival per epilogue warp
+      mbar_init(acc_empty(b), epi_warps(BN));   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -254,8 +256,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   } else {             // ------------------------------------------------------ epilogue
     const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
-    const int half = (warp - 2) >> 2;   // which half of the tile's columns it takes
-    constexpr int CHUNKS = BN / 32 / 2; // 32-column chunks per warp
+    const int half = (warp - 2) >> 2;   // which share of the tile's columns it takes
+    constexpr int CHUNKS = BN / 32 / (epi_warps(BN) / 4);   // 32-column chunks per warp
     const bool vec_f32 = (N % 4 == 0);
     const bool vec_b16 = (N % 8 == 0);
     uint32_t t = 0;
@@ -289,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             float x = __uint_as_float(v[j]);
             if (n < N) {
               if (bias) x += __ldg(bias + n);
-              x = nb_apply_act(x, act);
+              x = nb_apply_act_fast(x, act);
             }
             f[j] = x;
           }
@@ -419,8 +421,8 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
-  kern<<<grid, THREADS, smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
-                                        (int)num_tiles);
+  kern<<<grid, cta_threads(BN), smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act,
+                                                tiles_n, (int)num_tiles);
   return 0;
 }
 
