@@ -16,6 +16,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+// 2^x by the hardware unit (one instruction; relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float nb_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T>
 struct Lane16;   // the 16 bytes a lane reads, as floats
 template <>

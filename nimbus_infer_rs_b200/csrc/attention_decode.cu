@@ -422,12 +422,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
       }
       const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);   // finite: a key is valid
-      const float r0 = (m_run[0] == -INFINITY) ? 0.0f : exp2f(m_run[0] - mn0);
-      const float r1 = (m_run[1] == -INFINITY) ? 0.0f : exp2f(m_run[1] - mn1);
+      const float r0 = (m_run[0] == -INFINITY) ? 0.0f : nb_exp2(m_run[0] - mn0);
+      const float r1 = (m_run[1] == -INFINITY) ? 0.0f : nb_exp2(m_run[1] - mn1);
       m_run[0] = mn0;
       m_run[1] = mn1;
-      const float p0 = exp2f(s0 - mn0), p1 = exp2f(s1 - mn1);
-      const float p2 = exp2f(s2 - mn0), p3 = exp2f(s3 - mn1);
+      const float p0 = nb_exp2(s0 - mn0), p1 = nb_exp2(s1 - mn1);
+      const float p2 = nb_exp2(s2 - mn0), p3 = nb_exp2(s3 - mn1);
       l_run[0] = l_run[0] * r0 + p0 + p2;
       l_run[1] = l_run[1] * r1 + p1 + p3;
 #pragma unroll
@@ -486,7 +486,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
       const float mw = w_ml[(w * GH + gh) * 2];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+      const float f = (mw == -INFINITY) ? 0.0f : nb_exp2(mw - M);
       a += f * w_acc[(w * GH + gh) * HD + c];
       l += f * w_ml[(w * GH + gh) * 2 + 1];
     }
@@ -522,7 +522,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     float a = 0.0f, l = 0.0f;
     for (int s = 0; s < n_splits; ++s) {
       const float ms = __ldcg(&part_ml[(base + s) * 2]);
-      const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+      const float f = (ms == -INFINITY) ? 0.0f : nb_exp2(ms - M);
       a += f * __ldcg(&part_acc[(base + s) * HD + c]);
       l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
     }

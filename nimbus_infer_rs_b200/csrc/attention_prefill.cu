@@ -15,7 +15,7 @@
 //
 // Reference: src/model.rs:401-422 (scores = dot(q,k)*scale for keys 0..P+i, softmax with the
 // maximum subtracted, weighted values).
-#include "common.cuh"
+#include "attention_common.cuh"
 
 namespace {
 
@@ -24,15 +24,6 @@ constexpr int THREADS = 128;
 constexpr int BLOCK_Q = 64;
 constexpr int PAGE_TOKENS = 64;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -160,19 +151,32 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
         mma_bf16(sc[2 * n2 + 1], qf[ks], kb[2], kb[3]);
       }
     }
-    // causal limit, window, scale; running maximum
+    // causal limit, window, scale; running maximum.  A page that lies wholly before the first
+    // row of this warp (and needs no window) is visible to all of its rows: no comparisons.
     const int j0 = p * PAGE_TOKENS;
     float mx[2] = {-INFINITY, -INFINITY};
+    if (window <= 0 && j0 + PAGE_TOKENS - 1 <= pos0 + q0 + warp * 16) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < 8; ++n) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int key = j0 + n * 8 + t * 2 + (j & 1);
-        const int qp = (j < 2) ? qpos_a : qpos_b;
-        const bool ok = key <= qp && (window <= 0 || key > qp - window);
-        const float v = ok ? sc[n][j] * sl2 : -INFINITY;
-        sc[n][j] = v;
-        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        for (int j = 0; j < 4; ++j) {
+          const float v = sc[n][j] * sl2;
+          sc[n][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = j0 + n * 8 + t * 2 + (j & 1);
+          const int qp = (j < 2) ? qpos_a : qpos_b;
+          const bool ok = key <= qp && (window <= 0 || key > qp - window);
+          const float v = ok ? sc[n][j] * sl2 : -INFINITY;
+          sc[n][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
       }
     }
     float m_use[2], resc[2];
@@ -182,7 +186,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m_run[r], mx[r]);
       m_use[r] = (m_new == -INFINITY) ? 0.0f : m_new;
-      resc[r] = (m_run[r] == -INFINITY) ? 0.0f : exp2f(m_run[r] - m_use[r]);
+      resc[r] = (m_run[r] == -INFINITY) ? 0.0f : nb_exp2(m_run[r] - m_use[r]);
       m_run[r] = m_new;
       l_run[r] *= resc[r];
     }
@@ -195,8 +199,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     uint32_t pf[4][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
-      const float p0 = exp2f(sc[n][0] - m_use[0]), p1 = exp2f(sc[n][1] - m_use[0]);
-      const float p2 = exp2f(sc[n][2] - m_use[1]), p3 = exp2f(sc[n][3] - m_use[1]);
+      const float p0 = nb_exp2(sc[n][0] - m_use[0]), p1 = nb_exp2(sc[n][1] - m_use[0]);
+      const float p2 = nb_exp2(sc[n][2] - m_use[1]), p3 = nb_exp2(sc[n][3] - m_use[1]);
       l_run[0] += p0 + p1;
       l_run[1] += p2 + p3;
       pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);

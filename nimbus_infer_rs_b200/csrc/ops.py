@@ -22,6 +22,7 @@ ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GEL
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
 FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to this many rows
+FUSED_NORM_MAX_COLS = 16384    # ... and output columns (a long weight stream wants the leaner kernel)
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 
 
@@ -140,7 +141,8 @@ class CudaBackend:
         skinny = (M <= FUSED_NORM_MAX_ROWS or (M <= SKINNY_MAX_ROWS and not tensor_core)) \
             and (w.dtype == torch.float32 or K % 8 == 0)
         if skinny:
-            if norm is not None and (M > FUSED_NORM_MAX_ROWS or w.dtype != torch.bfloat16):
+            if norm is not None and (M > FUSED_NORM_MAX_ROWS or N > FUSED_NORM_MAX_COLS
+                                     or w.dtype != torch.bfloat16):
                 h = torch.empty((M, K), device=x.device, dtype=norm[3])
                 self.layernorm(x, norm[0], norm[1], norm[2], h)
                 x, norm = h, None
