@@ -25,10 +25,15 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE configs[2]: GPT-2 small 124M
+# GPT-2 small, 124M parameters
 MODEL = {"model_type": "gpt2", "vocab_size": 50257, "n_positions": 1024, "n_embd": 768,
          "n_layer": 12, "n_head": 12, "n_inner": 3072, "activation_function": "gelu_new",
          "layer_norm_epsilon": 1e-5, "tie_word_embeddings": True}
+# the larger members of the family, for --model (side measurements, not the headline)
+OTHER_MODELS = {
+    "gpt2-medium": dict(MODEL, n_embd=1024, n_layer=24, n_head=16, n_inner=4096),
+    "gpt2-xl": dict(MODEL, n_embd=1600, n_layer=48, n_head=25, n_inner=6400),
+}
 CONTEXT = 1024
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -201,6 +206,8 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one phase only (for profiling); prints a reduced line")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the decode step")
+    ap.add_argument("--model", default="gpt2-124M", choices=["gpt2-124M", *OTHER_MODELS],
+                    help="layer sizes; other than the default only with --only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -221,20 +228,31 @@ def main() -> int:
 
     peaks = load_peaks()
     dtype = "bfloat16" if args.dtype == "bf16" else "float32"
-    cfg = GPT2Config.from_json(MODEL)
-    cache_tokens = 64 * CONTEXT + 64
+    if args.model != "gpt2-124M" and args.only == "all":
+        print("--model other than gpt2-124M needs --only decode or --only prefill")
+        return 2
+    cfg = GPT2Config.from_json(OTHER_MODELS.get(args.model, MODEL))
+    cache_tokens = max(64, args.batch if args.only == "decode" else 64) * CONTEXT + 64
     engine = Engine.random(cfg, seed=0, dtype=dtype, cache_tokens=cache_tokens, std=0.02)
     elt = 2 if dtype == "bfloat16" else 4
 
     if args.only == "prefill":
-        pre_ms = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT, reps=2)
-        print(json.dumps({"only": "prefill", "ms": round(pre_ms, 4),
-                          "tokens_per_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1)}))
+        pre_ms = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT, reps=8)
+        flops = model_flops_prefill(cfg, PREFILL_TOKENS // CONTEXT, CONTEXT)
+        print(json.dumps({"only": "prefill", "model": args.model, "dtype": args.dtype,
+                          "ms": round(pre_ms, 4),
+                          "tokens_per_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1),
+                          "tflops": round(flops / (pre_ms * 1e-3) / 1e12, 1)}))
         return 0
     if args.only == "decode":
         ms, launches, mean_ctx = time_decode(engine, args.batch, CONTEXT, args.steps, args.warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
+        elt_ = 2 if dtype == "bfloat16" else 4
+        nbytes = engine.model.weight_bytes() + args.batch * mean_ctx * (
+            2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * elt_)
+        print(json.dumps({"only": "decode", "model": args.model, "dtype": args.dtype,
+                          "batch": args.batch, "ms_per_step": round(ms, 4),
                           "tokens_per_s": round(args.batch * 1000.0 / ms, 1),
+                          "gb_per_s": round(nbytes / (ms * 1e-3) / 1e9, 1),
                           "gpu_launches": launches}))
         return 0
 

@@ -5,7 +5,7 @@ import plain_gpt2 as P
 from tiny_configs import make_model
 
 WORKLOADS = {
-    # BASELINE workloads of the two tiny configurations: prompt lengths and greedy steps
+    # workloads of the two tiny configurations: prompt lengths and greedy steps
     "A": ([5, 9, 13], 8),
     "B": ([1, 17], 12),
 }
