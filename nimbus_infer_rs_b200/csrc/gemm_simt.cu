@@ -78,6 +78,18 @@ gemm_simt_kernel(const TIn* __restrict__ X, const TW* __restrict__ W,
     }
   }
 
+  // `residual` may be `out` itself: fetch all of it before the first store, or every load
+  // would have to wait for the store before it
+  float res[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      res[i][j] = (residual && m < M && n < N) ? residual[(size_t)m * N + n] : 0.0f;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + ty * 4 + i;
@@ -89,8 +101,7 @@ gemm_simt_kernel(const TIn* __restrict__ X, const TW* __restrict__ W,
       float v = acc[i][j];
       if (bias) v += bias[n];
       v = nb_apply_act(v, act);
-      if (residual) v += residual[(size_t)m * N + n];
-      out[(size_t)m * N + n] = nb_from_f32<TOut>(v);
+      out[(size_t)m * N + n] = nb_from_f32<TOut>(v + res[i][j]);
     }
   }
 }

@@ -283,56 +283,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
         }
         const int nb = n0 + c * 32;
-        if (m < M && nb < N) {
-          float f[32];
+        // bias of the chunk's 32 columns: one load per lane, handed round by shuffles
+        float bias_l = 0.0f;
+        if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
+        float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = nb + j;
-            float x = __uint_as_float(v[j]);
-            if (n < N) {
-              if (bias) x += __ldg(bias + n);
-              x = nb_apply_act_fast(x, act);
-            }
-            f[j] = x;
-          }
+        for (int j = 0; j < 32; ++j) {
+          const float x = __uint_as_float(v[j]) + __shfl_sync(0xffffffffu, bias_l, j);
+          f[j] = nb_apply_act_fast(x, act);
+        }
+        if (m < M && nb < N) {
           const size_t row = (size_t)m * N;
           const bool full = nb + 32 <= N;
           if constexpr (sizeof(TOut) == 4) {
             float* o = reinterpret_cast<float*>(out) + row + nb;
             const float* r = residual ? residual + row + nb : nullptr;
             if (full && vec_f32) {
+              // `residual` may be `out` itself: fetch all of it before the first store, or
+              // every load would have to wait for the store before it
+              float4 rr[8];
+              if (r) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 y = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                if (r) {
-                  const float4 rr = *reinterpret_cast<const float4*>(r + j);
-                  y.x += rr.x; y.y += rr.y; y.z += rr.z; y.w += rr.w;
-                }
-                *reinterpret_cast<float4*>(o + j) = y;
+                for (int j = 0; j < 8; ++j) rr[j] = *reinterpret_cast<const float4*>(r + 4 * j);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 y = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                if (r) { y.x += rr[j].x; y.y += rr[j].y; y.z += rr[j].z; y.w += rr[j].w; }
+                *reinterpret_cast<float4*>(o + 4 * j) = y;
               }
             } else {
+              float rs[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) rs[j] = (r && nb + j < N) ? r[j] : 0.0f;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (nb + j < N) o[j] = f[j] + (r ? r[j] : 0.0f);
+                if (nb + j < N) o[j] = f[j] + rs[j];
             }
           } else {
             bf16* o = reinterpret_cast<bf16*>(out) + row + nb;
             const float* r = residual ? residual + row + nb : nullptr;
+            if (r) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < N) f[j] += r[j];
+            }
             if (full && vec_b16) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 pk;
                 __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  h[e] = __floats2bfloat162_rn(f[j + 2 * e] + (r ? r[j + 2 * e] : 0.0f),
-                                               f[j + 2 * e + 1] + (r ? r[j + 2 * e + 1] : 0.0f));
+                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[j + 2 * e], f[j + 2 * e + 1]);
                 *reinterpret_cast<uint4*>(o + j) = pk;
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (nb + j < N) o[j] = __float2bfloat16_rn(f[j] + (r ? r[j] : 0.0f));
+                if (nb + j < N) o[j] = __float2bfloat16_rn(f[j]);
             }
           }
         }
