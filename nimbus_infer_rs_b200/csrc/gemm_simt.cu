@@ -54,10 +54,11 @@ gemm_simt_kernel(const TIn* __restrict__ X, const TW* __restrict__ W,
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+  // the next K block is fetched into registers while the current one is multiplied
+  float xv[4], wv[4];
+  load4<TIn>(X, m0 + lrow, M, lk, K, x_vec, xv);
+  load4<TW>(W, n0 + lrow, N, lk, K, w_vec, wv);
   for (int k0 = 0; k0 < K; k0 += BK) {
-    float xv[4], wv[4];
-    load4<TIn>(X, m0 + lrow, M, k0 + lk, K, x_vec, xv);
-    load4<TW>(W, n0 + lrow, N, k0 + lk, K, w_vec, wv);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -65,6 +66,10 @@ gemm_simt_kernel(const TIn* __restrict__ X, const TW* __restrict__ W,
       Ws[lk + i][lrow] = wv[i];
     }
     __syncthreads();
+    if (k0 + BK < K) {
+      load4<TIn>(X, m0 + lrow, M, k0 + BK + lk, K, x_vec, xv);
+      load4<TW>(W, n0 + lrow, N, k0 + BK + lk, K, w_vec, wv);
+    }
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       const float4 a = *reinterpret_cast<const float4*>(&Xs[k][ty * 4]);
