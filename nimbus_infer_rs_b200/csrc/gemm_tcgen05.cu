@@ -34,8 +34,12 @@ constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom r
 constexpr int UMMA_K = 16;
 // Epilogue warps per CTA: a warp may read only the 32 tensor-memory lanes of its quarter
 // (warp index mod 4), so the warps of a quarter share the tile's columns among them.
-__host__ __device__ constexpr int epi_warps(int bn) { return bn >= 128 ? 16 : 8; }
-__host__ __device__ constexpr int cta_threads(int bn) { return 64 + 32 * epi_warps(bn); }
+// With the direct-store epilogue (EPI 0) there are 16 warps for wide tiles, 8 otherwise; with
+// the shared-memory / TMA-store epilogue (EPI 1) every warp owns 64 columns of its quarter.
+__host__ __device__ constexpr int epi_warps(int bn, int epi) {
+  return epi ? bn / 16 : (bn >= 128 ? 16 : 8);
+}
+__host__ __device__ constexpr int cta_threads(int bn, int epi) { return 64 + 32 * epi_warps(bn, epi); }
 constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
 
 __device__ int g_error_flag = 0;
@@ -118,6 +122,21 @@ __device__ __forceinline__ void tc05_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16),
 // 128-byte swizzled, 1024-byte aligned: start address >> 4 in bits 0..13, leading byte
 // offset 1 (unused for swizzled K-major) in bits 16..29, stride byte offset (8 rows x 128 B =
@@ -140,38 +159,50 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
          ((uint32_t)(m >> 4) << 24);
 }
 
-// One CTA per SM (about 192 KB of stages) walks over tiles; two accumulators in tensor memory
-// let the epilogue of one tile overlap the main loop of the next.
-template <int BN, int STAGES_>
+// One CTA per SM walks over tiles; two accumulators in tensor memory let the epilogue of one
+// tile overlap the main loop of the next.  EPI 1 adds a staging area for the epilogue: 4 KB
+// (32 rows x 128 bytes, 128-byte swizzled) per epilogue warp for bf16 output, twice that for
+// fp32 output (two 32-column boxes per warp, which also receive the residual by TMA).
+template <int BN, int EPI, int ESIZE>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = STAGES_;
+  static constexpr int EPI_WARPS = epi_warps(BN, EPI);
+  static constexpr int STG_PER_WARP = EPI ? (ESIZE == 4 ? 8192 : 4096) : 0;
+  static constexpr int STG_BYTES = EPI_WARPS * STG_PER_WARP;
+  static constexpr int BUDGET = 222 * 1024;   // of the 227 KB a CTA may have
+  static constexpr int STAGES_RAW = (BUDGET - STG_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
-  // after the tiles: full[STAGES], empty[STAGES], accumulator full[2] / empty[2], then the
-  // tensor-memory base address and the abort flag
-  static constexpr int N_BARRIERS = 2 * STAGES + 4;
-  static constexpr int TOTAL = TILES_BYTES + N_BARRIERS * 8 + 16 + 1024 /* alignment slack */;
+  // after tiles and staging: full[STAGES], empty[STAGES], accumulator full[2] / empty[2], two
+  // residual barriers per epilogue warp, then the tensor-memory base address and the abort flag
+  static constexpr int N_BARRIERS = 2 * STAGES + 4 + 2 * EPI_WARPS;
+  static constexpr int TOTAL = TILES_BYTES + STG_BYTES + N_BARRIERS * 8 + 16 + 1024 /* alignment slack */;
 };
 
-template <int BN, int STAGES_, typename TOut>
-__global__ void __launch_bounds__(cta_threads(BN))
+template <int BN, int EPI, typename TOut>
+__global__ void __launch_bounds__(cta_threads(BN, EPI))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
-                    int K, int act, int tiles_n, int num_tiles) {
-  using L = SmemLayout<BN, STAGES_>;
+                    const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
+                    const float* residual, TOut* out, int M, int N, int K, int act, int tiles_n,
+                    int num_tiles) {
+  using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
+  constexpr int EW = L::EPI_WARPS;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment (swizzle atoms), computed on the shared-window address
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* gen = smem_dyn + (base - raw);
-  const uint32_t bars = base + L::TILES_BYTES;
+  const uint32_t stg_base = base + L::TILES_BYTES;          // epilogue staging (EPI 1)
+  const uint32_t bars = stg_base + L::STG_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (L::STAGES + s); };
   auto acc_full = [&](int b) { return bars + 8u * (2 * L::STAGES + b); };
   auto acc_empty = [&](int b) { return bars + 8u * (2 * L::STAGES + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + L::N_BARRIERS * 8);
+  auto res_bar = [&](int w, int u) { return bars + 8u * (2 * L::STAGES + 4 + 2 * w + u); };
+  uint32_t* tmem_slot =
+      reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + L::STG_BYTES + L::N_BARRIERS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,7 +215,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), epi_warps(BN));   // one arrival per epilogue warp
+      mbar_init(acc_empty(b), EW);   // one arrival per epilogue warp
+    }
+    for (int w = 0; w < EW; ++w) {
+      mbar_init(res_bar(w, 0), 1);
+      mbar_init(res_bar(w, 1), 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -254,10 +289,122 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (ok) tc05_commit(acc_full(ab));   // complete once all MMAs issued so far are done
       }
     }
-  } else {             // ------------------------------------------------------ epilogue
+  } else if constexpr (EPI == 1) {   // ---------- epilogue through shared memory and TMA stores
+    // Warp e of the epilogue owns the 32 tensor-memory lanes of its quarter and one 64-column
+    // unit of the tile.  bf16 output: the unit is one 32 x 64 box; fp32 output: two 32 x 32
+    // boxes, each in a buffer of its own, into which the residual (the output tensor itself,
+    // updated in place) is brought by TMA while the accumulator is still being computed.
+    // Rows and columns beyond M and N are clipped by the TMA unit.
+    constexpr bool F32 = sizeof(TOut) == 4;
+    constexpr int NBOX = F32 ? 2 : 1;
+    const int e = warp - 2;
+    const int quarter = warp & 3;
+    const int unit = e >> 2;                     // 64 columns each
+    const uint32_t stg = stg_base + (uint32_t)e * L::STG_PER_WARP;
+    const uint32_t my_row = stg + (uint32_t)lane * 128u;
+    const uint32_t swz = (uint32_t)(lane & 7);
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int row0 = m0 + quarter * 32, col0 = n0 + unit * 64;
+      const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
+      if (lane == 0) {
+        bulk_wait_read_all();   // the stores of the previous tile have read this warp's buffers
+        if (F32 && residual != nullptr) {
+#pragma unroll
+          for (int u = 0; u < NBOX; ++u) {
+            mbar_expect_tx(res_bar(e, u), 4096u);
+            tma_load_2d(stg + u * 4096u, &map_out, col0 + u * 32, row0, res_bar(e, u));
+          }
+        }
+      }
+      __syncwarp();
+      const bool ready =
+          __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
+      if (!ready) break;
+      tc05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN +
+                               (uint32_t)(unit * 64 + c * 32), v);
+        tc05_wait_ld();
+        if (c == 1) {   // this warp has read its share of the accumulator: hand it back
+          tc05_fence_before();
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
+        }
+        const int nb = col0 + c * 32;
+        float bias_l = 0.0f;
+        if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float x = __uint_as_float(v[j]) + __shfl_sync(0xffffffffu, bias_l, j);
+          f[j] = nb_apply_act_fast(x, act);
+        }
+        if constexpr (F32) {
+          const uint32_t buf = my_row + c * 4096u;
+          if (residual != nullptr) {
+            const bool got = __shfl_sync(0xffffffffu,
+                                         (int)mbar_wait(res_bar(e, c), t & 1u, abort_flag), 0) != 0;
+            if (got) {
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                float4 r4;
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=f"(r4.x), "=f"(r4.y), "=f"(r4.z), "=f"(r4.w)
+                             : "r"(buf + (((uint32_t)q4 ^ swz) << 4)));
+                f[4 * q4] += r4.x; f[4 * q4 + 1] += r4.y; f[4 * q4 + 2] += r4.z; f[4 * q4 + 3] += r4.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(buf + (((uint32_t)q4 ^ swz) << 4)),
+                         "f"(f[4 * q4]), "f"(f[4 * q4 + 1]), "f"(f[4 * q4 + 2]), "f"(f[4 * q4 + 3])
+                         : "memory");
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && nb < N && row0 < M) {
+            tma_store_2d(&map_out, stg + c * 4096u, nb, row0);
+            bulk_commit();
+          }
+        } else {
+          // 32 columns = four 16-byte pieces of the row's 128 bytes; the second chunk follows
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t p0, p1, p2, p3;
+            {
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(f[8 * q4], f[8 * q4 + 1]);
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(f[8 * q4 + 2], f[8 * q4 + 3]);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(f[8 * q4 + 4], f[8 * q4 + 5]);
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(f[8 * q4 + 6], f[8 * q4 + 7]);
+              p0 = *reinterpret_cast<uint32_t*>(&h0); p1 = *reinterpret_cast<uint32_t*>(&h1);
+              p2 = *reinterpret_cast<uint32_t*>(&h2); p3 = *reinterpret_cast<uint32_t*>(&h3);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(
+                             my_row + ((((uint32_t)(c * 4 + q4)) ^ swz) << 4)),
+                         "r"(p0), "r"(p1), "r"(p2), "r"(p3)
+                         : "memory");
+          }
+          if (c == 1) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && col0 < N && row0 < M) {
+              tma_store_2d(&map_out, stg, col0, row0);
+              bulk_commit();
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_all();   // stores must have left shared memory before it goes away
+  } else {             // ------------------------------------------------------ epilogue, direct stores
     const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
     const int half = (warp - 2) >> 2;   // which share of the tile's columns it takes
-    constexpr int CHUNKS = BN / 32 / (epi_warps(BN) / 4);   // 32-column chunks per warp
+    constexpr int CHUNKS = BN / 32 / (EW / 4);   // 32-column chunks per warp
     const bool vec_f32 = (N % 4 == 0);
     const bool vec_b16 = (N % 8 == 0);
     uint32_t t = 0;
@@ -346,6 +493,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
       }
     }
+  
   }
 
   tc05_fence_before();
@@ -387,33 +535,44 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A [rows, K] bf16 row-major matrix as a 2-D tensor map with boxes of `box_rows` x 64 elements.
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+// A [rows, cols] row-major matrix as a 2-D tensor map with 128-byte swizzled boxes of
+// box_rows x box_cols elements (box_cols * element size must be 128 bytes).
+int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows, int box_cols,
+             CUtensorMapDataType type, int esize) {
   EncodeTiledFn fn = encode_fn();
   NB_REQUIRE(fn != nullptr, NB_ERR_UNSUPPORTED, "gemm_tcgen05: cuTensorMapEncodeTiled not found");
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * esize};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = fn(map, type, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NB_REQUIRE(r == CUDA_SUCCESS, NB_ERR_BAD_ARG, "gemm_tcgen05: cuTensorMapEncodeTiled failed (%d)",
              (int)r);
   return 0;
 }
 
-template <int BN, int STAGES_, typename TOut>
+template <int BN, int EPI, typename TOut>
 int launch(const void* X, const void* W, const float* bias, const float* residual, void* out, int M,
            int N, int K, int act, cudaStream_t stream) {
-  CUtensorMap mx, mw;
-  int rc = make_map(&mx, X, M, K, BM);
+  using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
+  static_assert(L::STAGES >= 2, "tile shape leaves no room for a pipeline");
+  CUtensorMap mx, mw, mo;
+  int rc = make_map(&mx, X, M, K, BM, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, BN);
+  rc = make_map(&mw, W, N, K, BN, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES_, TOut>;
-  const int smem = SmemLayout<BN, STAGES_>::TOTAL;
+  if (EPI) {
+    rc = sizeof(TOut) == 4
+             ? make_map(&mo, out, M, N, 32, 32, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4)
+             : make_map(&mo, out, M, N, 32, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
+    if (rc) return rc;
+  } else {
+    mo = mx;   // unused
+  }
+  auto kern = gemm_tcgen05_kernel<BN, EPI, TOut>;
+  const int smem = L::TOTAL;
   static bool configured = false;   // per instantiation
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -429,8 +588,8 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
-  kern<<<grid, cta_threads(BN), smem, stream>>>(mx, mw, bias, residual, (TOut*)out, M, N, K, act,
-                                                tiles_n, (int)num_tiles);
+  kern<<<grid, cta_threads(BN, EPI), smem, stream>>>(mx, mw, mo, bias, residual, (TOut*)out, M, N, K,
+                                                      act, tiles_n, (int)num_tiles);
   return 0;
 }
 
@@ -470,20 +629,34 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   // tiles (more flops per byte brought in) win as soon as there is more than one row tile,
   // even when they leave some SMs without a tile; a single row tile (at most 128 rows) is a
   // weight stream, for which many narrow tiles with a deep ring are best.
-  const int bn = tiles_m == 1 ? 64 : (N >= 1024 ? 256 : (N >= 256 ? 128 : 64));
+  int bn = tiles_m == 1 ? 64 : (N >= 1024 ? 256 : (N >= 256 ? 128 : 64));
+  // Epilogue through shared memory and TMA stores (full-line writes, residual fetched by TMA)
+  // when the output rows are 16-byte multiples and the residual, if any, is the output
+  // itself; otherwise every thread stores its own row segment.
+  const int esize = out_dtype == NB_F32 ? 4 : 2;
+  const bool tma_epi = ((long long)N * esize) % 16 == 0 && (residual == nullptr || residual == out);
+  if (tma_epi && out_dtype == NB_F32 && bn == 256) bn = 128;   // two fp32 boxes per warp: room for 128
   int rc;
-#define NB_SHAPES(T_)                                                                   \
-  rc = bn == 256 ? launch<256, 4, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
-     : bn == 128 ? launch<128, 6, T_>(X, W, bias, residual, out, M, N, K, act, stream)  \
-                 : launch<64, 8, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
-    NB_SHAPES(float);
+    if (tma_epi)
+      rc = bn == 128 ? launch<128, 1, float>(X, W, bias, residual, out, M, N, K, act, stream)
+                     : launch<64, 1, float>(X, W, bias, residual, out, M, N, K, act, stream);
+    else
+      rc = bn == 256 ? launch<256, 0, float>(X, W, bias, residual, out, M, N, K, act, stream)
+         : bn == 128 ? launch<128, 0, float>(X, W, bias, residual, out, M, N, K, act, stream)
+                     : launch<64, 0, float>(X, W, bias, residual, out, M, N, K, act, stream);
   } else if (out_dtype == NB_BF16) {
-    NB_SHAPES(bf16);
+    if (tma_epi)
+      rc = bn == 256 ? launch<256, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+         : bn == 128 ? launch<128, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+                     : launch<64, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
+    else
+      rc = bn == 256 ? launch<256, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+         : bn == 128 ? launch<128, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
+                     : launch<64, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
   } else {
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
   }
-#undef NB_SHAPES
   if (rc) return rc;
   NB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
