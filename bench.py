@@ -256,30 +256,29 @@ def main() -> int:
                           "gpu_launches": launches}))
         return 0
 
+    # clocks and throttle reasons are sampled while all of the measurements below run
     with ClockSampler() as clocks:
         ms, launches, mean_ctx = time_decode(engine, BATCH, CONTEXT, args.steps, args.warmup)
-        clock_summary = None
-        time.sleep(0.15)
+        value = BATCH * 1000.0 / ms
+        kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * elt
+        step_bytes = engine.model.weight_bytes() + BATCH * mean_ctx * kv_bytes_per_token
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+
+        e2e = time_e2e(engine, BATCH, CONTEXT, args.steps, args.warmup)
+
+        pre_ms = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT)
+        pre_flops = model_flops_prefill(cfg, PREFILL_TOKENS // CONTEXT, CONTEXT)
+        peak_flops = peaks["bf16_tflops"] * 1e12 if dtype == "bfloat16" else 80e12
+        prefill = {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(pre_ms, 4), "frac": round(pre_flops / (pre_ms * 1e-3) / peak_flops, 4)}
+
+        points = {}
+        if not args.no_points:
+            for b in (1, 64):
+                pms, _, _ = time_decode(engine, b, CONTEXT, args.steps, args.warmup, seed=b)
+                points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+        time.sleep(0.12)
     clock_summary = clocks.summary()
-
-    value = BATCH * 1000.0 / ms
-    kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * elt
-    step_bytes = engine.model.weight_bytes() + BATCH * mean_ctx * kv_bytes_per_token
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-
-    e2e = time_e2e(engine, BATCH, CONTEXT, args.steps, args.warmup)
-
-    pre_ms = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT)
-    pre_flops = model_flops_prefill(cfg, PREFILL_TOKENS // CONTEXT, CONTEXT)
-    peak_flops = peaks["bf16_tflops"] * 1e12 if dtype == "bfloat16" else 80e12
-    prefill = {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
-               "ms": round(pre_ms, 4), "frac": round(pre_flops / (pre_ms * 1e-3) / peak_flops, 4)}
-
-    points = {}
-    if not args.no_points:
-        for b in (1, 64):
-            pms, _, _ = time_decode(engine, b, CONTEXT, args.steps, args.warmup, seed=b)
-            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
 
     out = {
         "metric": "decode tok/s, GPT-2 124M, batch 8, context 1024", "value": round(value, 1),

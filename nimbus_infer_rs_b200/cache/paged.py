@@ -9,6 +9,12 @@ A page holds ``PAGE`` consecutive tokens of one sequence, for every layer of the
 once, so a sequence's block table (its list of pages) is shared by the group's layers.  One
 (page, head) is a contiguous ``PAGE x head_dim`` tile, the unit the attention kernels load.
 
+A group with a window gives a page back to its pool as soon as every token of the page lies
+before the window of the sequence's next token (``trim``): a long sequence then holds about
+``window / PAGE + 2`` pages of that group, while a group without a window holds them all.
+The block-table entry of a page that was given back is never read again (the kernels start at
+the window's first key), so it is left as it is.
+
 The reference keeps one dense array per layer of ``(n_kv_heads, max_seq, head_dim)`` for a
 single sequence (src/cache.rs:10-29); paging replaces ``max_seq`` by the pages a sequence
 actually holds, so many sequences of unequal length share the memory.
@@ -80,7 +86,7 @@ class CacheGroup:
             dtype=dtype, device=device)
         self.block_table = torch.zeros((n_slots, self.max_pages), dtype=torch.int32, device=device)
         self._table_host = np.zeros((n_slots, self.max_pages), dtype=np.int32)
-        self._pages: dict[int, list[int]] = {}
+        self._pages: dict[int, list[int]] = {}   # slot -> page of every page index (-1: given back)
         self._dirty: set[int] = set()
 
     def bytes(self) -> int:
@@ -101,13 +107,29 @@ class CacheGroup:
         have.extend(new)
         self._dirty.add(slot)
 
+    def trim(self, slot: int, length: int) -> int:
+        """Give back the pages that lie wholly before the window of the token at position
+        ``length`` (the next one the sequence writes); returns how many.  That token reads the
+        keys at ``length - window + 1 .. length``."""
+        w = self.request.window
+        pages = self._pages.get(slot)
+        if w <= 0 or not pages:
+            return 0
+        first_needed = max(0, length - w + 1) // PAGE
+        gone = [p for p in pages[:first_needed] if p >= 0]
+        if gone:
+            self.pool.release(gone)
+            pages[:first_needed] = [-1] * first_needed
+        return len(gone)
+
     def release(self, slot: int) -> None:
         pages = self._pages.pop(slot, None)
         if pages:
-            self.pool.release(pages)
+            self.pool.release([p for p in pages if p >= 0])
 
     def pages_of(self, slot: int) -> list[int]:
-        return list(self._pages.get(slot, ()))
+        """The pages the slot holds now, in order of page index (pages given back left out)."""
+        return [p for p in self._pages.get(slot, ()) if p >= 0]
 
     def flush(self) -> None:
         """Bring the device block table up to date (one copy per changed row span)."""

@@ -90,7 +90,12 @@ class SequenceCache:
             g.flush()
 
     def advance(self, slot: int, n: int) -> None:
+        """The step that wrote ``n`` more tokens of ``slot`` has been launched.  Groups with a
+        window give back the pages no later token reads; work launched later on the same
+        stream may write them again, which is after every read of this step."""
         self.lens[slot] += n
+        for g in self.groups:
+            g.trim(slot, self.lens[slot])
 
     # ---------------------------------------------------------------- accounting
     def tokens_held(self) -> int:

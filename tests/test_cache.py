@@ -131,5 +131,36 @@ def test_random_traffic_never_loses_a_page():
             held = [p for s in live for p in g.pages_of(s)]
             assert len(held) == len(set(held))                       # no page held twice
             assert len(held) + g.pool.n_free == g.pool.n_pages       # none lost
+            w = g.request.window
             for s, n in live.items():
-                assert len(g.pages_of(s)) == pages_for(n)
+                before_window = max(0, n - w + 1) // PAGE if w else 0
+                assert len(g.pages_of(s)) == pages_for(n) - before_window
+
+
+def test_a_window_group_gives_back_the_pages_before_its_window():
+    kv = {0: KVRequest(2, 16), 1: KVRequest(2, 16, window=70)}
+    c = SequenceCache(kv, {}, cache_tokens=8 * PAGE, max_seq_len=8 * PAGE, dtype=torch.float32,
+                      device="cpu", n_slots=2)
+    full, win = c.groups
+    a = c.alloc_slot()
+    c.reserve([(a, 200)])                      # a prompt needs all of its pages during its step
+    assert len(full.pages_of(a)) == 4 and len(win.pages_of(a)) == 4
+    first_pages = win.pages_of(a)
+    c.advance(a, 200)
+    # the token at position 200 reads keys 131..200: page 2 (128..191) and page 3
+    assert len(full.pages_of(a)) == 4
+    assert win.pages_of(a) == first_pages[2:] and win.pool.n_free == 6
+    table = win.block_table[a].tolist()
+    assert table[2:4] == first_pages[2:]       # the pages still in use stay where they were
+    for step in range(200, 330):               # decode on: never more than three pages held
+        c.reserve([(a, 1)])
+        c.advance(a, 1)
+        assert len(win.pages_of(a)) <= 3 and len(full.pages_of(a)) == pages_for(step + 1)
+        first_key = max(0, c.lens[a] - 70 + 1)
+        assert win._pages[a][first_key // PAGE] >= 0          # the window's first page is held
+    b = c.alloc_slot()
+    c.reserve([(b, 2 * PAGE)])                 # room that the window group gave back is used
+    assert not set(win.pages_of(b)) & set(win.pages_of(a))
+    c.free_slot(a)
+    c.free_slot(b)
+    assert win.pool.n_free == 8 and full.pool.n_free == 8
