@@ -122,10 +122,21 @@ class Model:
         kv, st = {}, {}
         for entry, li in enumerate(self.run_order):
             layer = self.layers[li]
+            r = layer.mixer.cache_request()
             if layer.spec.cache_from is None:
-                r = layer.mixer.cache_request()
                 if r is not None:
                     kv[entry] = r
+            else:
+                # the reader must want what the owner keeps: same heads and head size, and no
+                # keys from before the owner's window
+                own = self.layers[layer.spec.cache_from].mixer.cache_request()
+                ok = (r is not None and own is not None and r.n_kv_heads == own.n_kv_heads
+                      and r.head_dim == own.head_dim
+                      and (own.window == 0 or 0 < r.window <= own.window))
+                if not ok:
+                    raise ValueError(
+                        f"layer {li} reads the cache of layer {layer.spec.cache_from}, which "
+                        f"keeps {own}, but asks for {r}")
             s = layer.mixer.state_request()
             if s is not None:
                 st[entry] = s

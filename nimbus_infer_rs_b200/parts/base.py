@@ -125,8 +125,11 @@ class Position(Part):
     #: the longest sequence this encoding can address, or None if unbounded
     max_positions: int | None = None
 
-    def rotate(self, ctx, qkv: torch.Tensor, layout) -> None:
-        """Hook for encodings that act on queries and keys before the cache write."""
+    def rotate(self, ctx, qkv: torch.Tensor, mixer) -> None:
+        """Hook for encodings that act on queries and keys, in place, before keys are written
+        to the cache.  ``qkv``: the step's rows [n_rows, q_width + 2 * kv_width] (queries, keys,
+        values side by side); ``mixer`` gives ``n_heads``, ``n_kv_heads``, ``head_dim``,
+        ``q_width`` and ``kv_width``; a row's position is ``ctx.layout.row_pos``."""
         return None
 
 
