@@ -52,7 +52,9 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return u;
 }
 
-constexpr int CH = 12;   // 32-wide K chunks whose weights a warp holds in registers at a time
+// CH, a template parameter of the kernel: the 32-wide K chunks whose weights a warp holds in
+// registers at a time (12 for long rows, 4 when that covers a whole row: fewer registers, so
+// that two CTAs fit on an SM).
 constexpr int VMAX = 8;  // most 8-element vectors of a row a thread may hold while it is normalised
 
 // Sum of `v` over the `tpr` consecutive threads that share a row (tpr is a multiple of 32 and
@@ -169,8 +171,8 @@ __device__ __forceinline__ void stage_rows_copy(const TX* __restrict__ X, bf16* 
 // blockIdx.x, blockIdx.x + gridDim.x, ... with the next group's weights already in flight.
 // Only the M real rows live in shared memory; the other rows of the 16-row MMA tile are zero
 // registers.  A fused norm needs a single segment (the launcher sees to it).
-template <int MT, int WARPS, typename TX, int VPT, typename TOut>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int MT, int WARPS, typename TX, int VPT, int CH, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32, (CH <= 4 && VPT <= 3 && MT == 1) ? 2 : 1)
 gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
                         const float* __restrict__ beta, float eps, const bf16* __restrict__ W,
                         const float* __restrict__ bias, const float* residual, TOut* out, int M,
@@ -415,8 +417,8 @@ inline int norm_threads_per_row(int n_threads, int M) {
   return n_threads / mp < 32 ? 32 : n_threads / mp;
 }
 
-template <int MT, int WARPS, typename TX, int VPT, typename TOut>
-int launch_bf16_v(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+template <int MT, int WARPS, typename TX, int VPT, int CH, typename TOut>
+int launch_bf16_c(const void* X, const float* gamma, const float* beta, float eps, const void* W,
                 const float* bias, const float* residual, void* out, int M, int N, int K, int act,
                 cudaStream_t stream) {
   // segment of K whose staged rows take about 96 KB at most (two CTAs per SM)
@@ -436,7 +438,7 @@ int launch_bf16_v(const void* X, const float* gamma, const float* beta, float ep
   }
   const size_t xs_bytes = (((size_t)M * (kseg + 8) * sizeof(bf16)) + 15) & ~(size_t)15;
   const size_t smem = xs_bytes + (size_t)WARPS * MT * 16 * 8 * sizeof(float) + WARPS * sizeof(float);
-  auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, VPT, TOut>;
+  auto kern = gemm_skinny_bf16_kernel<MT, WARPS, TX, VPT, CH, TOut>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int n_groups = (N + 7) / 8;
@@ -457,6 +459,19 @@ int launch_bf16_v(const void* X, const float* gamma, const float* beta, float ep
   return 0;
 }
 
+// Picks how many chunks of weights a warp holds at a time.
+template <int MT, int WARPS, typename TX, int VPT, typename TOut>
+int launch_bf16_v(const void* X, const float* gamma, const float* beta, float eps, const void* W,
+                  const float* bias, const float* residual, void* out, int M, int N, int K, int act,
+                  cudaStream_t stream) {
+  const int n_rounds = (K + 32 * WARPS - 1) / (32 * WARPS);
+  if (n_rounds <= 4)
+    return launch_bf16_c<MT, WARPS, TX, VPT, 4, TOut>(X, gamma, beta, eps, W, bias, residual, out, M,
+                                                      N, K, act, stream);
+  return launch_bf16_c<MT, WARPS, TX, VPT, 12, TOut>(X, gamma, beta, eps, W, bias, residual, out, M,
+                                                     N, K, act, stream);
+}
+
 // Picks the number of row vectors per thread for the fused norm (0 without a norm).
 template <int MT, int WARPS, typename TX, bool LN, typename TOut>
 int launch_bf16(const void* X, const float* gamma, const float* beta, float eps, const void* W,
@@ -471,6 +486,7 @@ int launch_bf16(const void* X, const float* gamma, const float* beta, float eps,
     const int vpt = (K / 8 + tpr - 1) / tpr;
     if (vpt <= 1) NB_V(1);
     if (vpt <= 2) NB_V(2);
+    if (vpt <= 3) NB_V(3);
     if (vpt <= 4) NB_V(4);
     NB_V(8);
   }

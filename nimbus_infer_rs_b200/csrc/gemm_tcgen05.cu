@@ -1,7 +1,8 @@
 // Matrix product on the 5th-generation tensor cores (sm_100a): out[M,N] = act(X[M,K] *
 // W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
 //
-// A CTA computes 128 x BN tiles (BN = 64, 128 or 256), one after another.  Warp 0 is the producer: one thread issues TMA loads of
+// A CTA computes 128 x BN tiles (BN = 64, 96, 128, 192 or 256, picked so that the tiles fill
+// the SMs in as few rounds as possible), one after another.  Warp 0 is the producer: one thread issues TMA loads of
 // 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
 // stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
@@ -37,7 +38,11 @@ constexpr int UMMA_K = 16;
 // With the direct-store epilogue (EPI 0) there are 16 warps for wide tiles, 8 otherwise; with
 // the shared-memory / TMA-store epilogue (EPI 1) every warp owns 64 columns of its quarter.
 __host__ __device__ constexpr int epi_warps(int bn, int epi) {
-  return epi ? bn / 16 : (bn >= 128 ? 16 : 8);
+  return epi ? 4 * ((bn + 63) / 64) : (bn >= 128 ? 16 : 8);
+}
+// Tensor-memory columns between the two accumulators of a CTA: allocations are powers of two.
+__host__ __device__ constexpr int acc_stride(int bn) {
+  return bn <= 64 ? 64 : (bn <= 128 ? 128 : 256);
 }
 __host__ __device__ constexpr int cta_threads(int bn, int epi) { return 64 + 32 * epi_warps(bn, epi); }
 constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
@@ -189,6 +194,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     int num_tiles) {
   using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
   constexpr int EW = L::EPI_WARPS;
+  constexpr int ACC = acc_stride(BN);
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
+  static_assert(EPI == 1 || BN == 64 || BN == 128 || BN == 256, "direct-store epilogue: 64/128/256");
+  static_assert(BN % 64 == 0 || (EPI == 1 && sizeof(TOut) == 4), "odd widths: fp32 TMA epilogue only");
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment (swizzle atoms), computed on the shared-window address
   const uint32_t raw = smem_u32(smem_dyn);
@@ -225,10 +234,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  if (warp == 1) {   // the whole warp allocates two accumulators of BN columns each
+  if (warp == 1) {   // the whole warp allocates two accumulators, ACC columns apart
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"((uint32_t)(2 * BN))
+                 "r"((uint32_t)(2 * ACC))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -268,7 +277,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         ok = mbar_wait(acc_empty(ab), aphase ^ 1u, abort_flag);   // the epilogue has drained it
         if (!ok) break;
         tc05_fence_after();
-        const uint32_t d_tmem = tmem_base + ab * BN;
+        const uint32_t d_tmem = tmem_base + ab * ACC;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t phase = (it / L::STAGES) & 1u;
@@ -291,15 +300,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   } else if constexpr (EPI == 1) {   // ---------- epilogue through shared memory and TMA stores
     // Warp e of the epilogue owns the 32 tensor-memory lanes of its quarter and one 64-column
-    // unit of the tile.  bf16 output: the unit is one 32 x 64 box; fp32 output: two 32 x 32
-    // boxes, each in a buffer of its own, into which the residual (the output tensor itself,
-    // updated in place) is brought by TMA while the accumulator is still being computed.
-    // Rows and columns beyond M and N are clipped by the TMA unit.
+    // unit of the tile (the last unit of a 96-wide tile has 32).  bf16 output: the unit is one
+    // 32 x 64 box; fp32 output: 32 x 32 boxes, each in a buffer of its own, into which the
+    // residual (the output tensor itself, updated in place) is brought by TMA while the
+    // accumulator is still being computed.  Rows and columns beyond M and N are clipped by the
+    // TMA unit.
     constexpr bool F32 = sizeof(TOut) == 4;
-    constexpr int NBOX = F32 ? 2 : 1;
     const int e = warp - 2;
     const int quarter = warp & 3;
     const int unit = e >> 2;                     // 64 columns each
+    const int nch = (unit * 64 + 64 <= BN) ? 2 : 1;   // 32-column chunks of this warp's unit
     const uint32_t stg = stg_base + (uint32_t)e * L::STG_PER_WARP;
     const uint32_t my_row = stg + (uint32_t)lane * 128u;
     const uint32_t swz = (uint32_t)(lane & 7);
@@ -311,8 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (lane == 0) {
         bulk_wait_read_all();   // the stores of the previous tile have read this warp's buffers
         if (F32 && residual != nullptr) {
-#pragma unroll
-          for (int u = 0; u < NBOX; ++u) {
+          for (int u = 0; u < nch; ++u) {
             mbar_expect_tx(res_bar(e, u), 4096u);
             tma_load_2d(stg + u * 4096u, &map_out, col0 + u * 32, row0, res_bar(e, u));
           }
@@ -324,12 +333,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (!ready) break;
       tc05_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < nch; ++c) {
         uint32_t v[32];
-        tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN +
+        tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * ACC +
                                (uint32_t)(unit * 64 + c * 32), v);
         tc05_wait_ld();
-        if (c == 1) {   // this warp has read its share of the accumulator: hand it back
+        if (c == nch - 1) {   // this warp has read its share of the accumulator: hand it back
           tc05_fence_before();
           __syncwarp();
           if (lane == 0)
@@ -421,7 +430,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
         uint32_t v[32];
         tc05_ld_32x32b_x32(
-            tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + (uint32_t)(c * 32), v);
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * ACC + (uint32_t)(c * 32), v);
         tc05_wait_ld();
         if (c == (half + 1) * CHUNKS - 1) {   // this warp has read its share: hand it back
           tc05_fence_before();
@@ -511,7 +520,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 1) {
     tc05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
-                 "r"((uint32_t)(2 * BN))
+                 "r"((uint32_t)(2 * ACC))
                  : "memory");
   }
 }
@@ -593,6 +602,38 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   return 0;
 }
 
+// Tile width.  A single row tile (at most 128 rows) is a weight stream: many narrow tiles
+// with a deep ring.  Otherwise every tile re-reads its 128 rows of X and its BN rows of W from
+// L2, so wide tiles win for large products; for products of a few hundred tiles what counts
+// is how many rounds the 148 SMs need and how long a round is, so the width is the one with
+// the least rounds x (width + a tile's fixed cost, about 48 columns' worth of time).  The
+// fp32 TMA epilogue has room for 128 columns at most and alone takes 96; the direct-store
+// epilogue takes 64, 128 and 256.
+int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {
+  const long long tiles_m = (M + BM - 1) / BM;
+  if (tiles_m == 1) return 64;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const int cand_f32_tma[] = {128, 96, 64}, cand_bf16_tma[] = {256, 192, 128, 64}, cand_direct[] = {256, 128, 64};
+  const int* cand = !tma_epi ? cand_direct : (f32_out ? cand_f32_tma : cand_bf16_tma);
+  const int n_cand = !tma_epi ? 3 : (f32_out ? 3 : 4);
+  int best = cand[n_cand - 1];
+  long long best_cost = -1;
+  for (int i = 0; i < n_cand; ++i) {
+    const int bn = cand[i];
+    if (bn > 64 && N < bn) continue;                       // wider than the output: wasted columns
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    const long long cost = ((tiles + sms - 1) / sms) * (bn + 48);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }   // ties: the wider
+  }
+  return best;
+}
+
 }  // namespace
 
 // 1 if the tensor-core kernel takes this product.
@@ -622,41 +663,31 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   NB_REQUIRE((uintptr_t)X % 16 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                  (uintptr_t)residual % 16 == 0,
              NB_ERR_UNSUPPORTED, "gemm_tcgen05: operands must be 16-byte aligned");
-  // tile shape: one row tile streaming a weight matrix -> narrow tiles, deep pipeline;
-  // otherwise fill the 148 SMs twice over (two CTAs per SM) before going to wider tiles
-  const long long tiles_m = (M + BM - 1) / BM;
-  // Tile width.  Every tile re-reads its 128 rows of X and its BN rows of W from L2, so wide
-  // tiles (more flops per byte brought in) win as soon as there is more than one row tile,
-  // even when they leave some SMs without a tile; a single row tile (at most 128 rows) is a
-  // weight stream, for which many narrow tiles with a deep ring are best.
-  int bn = tiles_m == 1 ? 64 : (N >= 1024 ? 256 : (N >= 256 ? 128 : 64));
   // Epilogue through shared memory and TMA stores (full-line writes, residual fetched by TMA)
   // when the output rows are 16-byte multiples and the residual, if any, is the output
   // itself; otherwise every thread stores its own row segment.
   const int esize = out_dtype == NB_F32 ? 4 : 2;
   const bool tma_epi = ((long long)N * esize) % 16 == 0 && (residual == nullptr || residual == out);
-  if (tma_epi && out_dtype == NB_F32 && bn == 256) bn = 128;   // two fp32 boxes per warp: room for 128
+  const int bn = pick_tile_width(M, N, out_dtype == NB_F32, tma_epi);
   int rc;
+#define NB_TC(BN_, EPI_, T_) rc = launch<BN_, EPI_, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
-    if (tma_epi)
-      rc = bn == 128 ? launch<128, 1, float>(X, W, bias, residual, out, M, N, K, act, stream)
-                     : launch<64, 1, float>(X, W, bias, residual, out, M, N, K, act, stream);
-    else
-      rc = bn == 256 ? launch<256, 0, float>(X, W, bias, residual, out, M, N, K, act, stream)
-         : bn == 128 ? launch<128, 0, float>(X, W, bias, residual, out, M, N, K, act, stream)
-                     : launch<64, 0, float>(X, W, bias, residual, out, M, N, K, act, stream);
+    if (tma_epi) {
+      if (bn == 128) NB_TC(128, 1, float); else if (bn == 96) NB_TC(96, 1, float); else NB_TC(64, 1, float);
+    } else {
+      if (bn == 256) NB_TC(256, 0, float); else if (bn == 128) NB_TC(128, 0, float); else NB_TC(64, 0, float);
+    }
   } else if (out_dtype == NB_BF16) {
-    if (tma_epi)
-      rc = bn == 256 ? launch<256, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-         : bn == 128 ? launch<128, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-                     : launch<64, 1, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
-    else
-      rc = bn == 256 ? launch<256, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-         : bn == 128 ? launch<128, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-                     : launch<64, 0, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
+    if (tma_epi) {
+      if (bn == 256) NB_TC(256, 1, bf16); else if (bn == 192) NB_TC(192, 1, bf16);
+      else if (bn == 128) NB_TC(128, 1, bf16); else NB_TC(64, 1, bf16);
+    } else {
+      if (bn == 256) NB_TC(256, 0, bf16); else if (bn == 128) NB_TC(128, 0, bf16); else NB_TC(64, 0, bf16);
+    }
   } else {
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
   }
+#undef NB_TC
   if (rc) return rc;
   NB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;

@@ -12,7 +12,6 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_double, c_float, c_int, c_void_p
 
 import torch
 
@@ -37,8 +36,15 @@ def dtype_code(t: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t}") from None
 
 
-def _ptr(t: torch.Tensor | None) -> c_void_p:
-    return c_void_p(0 if t is None else t.data_ptr())
+def _ptr(t: torch.Tensor | None) -> int:
+    """The tensor's address (0 for None); the entry points declare their pointer arguments."""
+    return 0 if t is None else t.data_ptr()
+
+
+try:    # the current stream's handle without building a Stream object (a few hundred ns)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:   # pragma: no cover
+    _raw_stream = None
 
 
 def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
@@ -59,8 +65,10 @@ class CudaBackend:
 
     def __init__(self):
         from . import build
+        from .signatures import declare
         self.lib = build.load()
-        self.lib.nb_last_error.restype = ctypes.c_char_p
+        declare(self.lib)
+        self._device_index = torch.cuda.current_device()
         self.launches = 0  # kernels launched through this backend (for measurement reports)
         self._scratch = {}
         self._argmax_scratch = {}
@@ -71,12 +79,14 @@ class CudaBackend:
         self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "0") == "1")
 
     def set_overlap(self, on: bool) -> None:
-        self.lib.nb_set_overlap(c_int(1 if on else 0))
+        self.lib.nb_set_overlap((1 if on else 0))
         self.overlap = bool(on)
 
     # -- plumbing ---------------------------------------------------------------------
-    def _stream(self) -> c_void_p:
-        return c_void_p(torch.cuda.current_stream().cuda_stream)
+    def _stream(self) -> int:
+        if _raw_stream is not None:
+            return _raw_stream(self._device_index)
+        return torch.cuda.current_stream().cuda_stream
 
     def _call(self, fn_name: str, *args) -> None:
         rc = getattr(self.lib, fn_name)(*args)
@@ -97,7 +107,7 @@ class CudaBackend:
         if tokens.numel() < n or pos.numel() < n or wte.shape[1] != d:
             raise KernelError("embed_pos: shapes do not agree")
         self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
-                   c_int(dtype_code(wte.dtype)), _ptr(out), c_int(n), c_int(d), self._stream())
+                   (dtype_code(wte.dtype)), _ptr(out), (n), (d), self._stream())
 
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         _check(x, "x", torch.float32, 2)
@@ -111,7 +121,7 @@ class CudaBackend:
         if x.shape[1] != d or gamma.numel() != d or (rows is None and x.shape[0] < n):
             raise KernelError("layernorm: shapes do not agree")
         self._call("nb_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
-                   c_int(dtype_code(out.dtype)), c_int(n), c_int(d), c_float(eps), self._stream())
+                   (dtype_code(out.dtype)), (n), (d), (eps), self._stream())
 
     # -- matrix products --------------------------------------------------------------
     def linear(self, x, w, bias, out, act=ACT_NONE, residual=None, norm=None):
@@ -147,24 +157,24 @@ class CudaBackend:
                 self.layernorm(x, norm[0], norm[1], norm[2], h)
                 x, norm = h, None
             gamma, beta, eps = (norm[0], norm[1], norm[2]) if norm is not None else (None, None, 0.0)
-            self._call("nb_gemm_skinny", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(gamma),
-                       _ptr(beta), c_float(eps), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
-                       _ptr(residual), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N),
-                       c_int(K), c_int(act), self._stream())
+            self._call("nb_gemm_skinny", _ptr(x), (dtype_code(x.dtype)), _ptr(gamma),
+                       _ptr(beta), (eps), _ptr(w), (dtype_code(w.dtype)), _ptr(bias),
+                       _ptr(residual), _ptr(out), (dtype_code(out.dtype)), (M), (N),
+                       (K), (act), self._stream())
             return
         if norm is not None:
             h = torch.empty((M, K), device=x.device, dtype=norm[3])
             self.layernorm(x, norm[0], norm[1], norm[2], h)
             x = h
         if self.use_tcgen05 and self.lib.nb_gemm_tcgen05_supported(
-                c_int(dtype_code(x.dtype)), c_int(dtype_code(w.dtype)), c_int(M), c_int(N), c_int(K)):
+                (dtype_code(x.dtype)), (dtype_code(w.dtype)), (M), (N), (K)):
             self._call("nb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
-                       c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),
+                       (dtype_code(out.dtype)), (M), (N), (K), (act),
                        self._stream())
             return
-        self._call("nb_gemm_simt", _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w),
-                   c_int(dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
-                   c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(act),
+        self._call("nb_gemm_simt", _ptr(x), (dtype_code(x.dtype)), _ptr(w),
+                   (dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
+                   (dtype_code(out.dtype)), (M), (N), (K), (act),
                    self._stream())
 
     def check_device_errors(self) -> None:
@@ -189,12 +199,17 @@ class CudaBackend:
             self._scratch[device] = s
         return s
 
+    def scratch_refs(self):
+        """The scratch tensors kernels currently use: whoever records launches in a CUDA graph
+        keeps these alive with it (growing a scratch buffer replaces the tensor)."""
+        return (dict(self._scratch), dict(self._argmax_scratch))
+
     def kv_append(self, src, k_col, v_col, row_slot, row_pos, kv, n_rows):
         _check(src, "src", kv.k.dtype, 2)
-        self._call("nb_kv_append", _ptr(src), c_int(dtype_code(src.dtype)), c_int(src.shape[1]),
-                   c_int(k_col), c_int(v_col), _ptr(row_slot), _ptr(row_pos), _ptr(kv.k),
-                   _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),
-                   c_int(kv.page), c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(n_rows),
+        self._call("nb_kv_append", _ptr(src), (dtype_code(src.dtype)), (src.shape[1]),
+                   (k_col), (v_col), _ptr(row_slot), _ptr(row_pos), _ptr(kv.k),
+                   _ptr(kv.v), _ptr(kv.block_table), (kv.block_table.shape[1]),
+                   (kv.page), (kv.n_kv_heads), (kv.head_dim), (n_rows),
                    self._stream())
 
     def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
@@ -208,44 +223,44 @@ class CudaBackend:
         if out.shape[0] < n_rows or out.shape[1] != n_heads * kv.head_dim:
             raise KernelError("attention: output shape does not match")
         if layout.is_decode and self.lib.nb_attention_decode_supported(
-                c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
-                c_int(kv.n_kv_heads), c_int(kv.page)):
+                (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
+                (kv.n_kv_heads), (kv.page)):
             pages = max(1, -(-layout.max_kv_len // kv.page))
             n_splits = max(1, min(pages, DECODE_TARGET_CTAS // (n_rows * kv.n_kv_heads)))
             acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
                                                      kv.head_dim, n_splits)
-            self._call("nb_attention_decode", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
-                       c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot),
+            self._call("nb_attention_decode", _ptr(q_src), (dtype_code(q_src.dtype)),
+                       (q_src.shape[1]), (q_col), _ptr(layout.row_slot),
                        _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
-                       c_int(kv.block_table.shape[1]), c_int(kv.page), c_int(n_heads),
-                       c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
-                       c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
-                       c_int(window), c_int(n_rows), c_int(n_splits), _ptr(acc), _ptr(ml),
-                       _ptr(counters), c_int(1 if append else 0),
-                       c_int(append[0] if append else 0), c_int(append[1] if append else 0),
+                       (kv.block_table.shape[1]), (kv.page), (n_heads),
+                       (kv.n_kv_heads), (kv.head_dim), _ptr(out),
+                       (dtype_code(out.dtype)), (out.shape[1]), (scale),
+                       (window), (n_rows), (n_splits), _ptr(acc), _ptr(ml),
+                       _ptr(counters), (1 if append else 0),
+                       (append[0] if append else 0), (append[1] if append else 0),
                        self._stream())
             return
         if append:
             self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
         if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
-                c_int(dtype_code(q_src.dtype)), c_int(kv.head_dim), c_int(n_heads),
-                c_int(kv.n_kv_heads), c_int(kv.page), c_int(q_src.shape[1]), c_int(q_col)):
+                (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
+                (kv.n_kv_heads), (kv.page), (q_src.shape[1]), (q_col)):
             if layout.n_rows > layout.n_tokens:
                 out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
-            self._call("nb_attention_prefill", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
-                       c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.cu_rows),
+            self._call("nb_attention_prefill", _ptr(q_src), (dtype_code(q_src.dtype)),
+                       (q_src.shape[1]), (q_col), _ptr(layout.cu_rows),
                        _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
-                       _ptr(kv.block_table), c_int(kv.block_table.shape[1]), c_int(kv.page),
-                       c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim), _ptr(out),
-                       c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
-                       c_int(window), c_int(layout.n_seqs), c_int(layout.max_q_len), self._stream())
+                       _ptr(kv.block_table), (kv.block_table.shape[1]), (kv.page),
+                       (n_heads), (kv.n_kv_heads), (kv.head_dim), _ptr(out),
+                       (dtype_code(out.dtype)), (out.shape[1]), (scale),
+                       (window), (layout.n_seqs), (layout.max_q_len), self._stream())
             return
-        self._call("nb_attention_generic", _ptr(q_src), c_int(dtype_code(q_src.dtype)),
-                   c_int(q_src.shape[1]), c_int(q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
-                   _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.shape[1]),
-                   c_int(kv.page), c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim),
-                   _ptr(out), c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_float(scale),
-                   c_int(window), c_int(n_rows), self._stream())
+        self._call("nb_attention_generic", _ptr(q_src), (dtype_code(q_src.dtype)),
+                   (q_src.shape[1]), (q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
+                   _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), (kv.block_table.shape[1]),
+                   (kv.page), (n_heads), (kv.n_kv_heads), (kv.head_dim),
+                   _ptr(out), (dtype_code(out.dtype)), (out.shape[1]), (scale),
+                   (window), (n_rows), self._stream())
 
     def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
         """tokens <- next_tokens, row_pos += 1 for live rows (between two decode steps)."""
@@ -253,7 +268,7 @@ class CudaBackend:
                      (row_slot, "row_slot")):
             _check(t, n, torch.int32, 1)
         self._call("nb_advance_decode", _ptr(tokens), _ptr(next_tokens), _ptr(row_pos),
-                   _ptr(row_slot), c_int(tokens.numel()), self._stream())
+                   _ptr(row_slot), (tokens.numel()), self._stream())
 
     # -- sampling ---------------------------------------------------------------------
     def argmax(self, logits, out):
@@ -267,26 +282,26 @@ class CudaBackend:
                 s = (torch.zeros(max(n, 256), dtype=torch.int64, device=logits.device),
                      torch.zeros(max(n, 256), dtype=torch.int32, device=logits.device))
                 self._argmax_scratch[logits.device] = s
-            self._call("nb_argmax_split", _ptr(logits), c_int(n), c_int(v), _ptr(out), _ptr(s[0]),
-                       _ptr(s[1]), c_int(n_ctas), self._stream())
+            self._call("nb_argmax_split", _ptr(logits), (n), (v), _ptr(out), _ptr(s[0]),
+                       _ptr(s[1]), (n_ctas), self._stream())
             return
-        self._call("nb_argmax", _ptr(logits), c_int(n), c_int(v), _ptr(out), self._stream())
+        self._call("nb_argmax", _ptr(logits), (n), (v), _ptr(out), self._stream())
 
     def sample_temperature(self, logits, temperature, u, out):
         _check(logits, "logits", torch.float32, 2)
         _check(u, "u", torch.float64, 1)
         _check(out, "out", torch.int32, 1)
         n, v = logits.shape
-        self._call("nb_sample_temperature", _ptr(logits), c_int(n), c_int(v),
-                   c_float(temperature), _ptr(u), _ptr(out), self._stream())
+        self._call("nb_sample_temperature", _ptr(logits), (n), (v),
+                   (temperature), _ptr(u), _ptr(out), self._stream())
 
     def repetition_penalty(self, logits, history, history_len, penalty):
         _check(logits, "logits", torch.float32, 2)
         _check(history, "history", torch.int32, 2)
         _check(history_len, "history_len", torch.int32, 1)
         n, v = logits.shape
-        self._call("nb_repetition_penalty", _ptr(logits), c_int(n), c_int(v), _ptr(history),
-                   c_int(history.shape[1]), _ptr(history_len), c_float(penalty), self._stream())
+        self._call("nb_repetition_penalty", _ptr(logits), (n), (v), _ptr(history),
+                   (history.shape[1]), _ptr(history_len), (penalty), self._stream())
 
 
 _backend = None

@@ -1,0 +1,50 @@
+"""Argument types of the library's ``extern "C"`` entry points, one letter per argument:
+``p`` pointer or stream, ``i`` int, ``f`` float, ``d`` double.  With these declared, the
+callers pass plain Python numbers and addresses, which ctypes converts without a wrapper
+object per argument (a prefill step makes about a hundred calls, and the host must keep ahead
+of the GPU).  ``tests/test_signatures.py`` derives the same table from the CUDA sources."""
+from __future__ import annotations
+
+import ctypes
+
+SIGNATURES = {
+    "nb_attention_decode_supported": "iiiii",
+    "nb_attention_decode_scratch": "iiiiippp",
+    "nb_attention_decode": "piiipppppiiiiipiifiiipppiiip",
+    "nb_attention_decode_static": "piiipppppiiiiipiifiiip",
+    "nb_attention_generic": "piiipppppiiiiipiifiip",
+    "nb_attention_prefill_supported": "iiiiiii",
+    "nb_attention_prefill": "piiippppppiiiiipiifiiip",
+    "nb_gemm_simt": "pipipppiiiiip",
+    "nb_gemm_skinny": "pippfpipppiiiiip",
+    "nb_gemm_tcgen05_supported": "iiiii",
+    "nb_gemm_tcgen05_error": "",
+    "nb_gemm_tcgen05": "pppppiiiiip",
+    "nb_abi_version": "",
+    "nb_set_overlap": "i",
+    "nb_get_overlap": "",
+    "nb_embed_pos": "ppppipiip",
+    "nb_layernorm": "pppppiiifp",
+    "nb_kv_append": "piiiipppppiiiiip",
+    "nb_advance_decode": "ppppip",
+    "nb_repetition_penalty": "piipipfp",
+    "nb_argmax_split": "piipppip",
+    "nb_argmax": "piipp",
+    "nb_sample_temperature": "piifppp",
+}
+
+_CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}
+
+
+def declare(lib) -> None:
+    """Set ``argtypes`` (and ``int`` results) on every entry point of the loaded library."""
+    for name, letters in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = [_CTYPE[c] for c in letters]
+        fn.restype = ctypes.c_int
+    lib.nb_set_overlap.restype = None
+    lib.nb_attention_decode_scratch.restype = None
+    lib.nb_last_error.argtypes = []
+    lib.nb_last_error.restype = ctypes.c_char_p
+    lib.nb_attention_decode_static_capacity.argtypes = []
+    lib.nb_attention_decode_static_capacity.restype = ctypes.c_longlong

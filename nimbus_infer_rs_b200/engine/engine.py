@@ -20,10 +20,11 @@ from ..csrc import ops as ops_mod
 from ..sampling import BatchSampler, SamplingParams, SequenceSampler
 from ..weights.loader import find_weight_file, load_params
 from ..weights.safetensors_io import SafeTensorsFile
-from .batch import build_layout
+from .batch import pack_step
 from .context import StepContext
 from .generate import plan_batches, run_batch, token_budget
 from .model import PRECISIONS, Model, Runtime
+from .step_graphs import StepGraphs
 
 
 class Engine:
@@ -43,6 +44,10 @@ class Engine:
         self.cache = SequenceCache(kv_req, st_req, cache_tokens=cache_tokens,
                                    max_seq_len=self.spec.max_seq_len, dtype=self.rt.act_dtype,
                                    device=self.rt.device, n_slots=n_slots)
+        # steps of a shape that comes again are replayed as CUDA graphs (``step_graphs = None``
+        # keeps every step on plain launches)
+        self.step_graphs = StepGraphs(self) if (
+            self.graph_safe and self.rt.device.type == "cuda") else None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -134,9 +139,14 @@ class Engine:
         entries = self._check_entries(entries)
         self.cache.reserve([(slot, len(toks)) for slot, toks, _ in entries])
         pos0 = [self.cache.lens[slot] for slot, _, _ in entries]
-        layout = build_layout(entries, pos0, self.rt.device)
-        ctx = StepContext(self.rt, self.ops, layout, self.model.position, self.cache)
-        logits = self.model.forward(ctx)
+        packed = pack_step(entries, pos0)
+        done, logits = self.step_graphs.run(packed) if self.step_graphs else (False, None)
+        if not done:
+            layout = packed.on_device(
+                packed.copy_to(self.rt.device),
+                max_kv_len=self.step_graphs.kv_bound(packed) if self.step_graphs else None)
+            ctx = StepContext(self.rt, self.ops, layout, self.model.position, self.cache)
+            logits = self.model.forward(ctx)
         for slot, toks, _ in entries:
             self.cache.advance(slot, len(toks))
         return logits

@@ -219,3 +219,46 @@ def test_stored_32bit_weights_stay_32bit_in_a_bfloat16_run(model_dirs):
     e = _engine(model_dirs, "A", "bfloat16")
     assert e.model.params["layers.0.ffn.fc.weight"].dtype == torch.bfloat16
     assert e.model.params["final_norm.weight"].dtype == torch.float32
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_steps_of_a_shape_that_comes_again_are_replayed_and_change_nothing(model_dirs, name, dtype):
+    """Steps of one shape (same numbers of rows, sequences and wanted places) with other
+    tokens, in other slots, at other lengths: from the second on they are replayed from a
+    recorded CUDA graph.  Each must equal the plain implementation and, bit for bit, an engine
+    that never records."""
+    e = _engine(model_dirs, name, dtype, n_slots=6)
+    plain = _engine(model_dirs, name, dtype, n_slots=6)
+    plain.step_graphs.capacity = 0            # never records
+    V = e.spec.vocab_size
+    # prompts: three steps of shape (20 + 7 tokens, wanted: 2 + 1), in different slots
+    held = []
+    for r in range(3):
+        for eng in (e, plain):
+            eng._slots = [eng.alloc_slot() for _ in range(2)]
+        assert e._slots == plain._slots
+        a, b = random_tokens(V, 20, seed=50 + r), random_tokens(V, 7, seed=60 + r)
+        req = [(e._slots[0], a, [3, 19]), (e._slots[1], b, [6])]
+        out, ref = e.step(req), plain.step(req)
+        assert torch.equal(out, ref), f"prompt step {r}"
+        assert_close(out, torch.cat([plain_logits(model_dirs[name], a)[[3, 19]],
+                                     plain_logits(model_dirs[name], b)[[6]]]), dtype, f"prompts {r}")
+        held.append((list(e._slots), [a, b]))
+    assert e.step_graphs.captures == 1 and e.step_graphs.replays == 2
+    # one token each for all six sequences, many times over: lengths cross a page boundary
+    # and the power-of-two range of the longest sequence changes on the way
+    seqs = [(s, list(t)) for slots, toks in held for s, t in zip(slots, toks)]
+    n_dec = min(60, e.spec.max_seq_len - 20)
+    new = [random_tokens(V, n_dec, seed=70 + i) for i in range(len(seqs))]
+    for t in range(n_dec):
+        req = [(s, [new[i][t]], [0]) for i, (s, _) in enumerate(seqs)]
+        out, ref = e.step(req), plain.step(req)
+        assert torch.equal(out, ref), f"decode step {t}"
+        for i, (_, toks) in enumerate(seqs):
+            toks.append(new[i][t])
+        if t in (0, 1, 2, n_dec // 2, n_dec - 1):
+            want = torch.stack([plain_logits(model_dirs[name], toks)[-1] for _, toks in seqs])
+            assert_close(out, want, dtype, f"decode step {t}")
+    assert e.step_graphs.replays >= 2 + n_dec - 4 and plain.step_graphs.replays == 0
+    e.ops.check_device_errors()
