@@ -272,13 +272,15 @@ def main() -> int:
         prefill = {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
                    "ms": round(pre_ms, 4), "frac": round(pre_flops / (pre_ms * 1e-3) / peak_flops, 4)}
 
-        points = {}
-        if not args.no_points:
-            for b in (1, 64):
-                pms, _, _ = time_decode(engine, b, CONTEXT, args.steps, args.warmup, seed=b)
-                points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
         time.sleep(0.12)
     clock_summary = clocks.summary()
+    # the other batch sizes run without the clock sampler beside them: a step at batch 1 is
+    # short enough for the sampler's process to show in it
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = time_decode(engine, b, CONTEXT, args.steps, args.warmup, seed=b)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
 
     out = {
         "metric": "decode tok/s, GPT-2 124M, batch 8, context 1024", "value": round(value, 1),

@@ -20,6 +20,10 @@ ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GEL
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
+# CTAs the tensor-core prefill attention aims to put on the GPU by cutting the keys of a tile
+# into runs: one per SM.  (Two of its CTAs on an SM are bound by instruction issue, so cutting
+# further only adds the merge; measured on GPT-2 124M, 2 x 1024 tokens.)
+PREFILL_TARGET_CTAS = 148
 FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to this many rows
 FUSED_NORM_MAX_COLS = 16384    # ... and output columns (a long weight stream wants the leaner kernel)
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
@@ -72,6 +76,7 @@ class CudaBackend:
         self.launches = 0  # kernels launched through this backend (for measurement reports)
         self._scratch = {}
         self._argmax_scratch = {}
+        self._prefill_scr = {}
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
@@ -182,6 +187,9 @@ class CudaBackend:
         if self.lib.nb_gemm_tcgen05_error() != 0:
             raise KernelError("gemm_tcgen05: a wait on a shared-memory barrier ran out of time; "
                               "the results of that product are not valid")
+        if self.lib.nb_attention_prefill_tc_error() != 0:
+            raise KernelError("attention_prefill_tc: a wait on a shared-memory barrier ran out of "
+                              "time; the results of that attention are not valid")
 
     # -- cache and attention ----------------------------------------------------------
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
@@ -202,7 +210,19 @@ class CudaBackend:
     def scratch_refs(self):
         """The scratch tensors kernels currently use: whoever records launches in a CUDA graph
         keeps these alive with it (growing a scratch buffer replaces the tensor)."""
-        return (dict(self._scratch), dict(self._argmax_scratch))
+        return (dict(self._scratch), dict(self._argmax_scratch), dict(self._prefill_scr))
+
+    def _prefill_scratch(self, device, n_tiles, max_splits, head_dim):
+        """Scratch of the split prefill attention: one record per (tile, split) and one counter
+        per tile; the counters start at zero and every launch leaves them at zero."""
+        rec = self.lib.nb_attention_prefill_tc_record(head_dim)
+        need = n_tiles * max_splits * rec
+        s = self._prefill_scr.get(device)
+        if s is None or s[0].numel() < need or s[1].numel() < n_tiles:
+            s = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device),
+                 torch.zeros(max(n_tiles, 1 << 12), dtype=torch.int32, device=device))
+            self._prefill_scr[device] = s
+        return s
 
     def kv_append(self, src, k_col, v_col, row_slot, row_pos, kv, n_rows):
         _check(src, "src", kv.k.dtype, 2)
@@ -242,6 +262,35 @@ class CudaBackend:
             return
         if append:
             self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
+        if (not layout.is_decode) and self.use_tcgen05 and self.lib.nb_attention_prefill_tc_supported(
+                dtype_code(q_src.dtype), kv.head_dim, n_heads, kv.n_kv_heads, kv.page,
+                q_src.shape[1], q_col, dtype_code(out.dtype), out.shape[1]):
+            # 5th-generation tensor cores, scores in tensor memory
+            if layout.n_rows > layout.n_tokens:
+                out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
+            # A CTA takes a 128-row tile of one head.  When there are too few of them to fill
+            # the GPU, the pages a tile reads are cut into up to four runs of at least four
+            # pages, one CTA each, and merged by the CTA that finishes last.
+            tiles = -(-layout.max_q_len // 128)
+            ctas = tiles * n_heads * layout.n_seqs
+            pages = -(-layout.max_kv_len // kv.page)
+            if window > 0:
+                pages = min(pages, (window + 127) // kv.page + 2)
+            max_splits = 1
+            if 2 * ctas <= PREFILL_TARGET_CTAS and pages >= 8:
+                max_splits = min(4, PREFILL_TARGET_CTAS // ctas, pages // 4)
+            chunk = -(-pages // max_splits)
+            part = counters = None
+            if max_splits > 1:
+                part, counters = self._prefill_scratch(q_src.device, ctas, max_splits, kv.head_dim)
+            self._call("nb_attention_prefill_tc", _ptr(q_src), dtype_code(q_src.dtype),
+                       q_src.shape[1], q_col, q_src.shape[0], _ptr(layout.cu_rows),
+                       _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
+                       kv.k.shape[0], _ptr(kv.block_table), kv.block_table.shape[1], kv.page,
+                       n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out), dtype_code(out.dtype),
+                       out.shape[1], scale, window, layout.n_seqs, layout.max_q_len,
+                       max_splits, chunk, _ptr(part), _ptr(counters), self._stream())
+            return
         if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
                 (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
                 (kv.n_kv_heads), (kv.page), (q_src.shape[1]), (q_col)):

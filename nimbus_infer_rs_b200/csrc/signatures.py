@@ -15,6 +15,10 @@ SIGNATURES = {
     "nb_attention_generic": "piiipppppiiiiipiifiip",
     "nb_attention_prefill_supported": "iiiiiii",
     "nb_attention_prefill": "piiippppppiiiiipiifiiip",
+    "nb_attention_prefill_tc_supported": "iiiiiiiii",
+    "nb_attention_prefill_tc_error": "",
+    "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippp",
+    "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",
     "nb_gemm_tcgen05_supported": "iiiii",

@@ -41,12 +41,12 @@ class StepGraphs:
         self.replays = 0
         self.captures = 0
 
-    def kv_bound(self, p: PackedStep) -> int | None:
-        """For a one-token step, the length that stands for ``max_kv_len`` in its launches (the
-        split of the keys among CTAs depends on it): the upper end of the range its longest
-        sequence falls in, so that one recording serves the whole range.  The plain first run
-        of a shape uses the same bound, so that it and the replays give identical results."""
-        return _kv_range(p.max_kv_len, self.engine.spec.max_seq_len) if p.is_decode else None
+    def kv_bound(self, p: PackedStep) -> int:
+        """The length that stands for ``max_kv_len`` in the step's launches (how the keys are
+        split among CTAs depends on it): the upper end of the range the longest sequence falls
+        in, so that one recording serves the whole range.  The plain first run of a shape uses
+        the same bound, so that it and the replays give identical results."""
+        return _kv_range(p.max_kv_len, self.engine.spec.max_seq_len)
 
     def key(self, p: PackedStep):
         return (p.n_rows, p.n_seqs, p.n_want, p.max_q_len, p.is_decode, p.want_all_rows,

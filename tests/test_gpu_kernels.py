@@ -183,6 +183,49 @@ def test_attention_over_paged_cache(ops, dtype, H, Hk, hd, window):
     assert (out[r:] == 0).all()                  # padding rows give zeros
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("lens, new", [([450, 129, 128, 64, 1, 391], [450, 128, 1, 64, 1, 300]),
+                                       ([1100, 70, 600], [1100, 6, 131])])
+@pytest.mark.parametrize("H, Hk, hd, window", [(12, 12, 64, 0), (8, 2, 64, 70), (4, 1, 128, 0),
+                                               (2, 2, 128, 150), (3, 3, 64, 1)])
+def test_tensor_core_prefill_attention(ops, H, Hk, hd, window, lens, new, out_dtype):
+    """The tcgen05 prefill kernel (bf16, head size 64 or 128): chunks of many rows that start
+    anywhere in a page, several 128-row tiles per sequence with a ragged last one, grouped
+    heads, windows that end inside a page, stale data in every page, the pages of a tile cut
+    into one to four runs that are merged (`new` are the rows of this step: the last
+    positions of each sequence); and no wait timed out."""
+    kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, torch.bfloat16, seed=H * 10 + hd + window)
+    entries = [(s + 1, [0] * n, []) for s, n in enumerate(new)]
+    pos0 = [l - n for l, n in zip(lens, new)]
+    lay = build_layout(entries, pos0, DEV, pad_rows_to=8)
+    assert not lay.is_decode
+    torch.manual_seed(6)
+    qkv = torch.randn(lay.n_rows, (H + 2 * Hk) * hd, device=DEV).to(torch.bfloat16)
+    out = torch.full((lay.n_rows, H * hd), 7.0, device=DEV, dtype=out_dtype)
+    scale = 0.6 / math.sqrt(hd)
+    ops.attention(qkv, 0, lay, kv, H, out, scale, window)
+    ops.check_device_errors()
+    r = 0
+    for s, n in enumerate(new):
+        q = qkv[r:r + n, :H * hd].view(n, H, hd).double().cpu()
+        k, v = dk[s].double(), dv[s].double()                     # [len, Hk, hd]
+        qpos = torch.arange(pos0[s], pos0[s] + n)[:, None]
+        key = torch.arange(lens[s])[None, :]
+        vis = key <= qpos
+        if window > 0:
+            vis &= key > qpos - window
+        for h in range(H):
+            sc = (q[:, h] @ k[:, h // (H // Hk)].t()) * scale
+            sc = sc.masked_fill(~vis, float("-inf"))
+            ref = torch.softmax(sc, dim=1) @ v[:, h // (H // Hk)]
+            got = out[r:r + n, h * hd:(h + 1) * hd].double().cpu()
+            err = (got - ref).abs().max(dim=1).values
+            assert err.max() <= 1.5e-2 * max(1.0, float(ref.abs().max())), \
+                f"sequence {s}, head {h}, worst row {int(err.argmax())}"
+        r += n
+    assert (out[r:] == 0).all()                  # padding rows give zeros
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_a_far_key_among_hundreds_is_found(ops, dtype):
     """One key, hundreds of positions back and on another page, is made to dominate."""
