@@ -257,6 +257,35 @@ __global__ void kv_append_kernel(const T* __restrict__ src, int src_stride, int 
   }
 }
 
+// The same in 16-byte pieces (head size, columns and pitch multiples of 16 bytes): a warp takes
+// a row at a time, the lanes its pieces; a block of 8 warps walks over rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_append_vec_kernel(const T* __restrict__ src, int src_stride, int k_col, int v_col,
+                     const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                     NbPagedKV kv, int n_rows) {
+  constexpr int E = 16 / sizeof(T);              // elements per piece
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pieces_per_head = kv.head_dim / E;
+  const int pieces = kv.n_kv_heads * pieces_per_head;   // of K, and as many of V
+  for (int r = blockIdx.x * 8 + warp; r < n_rows; r += gridDim.x * 8) {
+    const int slot = row_slot[r];
+    if (slot < 0) continue;
+    const int pos = row_pos[r];
+    const int page_id = kv.block_table[(size_t)slot * kv.max_pages + pos / kv.page];
+    const int in_page = pos % kv.page;
+    const T* srow = src + (size_t)r * src_stride;
+    for (int i = lane; i < 2 * pieces; i += 32) {
+      const bool is_v = i >= pieces;
+      const int p = is_v ? i - pieces : i;
+      const int h = p / pieces_per_head, c = (p - h * pieces_per_head) * E;
+      const size_t o = (((size_t)page_id * kv.n_kv_heads + h) * kv.page + in_page) * kv.head_dim + c;
+      const uint4 val = *reinterpret_cast<const uint4*>(srow + (is_v ? v_col : k_col) + p * E);
+      *reinterpret_cast<uint4*>((is_v ? (T*)kv.v : (T*)kv.k) + o) = val;
+    }
+  }
+}
+
 NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col, int v_col,
                            const int* row_slot, const int* row_pos, void* k_cache, void* v_cache,
                            const int* block_table, int max_pages, int page, int n_kv_heads,
@@ -265,6 +294,22 @@ NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col
   NbPagedKV kv{k_cache, v_cache, block_table, max_pages, page, n_kv_heads, head_dim};
   const int width = n_kv_heads * head_dim;
   const int threads = width >= 256 ? 256 : (width >= 128 ? 128 : 64);
+  const int esize = dtype == NB_F32 ? 4 : 2, e16 = 16 / esize;
+  const bool vec = (dtype == NB_F32 || dtype == NB_BF16) && head_dim % e16 == 0 &&
+                   src_stride % e16 == 0 && k_col % e16 == 0 && v_col % e16 == 0 &&
+                   (uintptr_t)src % 16 == 0 && (uintptr_t)k_cache % 16 == 0 &&
+                   (uintptr_t)v_cache % 16 == 0;
+  if (vec) {
+    const int blocks = (n_rows + 7) / 8 < 148 * 8 ? (n_rows + 7) / 8 : 148 * 8;
+    if (dtype == NB_F32)
+      kv_append_vec_kernel<float><<<blocks, 256, 0, stream>>>(
+          (const float*)src, src_stride, k_col, v_col, row_slot, row_pos, kv, n_rows);
+    else
+      kv_append_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+          (const __nv_bfloat16*)src, src_stride, k_col, v_col, row_slot, row_pos, kv, n_rows);
+    NB_CHECK_LAUNCH("kv_append");
+    return 0;
+  }
   if (dtype == NB_F32)
     kv_append_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)src, src_stride, k_col,
                                                             v_col, row_slot, row_pos, kv);

@@ -245,22 +245,25 @@ def test_a_far_key_among_hundreds_is_found(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_kv_append_writes_only_its_rows(ops, dtype):
-    Hk, hd = 3, 32
-    lens = [130, 5]
-    kv, dk, dv = _paged_cache(2, lens, Hk, hd, dtype, seed=2)
+@pytest.mark.parametrize("hd", [32, 12])                 # 16-byte pieces / single elements
+def test_kv_append_writes_only_its_rows(ops, dtype, hd):
+    Hk = 3
+    lens = [130, 5, 200]
+    kv, dk, dv = _paged_cache(3, lens, Hk, hd, dtype, seed=2)
     k_before, v_before = kv.k.clone(), kv.v.clone()
-    entries = [(1, [0] * 3, []), (2, [0] * 5, [])]       # positions 127..129 (two pages) and 0..4
-    lay = build_layout(entries, [127, 0], DEV, pad_rows_to=16)
+    # positions 127..129 (two pages), 0..4, and 50..199 (three pages)
+    entries = [(1, [0] * 3, []), (2, [0] * 5, []), (3, [0] * 150, [])]
+    lay = build_layout(entries, [127, 0, 50], DEV, pad_rows_to=16)
     width = 5 * hd + 2 * Hk * hd
     src = torch.randn(lay.n_rows, width, device=DEV).to(dtype)
     ops.kv_append(src, 5 * hd, 5 * hd + Hk * hd, lay.row_slot, lay.row_pos, kv, lay.n_rows)
     expect_k, expect_v = k_before.clone(), v_before.clone()
     r = 0
-    for slot, pos0, n in ((1, 127, 3), (2, 0, 5)):
+    table = kv.block_table.cpu()
+    for slot, pos0, n in ((1, 127, 3), (2, 0, 5), (3, 50, 150)):
         for i in range(n):
             pos = pos0 + i
-            page = int(kv.block_table[slot, pos // PAGE])
+            page = int(table[slot, pos // PAGE])
             expect_k[page, :, pos % PAGE] = src[r, 5 * hd:5 * hd + Hk * hd].view(Hk, hd)
             expect_v[page, :, pos % PAGE] = src[r, 5 * hd + Hk * hd:].view(Hk, hd)
             r += 1
