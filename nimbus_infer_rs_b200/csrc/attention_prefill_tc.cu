@@ -44,19 +44,6 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_b_mn(int m, int n) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
-// A wait for a role that has time: it sleeps between polls, so that it does not take issue
-// slots from the warps that compute.
-__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - start > WAIT_BUDGET) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-  return true;
-}
 // D (tensor memory) = A (tensor memory, bf16 packed two per column) * B (shared memory)
 __device__ __forceinline__ void tc05_mma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
                                                      uint32_t idesc, uint32_t accumulate) {
@@ -129,10 +116,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 buffers + sums][2 halves][128 rows]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // long tiles (late query rows see many keys) are handed out first
-  const int unit = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // CTAs start in the order of their linear index.  That order is made "all heads and
+  // sequences of the last tile, then of the tile before it, ...": the long tiles (late query
+  // rows see many keys) start first, each on an SM of its own, and the short ones fill in
+  // beside them at the end.
+  const int linear = (int)blockIdx.x + (int)gridDim.x * ((int)blockIdx.y + (int)gridDim.y * (int)blockIdx.z);
+  const int per_unit = (int)gridDim.y * (int)gridDim.z;
+  const int unit = (int)gridDim.x - 1 - linear / per_unit;
+  const int h = (linear % per_unit) % (int)gridDim.y, s = (linear % per_unit) / (int)gridDim.y;
   const int tile = unit / max_splits, split = unit % max_splits;
-  const int h = blockIdx.y, s = blockIdx.z;
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   const int q0 = tile * TILE_Q;
   const int slot = seq_slot[s];
@@ -192,7 +184,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const int st = j % L::STAGES;
         const int page_id = next_page;
         if (j + 1 < nb) next_page = table[p_begin + j + 1];
-        ok = mbar_wait_idle(kv_empty(st), ((j / L::STAGES) & 1u) ^ 1u, abort_flag);
+        ok = mbar_wait(kv_empty(st), ((j / L::STAGES) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         mbar_expect_tx(kv_full(st), L::STAGE_BYTES);
         const uint32_t k_dst = kv_smem + st * L::STAGE_BYTES;
@@ -208,7 +200,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     if (lane == 0) {   // ------------------------------------------------------ MMA issuer
       constexpr uint32_t idesc_s = instr_desc_bf16(TILE_Q, PAGE_TOKENS);
       constexpr uint32_t idesc_o = instr_desc_bf16_b_mn(TILE_Q, HD);
-      bool ok = mbar_wait_idle(q_full, 0u, abort_flag);
+      bool ok = mbar_wait(q_full, 0u, abort_flag);
       tc05_fence_after();
       // O_i = P_i V_i: A = the probabilities in tensor memory (16 keys = 8 columns per MMA),
       // B = the page's values, MN-major: 16 keys = two groups of 8 rows.  The MMAs of a CTA run
@@ -216,8 +208,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // score buffer needs no wait of its own.
       auto value_product = [&](int i) -> bool {
         const int b = i & 1, st = i % L::STAGES;
-        if (!mbar_wait_idle(p_full(b), (i >> 1) & 1u, abort_flag)) return false;
-        if (!mbar_wait_idle(o_empty(b), ((i >> 1) & 1u) ^ 1u, abort_flag)) return false;
+        if (!mbar_wait(p_full(b), (i >> 1) & 1u, abort_flag)) return false;
+        if (!mbar_wait(o_empty(b), ((i >> 1) & 1u) ^ 1u, abort_flag)) return false;
         tc05_fence_after();
         const uint32_t v_addr = kv_smem + st * L::STAGE_BYTES + L::K_BYTES;
         const uint32_t a_tmem = tmem_base + L::S_COL + b * PAGE_TOKENS;
@@ -233,7 +225,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       };
       for (int j = 0; j < nb && ok; ++j) {
         const int b = j & 1, st = j % L::STAGES;
-        ok = mbar_wait_idle(kv_full(st), (j / L::STAGES) & 1u, abort_flag);
+        ok = mbar_wait(kv_full(st), (j / L::STAGES) & 1u, abort_flag);
         if (!ok) break;
         tc05_fence_after();
         const uint32_t k_addr = kv_smem + st * L::STAGE_BYTES;
@@ -331,22 +323,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t dn = lo <= 0 ? ~0u : (lo > 31 ? 0u : (~0u << lo));
         vis = up & dn;
       }
+      // The scale is positive (the launcher sees to it), so the maximum is taken over the raw
+      // scores and scaled once, and the scaling of a score is folded into its exponent.
       float x[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (all_visible) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          x[e] = __uint_as_float(v[e]) * sl2;
+          x[e] = __uint_as_float(v[e]);
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          x[e] = ((vis >> e) & 1u) ? __uint_as_float(v[e]) * sl2 : -INFINITY;
+          x[e] = ((vis >> e) & 1u) ? __uint_as_float(v[e]) : -INFINITY;
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
       xch[(b * 2 + half) * TILE_Q + r] = mx;
       pair_barrier();   // also: both halves have read their scores, which the probabilities overwrite
       mx = fmaxf(mx, xch[(b * 2 + (half ^ 1)) * TILE_Q + r]);
@@ -358,7 +352,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t pk[16];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
-        const float p0 = nb_exp2(x[2 * e] - m_use), p1 = nb_exp2(x[2 * e + 1] - m_use);
+        const float p0 = nb_exp2(fmaf(x[2 * e], sl2, -m_use));
+        const float p1 = nb_exp2(fmaf(x[2 * e + 1], sl2, -m_use));
         sum4[e & 3] += p0 + p1;
         const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
         pk[e] = *reinterpret_cast<const uint32_t*>(&hh);
@@ -560,6 +555,8 @@ NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, in
              head_dim, n_heads, n_kv_heads, q_stride);
   NB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535 && n_rows > 0 && n_pages > 0, NB_ERR_UNSUPPORTED,
              "attention_prefill_tc: bad sizes");
+  NB_REQUIRE(scale > 0.0f, NB_ERR_UNSUPPORTED, "attention_prefill_tc: takes a positive scale (got %g)",
+             (double)scale);
   NB_REQUIRE(max_splits >= 1 && chunk_pages >= 1 && (max_splits == 1 || (part && counters)) &&
                  (uintptr_t)part % 16 == 0,
              NB_ERR_BAD_ARG, "attention_prefill_tc: bad split (%d runs of %d pages)", max_splits,

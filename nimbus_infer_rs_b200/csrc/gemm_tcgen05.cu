@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(cta_threads(BN, EPI))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
                     const float* residual, TOut* out, int M, int N, int K, int act, int tiles_n,
-                    int num_tiles) {
+                    int num_tiles, int a_box_bytes) {
   using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
   constexpr int EW = L::EPI_WARPS;
   constexpr int ACC = acc_stride(BN);
@@ -138,7 +138,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t phase = (it / L::STAGES) & 1u;
           ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          // the X box has fewer than 128 rows when the whole product has (see the launcher)
+          mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + L::B_BYTES);
           const uint32_t a_dst = base + s * L::STAGE_BYTES;
           tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
           tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
@@ -410,7 +411,12 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
   static_assert(L::STAGES >= 2, "tile shape leaves no room for a pipeline");
   CUtensorMap mx, mw, mo;
-  int rc = make_map(&mx, X, M, K, BM, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
+  // A product of fewer than 128 rows brings only its rows (in eighths of a tile) into the X
+  // part of a stage: the other rows of the MMA's 128 are whatever shared memory holds, and so
+  // are their results, which no epilogue stores (rows >= M).  Fewer bytes per K block matter:
+  // a single row tile is a stream bound by what one SM can load.
+  const int a_rows = M >= BM ? BM : ((M + 15) / 16) * 16;
+  int rc = make_map(&mx, X, M, K, a_rows, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
   rc = make_map(&mw, W, N, K, BN, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
@@ -440,7 +446,7 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
   kern<<<grid, cta_threads(BN, EPI), smem, stream>>>(mx, mw, mo, bias, residual, (TOut*)out, M, N, K,
-                                                      act, tiles_n, (int)num_tiles);
+                                                      act, tiles_n, (int)num_tiles, a_rows * BK * 2);
   return 0;
 }
 

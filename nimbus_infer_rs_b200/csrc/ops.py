@@ -262,7 +262,7 @@ class CudaBackend:
             return
         if append:
             self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
-        if (not layout.is_decode) and self.use_tcgen05 and self.lib.nb_attention_prefill_tc_supported(
+        if (not layout.is_decode) and self.use_tcgen05 and scale > 0 and self.lib.nb_attention_prefill_tc_supported(
                 dtype_code(q_src.dtype), kv.head_dim, n_heads, kv.n_kv_heads, kv.page,
                 q_src.shape[1], q_col, dtype_code(out.dtype), out.shape[1]):
             # 5th-generation tensor cores, scores in tensor memory

@@ -36,10 +36,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the budget ran out or another role gave up.
+// Bounded wait: false if the budget ran out or another role gave up.  A phase that is already
+// complete costs one try_wait; the clock and the abort flag are looked at once in 32 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
+  uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 31u) != 0u) continue;
     if (*abort_flag) return false;
     if (clock64() - start > WAIT_BUDGET) {
       *abort_flag = 1;

@@ -389,10 +389,12 @@ def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
 @pytest.mark.parametrize("M, N, K", [(65, 64, 8), (128, 128, 64), (129, 200, 72), (300, 2304, 768),
                                      (2048, 768, 3072), (1000, 3072, 768), (256, 50257, 768),
                                      (2048, 96, 320), (4096, 4096, 1600), (77, 1001, 2000),
-                                     (2048, 1536, 256), (640, 800, 128)])
+                                     (2048, 1536, 256), (640, 800, 128),
+                                     (64, 768, 3072), (100, 2304, 768), (17, 776, 520)])
 def test_tensor_core_product(ops, M, N, K):
     """The tcgen05 kernel (bf16, more than 64 rows) against float64: tile edges in M, N and K,
-    all tile widths (64, 96, 128, 192, 256), every epilogue; and no wait may have timed out."""
+    all tile widths (64, 96, 128, 192, 256), every epilogue, products of at most 128 rows (one
+    row tile); and no wait may have timed out."""
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
