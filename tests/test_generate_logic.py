@@ -103,3 +103,29 @@ def test_temperature_sampling_is_seeded_and_independent_of_batch_mates(engine_b)
     assert alone[0] == a[0]                                       # same stream when run alone
     c = engine_b.generate([[5, 6, 7]], SamplingParams(max_new_tokens=5, temperature=0.7, seed=124))
     assert c != alone
+
+
+def test_step_shapes_that_share_a_recording():
+    """The key under which a step's launches are recorded: its numbers of rows, sequences and
+    wanted places, its longest chunk, whether it is one token each, and the power-of-two range
+    of its longest sequence (not its tokens, slots or exact lengths)."""
+    from types import SimpleNamespace
+
+    from nimbus_infer_rs_b200.engine.batch import pack_step
+    from nimbus_infer_rs_b200.engine.step_graphs import StepGraphs, _kv_range
+
+    assert [_kv_range(n, 1024) for n in (1, 64, 65, 128, 129, 1000, 5000)] == \
+        [64, 64, 128, 128, 256, 1024, 1024]
+    g = StepGraphs(SimpleNamespace(spec=SimpleNamespace(max_seq_len=1024, vocab_size=100)))
+    a = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [0, 10])
+    b = pack_step([(5, [9, 9, 9], [0]), (2, [7], [0])], [30, 3])          # other slots, tokens, places
+    c = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [100, 10])        # a longer sequence
+    d = pack_step([(0, [1, 2], [1]), (1, [4, 5], [0])], [0, 10])          # another longest chunk
+    assert g.key(a) == g.key(b) and g.key(a) != g.key(c) and g.key(a) != g.key(d)
+    assert g.kv_bound(c) == 128 and not a.is_decode
+    e = pack_step([(0, [1], [0]), (1, [4], [0])], [70, 10])
+    assert e.is_decode and e.want_all_rows and g.kv_bound(e) == 128
+    # padding rows change the row count, and with it the key, but no sequence's rows
+    p = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [0, 10], pad_rows_to=8)
+    assert p.n_rows == 8 and p.n_tokens == 4 and g.key(p) != g.key(a)
+    assert list(p.buf[p.offs[0]:p.offs[1]]) == [1, 2, 3, 4, -1, -1, -1, -1]
