@@ -4,18 +4,19 @@
 //
 // One CTA takes 128 consecutive query rows of one sequence and one head; a row of the tile is
 // a lane of tensor memory.  Warp 0 is the producer: one thread brings the query tile and then,
-// page by page (64 keys), the page's keys and values into a ring of shared-memory stages with
-// TMA (the cache is [page][kv_head][64][head_dim], so a page of one head is a 64 x head_dim
-// matrix that a tensor map addresses by its first row).  Warp 1 issues the products: S = Q K^T
-// (tcgen05.mma, M=128, N=64, K=head_dim) into one of two score buffers in tensor memory, and
-// O_j = P_j V_j (M=128, N=head_dim, K=64) into one of two output buffers; P_j is read from
-// tensor memory, where the softmax wrote it over the scores it came from, and V is the
-// MN-major operand, straight from its page layout.  Warps 2..9 are the softmax, two threads
-// per row (32 keys and half of the head's columns each): a thread reads its scores with
+// two pages (128 keys) at a time, the pages' keys and values into a ring of shared-memory
+// stages with TMA (the cache is [page][kv_head][64][head_dim], so a page of one head is a
+// 64 x head_dim matrix that a tensor map addresses by its first row).  Warp 1 issues the
+// products: S = Q K^T (tcgen05.mma, M=128, N=128, K=head_dim) into one of two score buffers
+// in tensor memory, and O_j = P_j V_j (M=128, N=head_dim, K=128) into one of two output
+// buffers; P_j is read from tensor memory, where the softmax wrote it over the scores it came
+// from, and V is the MN-major operand, straight from its page layout.  Warps 2..9 are the
+// softmax, two threads per row (one of the two pages and half of the head's columns each; a
+// run of an odd number of pages ends with a half round): a thread reads its scores with
 // tcgen05.ld, applies scale, causal limit and window, keeps the running maximum and sum in
 // fp32, writes the probabilities as bf16 back with tcgen05.st, and adds an earlier page's
-// O_j, rescaled, to its fp32 outputs in registers.  The score product of page j+1 runs while
-// page j is in the softmax.
+// O_j, rescaled, to its fp32 outputs in registers.  The score product of round j+1 runs while
+// round j is in the softmax.
 //
 // Every wait on an mbarrier is bounded by a clock budget; a wait that runs out raises an error
 // flag (nb_attention_prefill_tc_error), all roles leave their loops, and the CTA frees its
@@ -54,12 +55,15 @@ __device__ __forceinline__ void tc05_mma_bf16_a_tmem(uint32_t tmem_d, uint32_t t
       "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
-__device__ __forceinline__ void tc05_st_32x32b_x16(uint32_t taddr, const uint32_t (&v)[16]) {
+__device__ __forceinline__ void tc05_st_32x32b_x32(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, "
+      "%21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
       "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+      "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
 __device__ __forceinline__ void tc05_wait_st() {
@@ -70,23 +74,24 @@ template <int HD>
 struct AttnSmem {
   static constexpr int HB = HD / 64;                      // 64-column boxes per row of a head
   static constexpr int Q_BYTES = TILE_Q * 128 * HB;       // [HB][128 rows][128 B]
-  static constexpr int K_BYTES = PAGE_TOKENS * 128 * HB;  // [HB][64 keys][128 B]
+  static constexpr int PAGE_BOX = PAGE_TOKENS * 128;      // one page, 64 head columns: 8 KB
+  static constexpr int K_BYTES = 2 * PAGE_BOX * HB;       // [HB][2 pages][64 keys][128 B]
   static constexpr int V_BYTES = K_BYTES;
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-  static constexpr int STAGES = 4;   // head size 64: 80 KB a CTA, two CTAs on an SM
+  static constexpr int STAGES = HD == 64 ? 4 : 2;         // 144 KB / 160 KB of tiles
   static constexpr int TILES_BYTES = Q_BYTES + STAGES * STAGE_BYTES;
   // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2]
   static constexpr int N_BARRIERS = 1 + 2 * STAGES + 8;
   static constexpr int XCH_BYTES = 6 * TILE_Q * 4;   // row maxima (two buffers) and sums of the two halves
   static constexpr int TOTAL = TILES_BYTES + N_BARRIERS * 8 + 16 + XCH_BYTES + 1024 /* alignment slack */;
-  // tensor memory columns: two score buffers of 64 (the probabilities of a page take the first
-  // 32 columns of its score buffer), two output buffers of HD
-  static constexpr int S_COL = 0, O_COL = 128;
-  static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;
+  // tensor memory columns: two score buffers of 128 (the probabilities of a round take the
+  // first 64 columns of its score buffer), two output buffers of HD
+  static constexpr int S_COL = 0, O_COL = 256;
+  static constexpr int TMEM_COLS = 512;
 };
 
 template <int HD, typename TOut>
-__global__ void __launch_bounds__(TC_THREADS, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, int q_col,
@@ -141,7 +146,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int n_splits = (p_last - p_first + chunk_pages - 1) / chunk_pages;
   if (split >= n_splits) return;
   const int p_begin = p_first + split * chunk_pages, p_end = min(p_last, p_begin + chunk_pages);
-  const int nb = p_end - p_begin;
+  const int nb = (p_end - p_begin + 1) / 2;             // rounds of two pages
+  // round i takes pages p_begin + 2i and, if it is still in the run, the next one
+  auto two_pages = [&](int i) { return p_begin + 2 * i + 1 < p_end; };
   const int* table = block_table + (size_t)slot * max_pages;
 
   if (tid == 0) {
@@ -179,45 +186,62 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int b = 0; b < HB; ++b)
         tma_load_2d(q_smem + b * (TILE_Q * 128), &map_q, q_col + h * HD + b * 64, row0 + q0, q_full);
       bool ok = true;
-      int next_page = table[p_begin];
+      int next_a = table[p_begin];
+      int next_b = two_pages(0) ? table[p_begin + 1] : 0;
       for (int j = 0; j < nb && ok; ++j) {
         const int st = j % L::STAGES;
-        const int page_id = next_page;
-        if (j + 1 < nb) next_page = table[p_begin + j + 1];
+        const int page_a = next_a, page_b = next_b;
+        const bool two = two_pages(j);
+        if (j + 1 < nb) {
+          next_a = table[p_begin + 2 * j + 2];
+          next_b = two_pages(j + 1) ? table[p_begin + 2 * j + 3] : 0;
+        }
         ok = mbar_wait(kv_empty(st), ((j / L::STAGES) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
-        mbar_expect_tx(kv_full(st), L::STAGE_BYTES);
+        mbar_expect_tx(kv_full(st), two ? L::STAGE_BYTES : L::STAGE_BYTES / 2);
         const uint32_t k_dst = kv_smem + st * L::STAGE_BYTES;
-        const int row = (page_id * n_kv_heads + kvh) * PAGE_TOKENS;
+        const int row_a = (page_a * n_kv_heads + kvh) * PAGE_TOKENS;
+        const int row_b = (page_b * n_kv_heads + kvh) * PAGE_TOKENS;
 #pragma unroll
         for (int b = 0; b < HB; ++b) {
-          tma_load_2d(k_dst + b * (PAGE_TOKENS * 128), &map_k, b * 64, row, kv_full(st));
-          tma_load_2d(k_dst + L::K_BYTES + b * (PAGE_TOKENS * 128), &map_v, b * 64, row, kv_full(st));
+          const uint32_t kb = k_dst + b * (2 * L::PAGE_BOX), vb = kb + L::K_BYTES;
+          tma_load_2d(kb, &map_k, b * 64, row_a, kv_full(st));
+          tma_load_2d(vb, &map_v, b * 64, row_a, kv_full(st));
+          if (two) {
+            tma_load_2d(kb + L::PAGE_BOX, &map_k, b * 64, row_b, kv_full(st));
+            tma_load_2d(vb + L::PAGE_BOX, &map_v, b * 64, row_b, kv_full(st));
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // ------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc_s = instr_desc_bf16(TILE_Q, PAGE_TOKENS);
+      constexpr uint32_t idesc_s2 = instr_desc_bf16(TILE_Q, 2 * PAGE_TOKENS);   // two pages of keys
+      constexpr uint32_t idesc_s1 = instr_desc_bf16(TILE_Q, PAGE_TOKENS);       // one
       constexpr uint32_t idesc_o = instr_desc_bf16_b_mn(TILE_Q, HD);
       bool ok = mbar_wait(q_full, 0u, abort_flag);
       tc05_fence_after();
       // O_i = P_i V_i: A = the probabilities in tensor memory (16 keys = 8 columns per MMA),
-      // B = the page's values, MN-major: 16 keys = two groups of 8 rows.  The MMAs of a CTA run
-      // in the order they were issued, so the score product that later reuses this page's
-      // score buffer needs no wait of its own.
+      // B = the pages' values, MN-major: 16 keys = two groups of 8 rows, the second page 8 KB
+      // after the first, the head's second 64 columns 16 KB on.  The MMAs of a CTA run in the
+      // order they were issued, so the score product that later reuses this round's score
+      // buffer needs no wait of its own.
       auto value_product = [&](int i) -> bool {
         const int b = i & 1, st = i % L::STAGES;
         if (!mbar_wait(p_full(b), (i >> 1) & 1u, abort_flag)) return false;
         if (!mbar_wait(o_empty(b), ((i >> 1) & 1u) ^ 1u, abort_flag)) return false;
         tc05_fence_after();
         const uint32_t v_addr = kv_smem + st * L::STAGE_BYTES + L::K_BYTES;
-        const uint32_t a_tmem = tmem_base + L::S_COL + b * PAGE_TOKENS;
+        const uint32_t a_tmem = tmem_base + L::S_COL + b * (2 * PAGE_TOKENS);
         const uint32_t d_tmem = tmem_base + L::O_COL + b * HD;
+        const int k_steps = two_pages(i) ? 8 : 4;
 #pragma unroll
-        for (int k = 0; k < PAGE_TOKENS / 16; ++k) {
-          const uint64_t db = smem_desc_sw128_mn(v_addr + k * 2048u, PAGE_TOKENS * 128u, 1024u);
-          tc05_mma_bf16_a_tmem(d_tmem, a_tmem + k * 8, db, idesc_o, k > 0 ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) {
+          if (k < k_steps) {
+            const uint64_t db = smem_desc_sw128_mn(v_addr + (k >> 2) * L::PAGE_BOX + (k & 3) * 2048u,
+                                                   2 * L::PAGE_BOX, 1024u);
+            tc05_mma_bf16_a_tmem(d_tmem, a_tmem + k * 8, db, idesc_o, k > 0 ? 1u : 0u);
+          }
         }
         tc05_commit(o_full(b));
         tc05_commit(kv_empty(st));
@@ -229,13 +253,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         tc05_fence_after();
         const uint32_t k_addr = kv_smem + st * L::STAGE_BYTES;
-        const uint32_t d_tmem = tmem_base + L::S_COL + b * PAGE_TOKENS;
+        const uint32_t d_tmem = tmem_base + L::S_COL + b * (2 * PAGE_TOKENS);
+        const uint32_t idesc_s = two_pages(j) ? idesc_s2 : idesc_s1;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           // 16 head columns per MMA: 32 bytes inside a 64-column box, the next box after four
           const uint32_t box = k >> 2, in_box = (k & 3) * 2;
           const uint64_t da = smem_desc_sw128(q_smem + box * (TILE_Q * 128)) + in_box;
-          const uint64_t db = smem_desc_sw128(k_addr + box * (PAGE_TOKENS * 128)) + in_box;
+          const uint64_t db = smem_desc_sw128(k_addr + box * (2 * L::PAGE_BOX)) + in_box;
           tc05_mma_bf16(d_tmem, da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         tc05_commit(s_full(b));
@@ -244,8 +269,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (ok) value_product(nb - 1);
     }
   } else {             // ------------------------------------------------------ softmax
-    // Two threads share a row: the warps 2..5 take the first 32 keys of a page and the first
-    // half of the head's columns, the warps 6..9 the second halves.  The two halves of a row
+    // Two threads share a row: the warps 2..5 take the first page of a round and the first
+    // half of the head's columns, the warps 6..9 the second page and the second half.  The two halves of a row
     // agree on the row's maximum through shared memory once per page (a named barrier of the
     // two warps); each keeps the sum of its own keys, added up at the end.  A thread that has
     // seen a wait run out goes on through the loop without touching tensor memory, so that
@@ -298,45 +323,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
     for (int j = 0; j < nb; ++j) {
       const int b = j & 1;
-      uint32_t v[32];
+      const bool has_keys = half == 0 || two_pages(j);   // a half round has one page only
+      uint32_t v0[32], v1[32];
       if (ok) ok = warp_wait(s_full(b), (j >> 1) & 1u);
-      if (ok) {
+      if (ok && has_keys) {
         tc05_fence_after();
-        tc05_ld_32x32b_x32(lane_addr + L::S_COL + b * PAGE_TOKENS + half * 32, v);
+        tc05_ld_32x32b_x32(lane_addr + L::S_COL + b * (2 * PAGE_TOKENS) + half * PAGE_TOKENS, v0);
+        tc05_ld_32x32b_x32(lane_addr + L::S_COL + b * (2 * PAGE_TOKENS) + half * PAGE_TOKENS + 32, v1);
         tc05_wait_ld();
       } else {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) v[e] = 0u;
+        for (int e = 0; e < 32; ++e) v0[e] = v1[e] = 0u;
       }
 
-      // scale, causal limit, window; the maximum of this thread's 32 keys.  A page that lies
+      // causal limit and window; the maximum of this thread's 64 keys.  A round that lies
       // wholly before the first row of this warp (and needs no window) is visible to all of
       // its rows.  Bit e of `vis`: key k0 + e counts for this row.
-      const int k0 = (p_begin + j) * PAGE_TOKENS + half * 32;
+      const int k0 = (p_begin + 2 * j + half) * PAGE_TOKENS;
       const bool all_visible =
-          window <= 0 && (p_begin + j) * PAGE_TOKENS + PAGE_TOKENS - 1 <= pos0 + q0 + quarter * 32;
-      uint32_t vis = ~0u;
-      if (!all_visible) {
+          window <= 0 && two_pages(j) &&
+          (p_begin + 2 * j + 2) * PAGE_TOKENS - 1 <= pos0 + q0 + quarter * 32;
+      unsigned long long vis = 0ull;
+      if (has_keys) {
         const int hi = qpos - k0;                                   // keys 0..hi are not in the future
         const int lo = window > 0 ? qpos - window + 1 - k0 : 0;     // keys lo.. are inside the window
-        const uint32_t up = hi >= 31 ? ~0u : (hi < 0 ? 0u : ((2u << hi) - 1u));
-        const uint32_t dn = lo <= 0 ? ~0u : (lo > 31 ? 0u : (~0u << lo));
+        const unsigned long long up = hi >= 63 ? ~0ull : (hi < 0 ? 0ull : ((2ull << hi) - 1ull));
+        const unsigned long long dn = lo <= 0 ? ~0ull : (lo > 63 ? 0ull : (~0ull << lo));
         vis = up & dn;
       }
       // The scale is positive (the launcher sees to it), so the maximum is taken over the raw
       // scores and scaled once, and the scaling of a score is folded into its exponent.
-      float x[32];
+      float x[64];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (all_visible) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          x[e] = __uint_as_float(v[e]);
+        for (int e = 0; e < 64; ++e) {
+          x[e] = __uint_as_float(e < 32 ? v0[e] : v1[e - 32]);
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          x[e] = ((vis >> e) & 1u) ? __uint_as_float(v[e]) : -INFINITY;
+        for (int e = 0; e < 64; ++e) {
+          x[e] = ((vis >> e) & 1ull) ? __uint_as_float(e < 32 ? v0[e] : v1[e - 32]) : -INFINITY;
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       }
@@ -349,9 +377,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const float resc = (m_run == -INFINITY) ? 0.0f : nb_exp2(m_run - m_use);
       m_run = m_new;
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t pk[16];
+      uint32_t pk[32];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
+      for (int e = 0; e < 32; ++e) {
         const float p0 = nb_exp2(fmaf(x[2 * e], sl2, -m_use));
         const float p1 = nb_exp2(fmaf(x[2 * e + 1], sl2, -m_use));
         sum4[e & 3] += p0 + p1;
@@ -360,10 +388,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       l_run = fmaf(l_run, resc, (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-      // this thread's probabilities: 32 bf16 = 16 columns of the row, over the scores
+      // this thread's probabilities: 64 bf16 = 32 columns of the row, over the scores
       if (ok) {
-        tc05_st_32x32b_x16(lane_addr + L::S_COL + b * PAGE_TOKENS + half * 16, pk);
-        tc05_wait_st();
+        if (has_keys) {
+          tc05_st_32x32b_x32(lane_addr + L::S_COL + b * (2 * PAGE_TOKENS) + half * 32, pk);
+          tc05_wait_st();
+        }
         tc05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(b));
