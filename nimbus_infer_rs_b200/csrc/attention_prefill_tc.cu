@@ -12,11 +12,11 @@
 // buffers; P_j is read from tensor memory, where the softmax wrote it over the scores it came
 // from, and V is the MN-major operand, straight from its page layout.  Warps 2..9 are the
 // softmax, two threads per row (one of the two pages and half of the head's columns each; a
-// run of an odd number of pages ends with a half round): a thread reads its scores with
+// run of an odd number of pages ends with a turn of one page): a thread reads its scores with
 // tcgen05.ld, applies scale, causal limit and window, keeps the running maximum and sum in
 // fp32, writes the probabilities as bf16 back with tcgen05.st, and adds an earlier page's
-// O_j, rescaled, to its fp32 outputs in registers.  The score product of round j+1 runs while
-// round j is in the softmax.
+// O_j, rescaled, to its fp32 outputs in registers.  The score product of turn j+1 runs while
+// turn j is in the softmax.
 //
 // Every wait on an mbarrier is bounded by a clock budget; a wait that runs out raises an error
 // flag (nb_attention_prefill_tc_error), all roles leave their loops, and the CTA frees its
@@ -84,7 +84,7 @@ struct AttnSmem {
   static constexpr int N_BARRIERS = 1 + 2 * STAGES + 8;
   static constexpr int XCH_BYTES = 6 * TILE_Q * 4;   // row maxima (two buffers) and sums of the two halves
   static constexpr int TOTAL = TILES_BYTES + N_BARRIERS * 8 + 16 + XCH_BYTES + 1024 /* alignment slack */;
-  // tensor memory columns: two score buffers of 128 (the probabilities of a round take the
+  // tensor memory columns: two score buffers of 128 (the probabilities of a turn take the
   // first 64 columns of its score buffer), two output buffers of HD
   static constexpr int S_COL = 0, O_COL = 256;
   static constexpr int TMEM_COLS = 512;
@@ -146,8 +146,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int n_splits = (p_last - p_first + chunk_pages - 1) / chunk_pages;
   if (split >= n_splits) return;
   const int p_begin = p_first + split * chunk_pages, p_end = min(p_last, p_begin + chunk_pages);
-  const int nb = (p_end - p_begin + 1) / 2;             // rounds of two pages
-  // round i takes pages p_begin + 2i and, if it is still in the run, the next one
+  const int nb = (p_end - p_begin + 1) / 2;             // turns of two pages
+  // turn i takes pages p_begin + 2i and, if it is still in the run, the next one
   auto two_pages = [&](int i) { return p_begin + 2 * i + 1 < p_end; };
   const int* table = block_table + (size_t)slot * max_pages;
 
@@ -224,7 +224,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // O_i = P_i V_i: A = the probabilities in tensor memory (16 keys = 8 columns per MMA),
       // B = the pages' values, MN-major: 16 keys = two groups of 8 rows, the second page 8 KB
       // after the first, the head's second 64 columns 16 KB on.  The MMAs of a CTA run in the
-      // order they were issued, so the score product that later reuses this round's score
+      // order they were issued, so the score product that later reuses this turn's score
       // buffer needs no wait of its own.
       auto value_product = [&](int i) -> bool {
         const int b = i & 1, st = i % L::STAGES;
@@ -269,7 +269,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (ok) value_product(nb - 1);
     }
   } else {             // ------------------------------------------------------ softmax
-    // Two threads share a row: the warps 2..5 take the first page of a round and the first
+    // Two threads share a row: the warps 2..5 take the first page of a turn and the first
     // half of the head's columns, the warps 6..9 the second page and the second half.  The two halves of a row
     // agree on the row's maximum through shared memory once per page (a named barrier of the
     // two warps); each keeps the sum of its own keys, added up at the end.  A thread that has
@@ -323,7 +323,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
     for (int j = 0; j < nb; ++j) {
       const int b = j & 1;
-      const bool has_keys = half == 0 || two_pages(j);   // a half round has one page only
+      const bool has_keys = half == 0 || two_pages(j);   // a turn may have one page only
       uint32_t v0[32], v1[32];
       if (ok) ok = warp_wait(s_full(b), (j >> 1) & 1u);
       if (ok && has_keys) {
@@ -336,7 +336,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int e = 0; e < 32; ++e) v0[e] = v1[e] = 0u;
       }
 
-      // causal limit and window; the maximum of this thread's 64 keys.  A round that lies
+      // causal limit and window; the maximum of this thread's 64 keys.  A turn that lies
       // wholly before the first row of this warp (and needs no window) is visible to all of
       // its rows.  Bit e of `vis`: key k0 + e counts for this row.
       const int k0 = (p_begin + 2 * j + half) * PAGE_TOKENS;

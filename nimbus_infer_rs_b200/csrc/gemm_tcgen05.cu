@@ -2,7 +2,7 @@
 // W[N,K]^T + bias) (+ residual), bf16 operands, fp32 accumulation in tensor memory.
 //
 // A CTA computes 128 x BN tiles (BN = 64, 96, 128, 192 or 256, picked so that the tiles fill
-// the SMs in as few rounds as possible), one after another.  Warp 0 is the producer: one thread issues TMA loads of
+// the SMs in as few waves as possible), one after another.  Warp 0 is the producer: one thread issues TMA loads of
 // 128 x 64 (X) and BN x 64 (W) bf16 boxes, 128-byte swizzled, into a ring of shared-memory
 // stages, each guarded by a full/empty mbarrier pair.  Warp 1 owns the tensor memory
 // allocation and one of its threads issues `tcgen05.mma` (M=128, N=BN, K=16; four per stage)
@@ -318,7 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
         }
         const int nb = n0 + c * 32;
-        // bias of the chunk's 32 columns: one load per lane, handed round by shuffles
+        // bias of the chunk's 32 columns: one load per lane, passed on by shuffles
         float bias_l = 0.0f;
         if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
         float f[32];
@@ -453,8 +453,8 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
 // Tile width.  A single row tile (at most 128 rows) is a weight stream: many narrow tiles
 // with a deep ring.  Otherwise every tile re-reads its 128 rows of X and its BN rows of W from
 // L2, so wide tiles win for large products; for products of a few hundred tiles what counts
-// is how many rounds the 148 SMs need and how long a round is, so the width is the one with
-// the least rounds x (width + a tile's fixed cost, about 48 columns' worth of time).  The
+// is how many waves the 148 SMs need and how long a wave is, so the width is the one with
+// the least waves x (width + a tile's fixed cost, about 48 columns' worth of time).  The
 // fp32 TMA epilogue has room for 128 columns at most and alone takes 96; the direct-store
 // epilogue takes 64, 128 and 256.
 int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {

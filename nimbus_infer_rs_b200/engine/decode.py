@@ -49,6 +49,7 @@ class DecodeSession:
         self.logits = None
         self._graph = None
         self._stage = None
+        self._out_stage = None
         self._steps = 0
         if self.params.repetition_penalty != 1.0 or (
                 not self.params.greedy and (self.params.top_k > 0 or self.params.top_p < 1.0)):
@@ -92,7 +93,8 @@ class DecodeSession:
             if self._stage is None:
                 self._stage = torch.empty(self.n, dtype=torch.int32,
                                           pin_memory=eng.rt.device.type == "cuda")
-            self._stage.copy_(torch.as_tensor(tokens, dtype=torch.int32))
+                self._stage_np = self._stage.numpy()      # the same pinned memory
+            self._stage_np[:] = tokens
             self.tokens.copy_(self._stage, non_blocking=True)
         if any(cache.lens[s] % PAGE == 0 or cache.lens[s] + 1 > cache.max_seq_len for s, _ in grow):
             cache.reserve(grow)            # a new page somewhere, or an error to raise
@@ -124,8 +126,16 @@ class DecodeSession:
 
     # ------------------------------------------------------------------ host side
     def read_tokens(self) -> list[int]:
-        """The tokens selected by the last step, on the host (synchronises)."""
-        return self.next_tokens.to("cpu").tolist()
+        """The tokens selected by the last step, on the host (waits for the step): one copy
+        into pinned memory on the step's stream, then a wait for that stream."""
+        if self.next_tokens.device.type != "cuda":
+            return self.next_tokens.tolist()
+        if self._out_stage is None:
+            self._out_stage = torch.empty(self.n, dtype=torch.int32, pin_memory=True)
+            self._out_np = self._out_stage.numpy()
+        self._out_stage.copy_(self.next_tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_np.tolist()
 
     def retire(self, index: int) -> None:
         """Sequence ``index`` of the session has ended: its row becomes padding."""
