@@ -262,3 +262,24 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_and_change_nothing(model
             assert_close(out, want, dtype, f"decode step {t}")
     assert e.step_graphs.replays >= 2 + n_dec - 4 and plain.step_graphs.replays == 0
     e.ops.check_device_errors()
+
+
+def test_recorded_steps_are_dropped_least_recently_used_first(model_dirs):
+    """With room for one recording, two shapes taking turns are recorded again and again and
+    still give what the plain launches give."""
+    e = _engine(model_dirs, "A", "bfloat16", n_slots=4)
+    plain = _engine(model_dirs, "A", "bfloat16", n_slots=4)
+    e.step_graphs.capacity = 1
+    plain.step_graphs.capacity = 0
+    V = e.spec.vocab_size
+    for r in range(6):
+        n = 9 if r % 2 == 0 else 14                       # two shapes, alternating
+        toks = random_tokens(V, n, seed=200 + r)
+        for eng in (e, plain):
+            eng._s = eng.alloc_slot()
+        out, ref = e.step([(e._s, toks, [n - 1])]), plain.step([(plain._s, toks, [n - 1])])
+        assert torch.equal(out, ref)
+        assert_close(out, plain_logits(model_dirs["A"], toks)[-1:], "bfloat16", f"step {r}")
+        for eng in (e, plain):
+            eng.free_slot(eng._s)
+    assert len(e.step_graphs._graphs) == 1 and e.step_graphs.captures >= 3
