@@ -10,7 +10,11 @@
 // products: S = Q K^T (tcgen05.mma, M=128, N=128, K=head_dim) into one of two score buffers
 // in tensor memory, and O_j = P_j V_j (M=128, N=head_dim, K=128) into one of two output
 // buffers; P_j is read from tensor memory, where the softmax wrote it over the scores it came
-// from, and V is the MN-major operand, straight from its page layout.  Warps 2..9 are the
+// from, and V is the MN-major operand, straight from its page layout.  With `append`, the
+// step's own keys and values are not in the cache yet: pages at or after a sequence's cached
+// length (a multiple of the page size) are read from the step's rows instead, and the CTA
+// whose query rows a page belongs to copies it from shared memory into the cache with a TMA
+// store (one CTA per key/value head).  Warps 2..9 are the
 // softmax, two threads per row (one of the two pages and half of the head's columns each; a
 // run of an odd number of pages ends with a turn of one page): a thread reads its scores with
 // tcgen05.ld, applies scale, causal limit and window, keeps the running maximum and sum in
@@ -94,7 +98,9 @@ template <int HD, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, int q_col,
+                            const __grid_constant__ CUtensorMap map_v,
+                            const __grid_constant__ CUtensorMap map_new, int append, int k_col,
+                            int v_col, int q_col,
                             const int* __restrict__ cu_rows, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_pos0, const int* __restrict__ block_table,
                             int max_pages, int n_kv_heads, int group, TOut* __restrict__ out,
@@ -186,6 +192,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int b = 0; b < HB; ++b)
         tma_load_2d(q_smem + b * (TILE_Q * 128), &map_q, q_col + h * HD + b * 64, row0 + q0, q_full);
       bool ok = true;
+      // keys and values of page p of the sequence, 64 head columns at a time: from the cache,
+      // or (append) from the step's own rows when the page lies at or after the cached length
+      auto load_page = [&](int p, int page_id, uint32_t kb, uint32_t vb, int b, uint32_t bar) {
+        if (append && p * PAGE_TOKENS >= pos0) {
+          const int row = row0 + p * PAGE_TOKENS - pos0;
+          tma_load_2d(kb, &map_new, k_col + kvh * HD + b * 64, row, bar);
+          tma_load_2d(vb, &map_new, v_col + kvh * HD + b * 64, row, bar);
+        } else {
+          const int row = (page_id * n_kv_heads + kvh) * PAGE_TOKENS;
+          tma_load_2d(kb, &map_k, b * 64, row, bar);
+          tma_load_2d(vb, &map_v, b * 64, row, bar);
+        }
+      };
+      // (append) a page of this tile's own query rows goes from shared memory into the cache
+      const bool writer = append && (h % group == 0);
+      bool stored = false;
+      auto store_page = [&](int p, int page_id, uint32_t kb, uint32_t vb, int b) {
+        if (p * PAGE_TOKENS < pos0 + q0) return;
+        const int row = (page_id * n_kv_heads + kvh) * PAGE_TOKENS;
+        tma_store_2d(&map_k, kb, b * 64, row);
+        tma_store_2d(&map_v, vb, b * 64, row);
+        stored = true;
+      };
       int next_a = table[p_begin];
       int next_b = two_pages(0) ? table[p_begin + 1] : 0;
       for (int j = 0; j < nb && ok; ++j) {
@@ -200,19 +229,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         mbar_expect_tx(kv_full(st), two ? L::STAGE_BYTES : L::STAGE_BYTES / 2);
         const uint32_t k_dst = kv_smem + st * L::STAGE_BYTES;
-        const int row_a = (page_a * n_kv_heads + kvh) * PAGE_TOKENS;
-        const int row_b = (page_b * n_kv_heads + kvh) * PAGE_TOKENS;
+        const int pa = p_begin + 2 * j;
 #pragma unroll
         for (int b = 0; b < HB; ++b) {
           const uint32_t kb = k_dst + b * (2 * L::PAGE_BOX), vb = kb + L::K_BYTES;
-          tma_load_2d(kb, &map_k, b * 64, row_a, kv_full(st));
-          tma_load_2d(vb, &map_v, b * 64, row_a, kv_full(st));
-          if (two) {
-            tma_load_2d(kb + L::PAGE_BOX, &map_k, b * 64, row_b, kv_full(st));
-            tma_load_2d(vb + L::PAGE_BOX, &map_v, b * 64, row_b, kv_full(st));
+          load_page(pa, page_a, kb, vb, b, kv_full(st));
+          if (two) load_page(pa + 1, page_b, kb + L::PAGE_BOX, vb + L::PAGE_BOX, b, kv_full(st));
+        }
+        if (writer && (pa + (two ? 2 : 1)) * PAGE_TOKENS > pos0 + q0) {
+          // the tile's own pages are the last it reads: their stages are not filled again
+          ok = mbar_wait(kv_full(st), (j / L::STAGES) & 1u, abort_flag);
+          if (!ok) break;
+#pragma unroll
+          for (int b = 0; b < HB; ++b) {
+            const uint32_t kb = k_dst + b * (2 * L::PAGE_BOX), vb = kb + L::K_BYTES;
+            store_page(pa, page_a, kb, vb, b);
+            if (two) store_page(pa + 1, page_b, kb + L::PAGE_BOX, vb + L::PAGE_BOX, b);
           }
+          bulk_commit();
         }
       }
+      if (stored) bulk_wait_all();   // the stores have left shared memory and reached the cache
     }
   } else if (warp == 1) {
     if (lane == 0) {   // ------------------------------------------------------ MMA issuer
@@ -511,15 +548,18 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
               const int* seq_slot, const int* seq_pos0, const void* k_cache, const void* v_cache,
               long long n_pages, const int* block_table, int max_pages, int n_heads, int n_kv_heads,
               void* out, int out_stride, float scale, int window, int n_seqs, int max_q_len,
-              int max_splits, int chunk_pages, float* part, int* counters, cudaStream_t stream) {
+              int max_splits, int chunk_pages, float* part, int* counters, int append, int k_col,
+              int v_col, cudaStream_t stream) {
   using L = AttnSmem<HD>;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mn;
   int rc = make_map(&mq, q, n_rows, q_stride, TILE_Q, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
   const long long kv_rows = n_pages * n_kv_heads * PAGE_TOKENS;
   rc = make_map(&mk, k_cache, kv_rows, HD, PAGE_TOKENS, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
   rc = make_map(&mv, v_cache, kv_rows, HD, PAGE_TOKENS, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
+  if (rc) return rc;
+  rc = make_map(&mn, q, n_rows, q_stride, PAGE_TOKENS, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
   auto kern = attention_prefill_tc_kernel<HD, TOut>;
   static bool configured = false;   // per instantiation
@@ -528,7 +568,7 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
     configured = true;
   }
   dim3 grid(((max_q_len + TILE_Q - 1) / TILE_Q) * max_splits, n_heads, n_seqs);
-  kern<<<grid, TC_THREADS, L::TOTAL, stream>>>(mq, mk, mv, q_col, cu_rows, seq_slot, seq_pos0,
+  kern<<<grid, TC_THREADS, L::TOTAL, stream>>>(mq, mk, mv, mn, append, k_col, v_col, q_col, cu_rows, seq_slot, seq_pos0,
                                                block_table, max_pages, n_kv_heads,
                                                n_heads / n_kv_heads, (TOut*)out, out_stride, scale,
                                                window, max_splits, chunk_pages, part, counters);
@@ -569,6 +609,9 @@ NB_EXPORT int nb_attention_prefill_tc_record(int head_dim) { return 2 * TILE_Q +
 // runs of chunk_pages (max_splits * chunk_pages must cover the longest sequence); it needs
 // `part` (n_seqs * n_heads * tiles * max_splits records) and `counters` (one int per
 // (sequence, head, tile), zero before the first use; every launch leaves them at zero).
+// append != 0: the rows also hold the step's keys and values at columns k_col / v_col (key/value
+// head after head); every seq_pos0 must then be a multiple of the page size, and the kernel
+// writes them to the cache itself.
 NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, int q_col, int n_rows,
                                       const int* cu_rows, const int* seq_slot, const int* seq_pos0,
                                       const void* k_cache, const void* v_cache, int n_pages,
@@ -576,7 +619,8 @@ NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, in
                                       int n_kv_heads, int head_dim, void* out, int out_dtype,
                                       int out_stride, float scale, int window, int n_seqs,
                                       int max_q_len, int max_splits, int chunk_pages, float* part,
-                                      int* counters, cudaStream_t stream) {
+                                      int* counters, int append, int k_col, int v_col,
+                                      cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   NB_REQUIRE(nb_attention_prefill_tc_supported(dtype, head_dim, n_heads, n_kv_heads, page, q_stride,
                                                q_col, out_dtype, out_stride),
@@ -585,6 +629,9 @@ NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, in
              head_dim, n_heads, n_kv_heads, q_stride);
   NB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535 && n_rows > 0 && n_pages > 0, NB_ERR_UNSUPPORTED,
              "attention_prefill_tc: bad sizes");
+  NB_REQUIRE(!append || (k_col % 8 == 0 && v_col % 8 == 0 && k_col >= 0 && v_col >= 0),
+             NB_ERR_UNSUPPORTED, "attention_prefill_tc: key/value columns %d/%d are not 16-byte aligned",
+             k_col, v_col);
   NB_REQUIRE(scale > 0.0f, NB_ERR_UNSUPPORTED, "attention_prefill_tc: takes a positive scale (got %g)",
              (double)scale);
   NB_REQUIRE(max_splits >= 1 && chunk_pages >= 1 && (max_splits == 1 || (part && counters)) &&
@@ -597,7 +644,7 @@ NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, in
                  (uintptr_t)out % 16 == 0,
              NB_ERR_UNSUPPORTED, "attention_prefill_tc: operands must be 16-byte aligned");
   int rc = NB_ERR_UNSUPPORTED;
-#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, window, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, stream
+#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, window, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, append, k_col, v_col, stream
   if (head_dim == 64)
     rc = out_dtype == NB_F32 ? launch_tc<64, float>(NB_ARGS) : launch_tc<64, bf16>(NB_ARGS);
   else

@@ -235,8 +235,9 @@ class CudaBackend:
     def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
         """Causal attention of the packed rows of ``layout`` over the cache ``kv``.
         ``append=(k_col, v_col)``: the rows of ``q_src`` also hold this step's keys and values
-        at those columns; they are written to the cache first (inside the decode kernel, or by
-        a pass of their own before the other kernels)."""
+        at those columns; they are written to the cache as well (inside the decode kernel and,
+        for sequences that start at a page boundary, inside the tensor-core prefill kernel;
+        else by a pass of their own before the attention kernel)."""
         _check(q_src, "q", kv.k.dtype, 2)
         _check(out, "out", None, 2)
         n_rows = layout.n_rows
@@ -260,12 +261,17 @@ class CudaBackend:
                        (append[0] if append else 0), (append[1] if append else 0),
                        self._stream())
             return
-        if append:
-            self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
         if (not layout.is_decode) and self.use_tcgen05 and scale > 0 and self.lib.nb_attention_prefill_tc_supported(
                 dtype_code(q_src.dtype), kv.head_dim, n_heads, kv.n_kv_heads, kv.page,
                 q_src.shape[1], q_col, dtype_code(out.dtype), out.shape[1]):
-            # 5th-generation tensor cores, scores in tensor memory
+            # 5th-generation tensor cores, scores in tensor memory.  When every sequence's cached
+            # length is a whole number of pages (prompts from their first token, chunks cut at
+            # page ends) the kernel reads the step's keys and values from the step's rows and
+            # writes them to the cache itself; else they are appended first.
+            fused = bool(append) and append[0] % 8 == 0 and append[1] % 8 == 0 and \
+                all(p % kv.page == 0 for p in layout.seq_pos0_host)
+            if append and not fused:
+                self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
             if layout.n_rows > layout.n_tokens:
                 out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
             # A CTA takes a 128-row tile of one head.  When there are too few of them to fill
@@ -289,8 +295,11 @@ class CudaBackend:
                        kv.k.shape[0], _ptr(kv.block_table), kv.block_table.shape[1], kv.page,
                        n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out), dtype_code(out.dtype),
                        out.shape[1], scale, window, layout.n_seqs, layout.max_q_len,
-                       max_splits, chunk, _ptr(part), _ptr(counters), self._stream())
+                       max_splits, chunk, _ptr(part), _ptr(counters), 1 if fused else 0,
+                       append[0] if fused else 0, append[1] if fused else 0, self._stream())
             return
+        if append:
+            self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
         if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
                 (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
                 (kv.n_kv_heads), (kv.page), (q_src.shape[1]), (q_col)):

@@ -17,7 +17,7 @@ SIGNATURES = {
     "nb_attention_prefill": "piiippppppiiiiipiifiiip",
     "nb_attention_prefill_tc_supported": "iiiiiiiii",
     "nb_attention_prefill_tc_error": "",
-    "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippp",
+    "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippiiip",
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",

@@ -49,8 +49,12 @@ class StepGraphs:
         return _kv_range(p.max_kv_len, self.engine.spec.max_seq_len)
 
     def key(self, p: PackedStep):
+        # whether every sequence starts at a page boundary decides which kernels append keys
+        # and values, so it is part of the shape
+        from ..cache.paged import PAGE
+        aligned = all(q % PAGE == 0 for q in p.seq_pos0_host)
         return (p.n_rows, p.n_seqs, p.n_want, p.max_q_len, p.is_decode, p.want_all_rows,
-                self.kv_bound(p))
+                self.kv_bound(p), aligned)
 
     def run(self, p: PackedStep):
         """Run the step by replay if its shape has a graph (recording one if it is due);

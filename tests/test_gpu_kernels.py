@@ -226,6 +226,63 @@ def test_tensor_core_prefill_attention(ops, H, Hk, hd, window, lens, new, out_dt
     assert (out[r:] == 0).all()                  # padding rows give zeros
 
 
+@pytest.mark.parametrize("H, Hk, hd, window", [(12, 12, 64, 0), (8, 2, 64, 100), (4, 2, 128, 0)])
+def test_tensor_core_prefill_attention_appends_its_own_keys_and_values(ops, H, Hk, hd, window):
+    """Sequences whose cached length is a whole number of pages (0, 64, 192): the kernel must
+    read the step's keys and values from the step's rows, not from the cache (which holds
+    other data there), give what append-then-attend gives, and leave the same cache behind."""
+    lens = [450, 128, 64 + 70, 192 + 300, 1]
+    pos0 = [0, 0, 64, 192, 0]
+    new = [l - p for l, p in zip(lens, pos0)]
+    kv_true, dk, dv = _paged_cache(len(lens), lens, Hk, hd, torch.bfloat16, seed=H + hd + window)
+    k_stale, v_stale = kv_true.k.clone(), kv_true.v.clone()
+    table = kv_true.block_table.cpu()
+    for s, (l, p) in enumerate(zip(lens, pos0)):          # spoil the cache where new tokens go
+        for pos in range(p, l):
+            page = int(table[s + 1, pos // PAGE])
+            k_stale[page, :, pos % PAGE] = 9.0
+            v_stale[page, :, pos % PAGE] = -9.0
+    kv = LayerKV(k_stale, v_stale, kv_true.block_table, PAGE, Hk, hd)
+    entries = [(s + 1, [0] * n, []) for s, n in enumerate(new)]
+    lay = build_layout(entries, pos0, DEV, pad_rows_to=8)
+    torch.manual_seed(7)
+    qw, kw = H * hd, Hk * hd
+    qkv = torch.randn(lay.n_rows, qw + 2 * kw, device=DEV).to(torch.bfloat16)
+    r = 0
+    for s, n in enumerate(new):                            # the step's own keys and values
+        qkv[r:r + n, qw:qw + kw] = dk[s][pos0[s]:].reshape(n, kw).to(DEV)
+        qkv[r:r + n, qw + kw:] = dv[s][pos0[s]:].reshape(n, kw).to(DEV)
+        r += n
+    out = torch.full((lay.n_rows, qw), 7.0, device=DEV, dtype=torch.bfloat16)
+    scale = 0.6 / math.sqrt(hd)
+    launches = ops.launches
+    ops.attention(qkv, 0, lay, kv, H, out, scale, window, (qw, qw + kw))
+    assert ops.launches == launches + 1                    # no pass of its own for the append
+    ops.check_device_errors()
+    r = 0
+    for s, n in enumerate(new):
+        q = qkv[r:r + n, :qw].view(n, H, hd).double().cpu()
+        k, v = dk[s].double(), dv[s].double()
+        qpos = torch.arange(pos0[s], pos0[s] + n)[:, None]
+        key = torch.arange(lens[s])[None, :]
+        vis = key <= qpos
+        if window > 0:
+            vis &= key > qpos - window
+        for h in range(H):
+            sc = (q[:, h] @ k[:, h // (H // Hk)].t()) * scale
+            ref = torch.softmax(sc.masked_fill(~vis, float("-inf")), dim=1) @ v[:, h // (H // Hk)]
+            got = out[r:r + n, h * hd:(h + 1) * hd].double().cpu()
+            err = (got - ref).abs().max(dim=1).values
+            assert err.max() <= 1.5e-2 * max(1.0, float(ref.abs().max())), \
+                f"sequence {s}, head {h}, worst row {int(err.argmax())}"
+        # every token of the sequence is in the cache now, bit for bit
+        for pos in range(lens[s]):
+            page = int(table[s + 1, pos // PAGE])
+            assert torch.equal(kv.k[page, :, pos % PAGE], kv_true.k[page, :, pos % PAGE]), (s, pos)
+            assert torch.equal(kv.v[page, :, pos % PAGE], kv_true.v[page, :, pos % PAGE]), (s, pos)
+        r += n
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_a_far_key_among_hundreds_is_found(ops, dtype):
     """One key, hundreds of positions back and on another page, is made to dominate."""
