@@ -21,6 +21,7 @@ actually holds, so many sequences of unequal length share the memory.
 """
 from __future__ import annotations
 
+import heapq
 from dataclasses import dataclass
 
 import numpy as np
@@ -49,9 +50,12 @@ class LayerKV:
 
 
 class PagePool:
+    """Free pages are handed out lowest number first (a heap): the pages a prompt takes in one
+    go are then neighbours in memory, also after many batches have come and gone."""
+
     def __init__(self, n_pages: int):
         self.n_pages = int(n_pages)
-        self._free = list(range(self.n_pages - 1, -1, -1))
+        self._free = list(range(self.n_pages))      # a heap: sorted lists are heaps
         self._held: set[int] = set()
 
     @property
@@ -62,7 +66,7 @@ class PagePool:
         if n > len(self._free):
             raise CacheError(f"cache is full: {n} pages wanted, {len(self._free)} free "
                              f"of {self.n_pages}")
-        out = [self._free.pop() for _ in range(n)]
+        out = [heapq.heappop(self._free) for _ in range(n)]
         self._held.update(out)
         return out
 
@@ -71,7 +75,7 @@ class PagePool:
             if p not in self._held:
                 raise CacheError(f"page {p} is not held (released twice)")
             self._held.remove(p)
-            self._free.append(p)
+            heapq.heappush(self._free, p)
 
 
 class CacheGroup:
