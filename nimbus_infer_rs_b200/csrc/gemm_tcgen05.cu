@@ -46,10 +46,12 @@ __device__ int g_error_flag = 0;
 // tile overlap the main loop of the next.  EPI 1 adds a staging area for the epilogue: 4 KB
 // (32 rows x 128 bytes, 128-byte swizzled) per epilogue warp for bf16 output, twice that for
 // fp32 output (two 32-column boxes per warp, which also receive the residual by TMA).
-template <int BN, int EPI, int ESIZE>
+// PAIR 1: two CTAs of a cluster share 256 x BN tiles (`cta_group::2`): each brings its 128
+// rows of X and half of the tile's rows of W, so a stage holds BN / 2 rows of W.
+template <int BN, int EPI, int ESIZE, int PAIR>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_WARPS = epi_warps(BN, EPI);
   static constexpr int STG_PER_WARP = EPI ? (ESIZE == 4 ? 8192 : 4096) : 0;
@@ -64,15 +66,16 @@ struct SmemLayout {
   static constexpr int TOTAL = TILES_BYTES + STG_BYTES + N_BARRIERS * 8 + 16 + 1024 /* alignment slack */;
 };
 
-template <int BN, int EPI, typename TOut>
+template <int BN, int EPI, typename TOut, int PAIR>
 __global__ void __launch_bounds__(cta_threads(BN, EPI))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
                     const float* residual, TOut* out, int M, int N, int K, int act, int tiles_n,
                     int num_tiles, int a_box_bytes) {
-  using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
+  using L = SmemLayout<BN, EPI, (int)sizeof(TOut), PAIR>;
   constexpr int EW = L::EPI_WARPS;
   constexpr int ACC = acc_stride(BN);
+  static_assert(!PAIR || (EPI == 1 && BN % 32 == 0), "paired CTAs: TMA epilogue only");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
   static_assert(EPI == 1 || BN == 64 || BN == 128 || BN == 256, "direct-store epilogue: 64/128/256");
   static_assert(BN % 64 == 0 || (EPI == 1 && sizeof(TOut) == 4), "odd widths: fp32 TMA epilogue only");
@@ -94,6 +97,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int num_kb = (K + BK - 1) / BK;
+  // Paired CTAs: rank 0 is the leader.  It alone issues the MMAs (which read both CTAs'
+  // shared memory and write both CTAs' tensor memory); the TMA loads of both CTAs count on the
+  // leader's full barriers; commits go to the barriers of both; the epilogue warps of both tell
+  // the leader's accumulator-empty barriers.
+  uint32_t rank = 0;
+  if constexpr (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+  const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;    // who walks over tiles
+  const int n_walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int m_off = PAIR ? (int)rank * BM : 0;                   // this CTA's rows in a tile
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;
 
   if (tid == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -102,7 +115,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), EW);   // one arrival per epilogue warp
+      mbar_init(acc_empty(b), PAIR ? 2 * EW : EW);   // one arrival per epilogue warp (of both CTAs)
     }
     for (int w = 0; w < EW; ++w) {
       mbar_init(res_bar(w, 0), 1);
@@ -112,12 +125,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
+  if constexpr (PAIR) {   // the peer's barriers exist before anything of ours can reach them
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  }
   if (warp == 1) {   // the whole warp allocates two accumulators, ACC columns apart
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"((uint32_t)(2 * ACC))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    if constexpr (PAIR) {   // warp 1 of both CTAs, the same columns in both
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                       smem_u32(tmem_slot)),
+                   "r"((uint32_t)(2 * ACC))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                       smem_u32(tmem_slot)),
+                   "r"((uint32_t)(2 * ACC))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
   }
   tc05_fence_before();
   __syncthreads();
@@ -131,27 +156,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (lane == 0) {   // ---------------------------------------------------- TMA producer
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      for (int tile = walker; tile < num_tiles && ok; tile += n_walkers) {
+        const int m0 = (tile / tiles_n) * TILE_M + m_off;
+        const int n0 = (tile % tiles_n) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t phase = (it / L::STAGES) & 1u;
           ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
           if (!ok) break;
-          // the X box has fewer than 128 rows when the whole product has (see the launcher)
-          mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + L::B_BYTES);
           const uint32_t a_dst = base + s * L::STAGE_BYTES;
-          tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
-          tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier, which the leader arms
+            if (rank == 0) mbar_expect_tx(full_bar(s), 2u * ((uint32_t)a_box_bytes + L::B_BYTES));
+            const uint32_t lead_bar = cluster_addr(full_bar(s), 0);
+            tma_load_2d_pair(a_dst, &map_x, kb * BK, m0, lead_bar);
+            tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, kb * BK, n0, lead_bar);
+          } else {
+            // the X box has fewer than 128 rows when the whole product has (see the launcher)
+            mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + L::B_BYTES);
+            tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
+            tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {   // ---------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+    if (lane == 0 && rank == 0) {   // ------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = instr_desc_bf16(TILE_M, BN);
       uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      for (int tile = walker; tile < num_tiles && ok; tile += n_walkers, ++t) {
         const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
         ok = mbar_wait(acc_empty(ab), aphase ^ 1u, abort_flag);   // the epilogue has drained it
         if (!ok) break;
@@ -169,12 +203,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K by 16 elements inside the swizzle atom = 32 bytes = 2 address units
-            tc05_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                          (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (PAIR)
+              tc05_mma_bf16_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+            else
+              tc05_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                            (kb > 0 || k > 0) ? 1u : 0u);
           }
-          tc05_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+          // the stage is free (in both CTAs) once these MMAs have read it
+          if constexpr (PAIR) tc05_commit_pair(empty_bar(s)); else tc05_commit(empty_bar(s));
         }
-        if (ok) tc05_commit(acc_full(ab));   // complete once all MMAs issued so far are done
+        // complete once all MMAs issued so far are done
+        if (ok) { if constexpr (PAIR) tc05_commit_pair(acc_full(ab)); else tc05_commit(acc_full(ab)); }
       }
     }
   } else if constexpr (EPI == 1) {   // ---------- epilogue through shared memory and TMA stores
@@ -193,8 +233,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t my_row = stg + (uint32_t)lane * 128u;
     const uint32_t swz = (uint32_t)(lane & 7);
     uint32_t t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    const uint32_t lead_empty0 = PAIR ? cluster_addr(acc_empty(0), 0) : 0u;
+    for (int tile = walker; tile < num_tiles; tile += n_walkers, ++t) {
+      const int m0 = (tile / tiles_n) * TILE_M + m_off, n0 = (tile % tiles_n) * BN;
       const int row0 = m0 + quarter * 32, col0 = n0 + unit * 64;
       const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
       if (lane == 0) {
@@ -220,8 +261,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (c == nch - 1) {   // this warp has read its share of the accumulator: hand it back
           tc05_fence_before();
           __syncwarp();
-          if (lane == 0)
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
+          if (lane == 0) {
+            if constexpr (PAIR)
+              asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(
+                               lead_empty0 + 8u * ab)
+                           : "memory");
+            else
+              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
+          }
         }
         const int nb = col0 + c * 32;
         float bias_l = 0.0f;
@@ -396,19 +443,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     __syncthreads();
   }
+  if constexpr (PAIR) {   // neither CTA leaves while the other may still reach into it
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  }
   if (warp == 1) {
     tc05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
-                 "r"((uint32_t)(2 * ACC))
-                 : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
+                   "r"((uint32_t)(2 * ACC))
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
+                   "r"((uint32_t)(2 * ACC))
+                   : "memory");
   }
 }
 
 // ---------------------------------------------------------------------------------- host
-template <int BN, int EPI, typename TOut>
+template <int BN, int EPI, typename TOut, int PAIR = 0>
 int launch(const void* X, const void* W, const float* bias, const float* residual, void* out, int M,
            int N, int K, int act, cudaStream_t stream) {
-  using L = SmemLayout<BN, EPI, (int)sizeof(TOut)>;
+  using L = SmemLayout<BN, EPI, (int)sizeof(TOut), PAIR>;
   static_assert(L::STAGES >= 2, "tile shape leaves no room for a pipeline");
   CUtensorMap mx, mw, mo;
   // A product of fewer than 128 rows brings only its rows (in eighths of a tile) into the X
@@ -418,7 +474,7 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   const int a_rows = M >= BM ? BM : ((M + 15) / 16) * 16;
   int rc = make_map(&mx, X, M, K, a_rows, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, BN, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
+  rc = make_map(&mw, W, N, K, PAIR ? BN / 2 : BN, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
   if (EPI) {
     rc = sizeof(TOut) == 4
@@ -428,21 +484,41 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   } else {
     mo = mx;   // unused
   }
-  auto kern = gemm_tcgen05_kernel<BN, EPI, TOut>;
+  auto kern = gemm_tcgen05_kernel<BN, EPI, TOut, PAIR>;
   const int smem = L::TOTAL;
   static bool configured = false;   // per instantiation
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const long long num_tiles = (long long)tiles_n * ((M + BM - 1) / BM);
+  const long long num_tiles = (long long)tiles_n * ((M + TILE_M - 1) / TILE_M);
   NB_REQUIRE(num_tiles < (1ll << 31), NB_ERR_UNSUPPORTED, "gemm_tcgen05: too many tiles");
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
     NB_CUDA(cudaGetDevice(&dev));
     NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if constexpr (PAIR) {
+    // clusters of two CTAs, one cluster per pair of SMs
+    const int pairs = (int)(num_tiles < sms / 2 ? num_tiles : sms / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(cta_threads(BN, EPI));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
+                               (int)num_tiles, a_rows * BK * 2));
+    return 0;
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
   kern<<<grid, cta_threads(BN, EPI), smem, stream>>>(mx, mw, mo, bias, residual, (TOut*)out, M, N, K,
@@ -482,12 +558,56 @@ int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {
   return best;
 }
 
+// Off by default: measured on GPT-2 124M and XL prefill (2 x 1024 tokens) the paired tiles are
+// no faster than single CTAs (1.26 against 1.21 ms, 10.3 against 10.3 ms): the products are a
+// wave or two of tiles, and the cluster's start-up and its barriers cost what the lighter
+// loads save.
+int g_use_pairs = 0;   // 0 off, 1 where the cost model prefers them, 2 wherever a paired kernel exists
+
+// Width of 256-row tiles for pairs of CTAs, or 0 if single CTAs with `single_bn` are better.
+// Cost of a shape: waves over the SMs (or pairs of SMs) x what a CTA brings in per K block
+// (its rows of X, its rows of W) plus a tile's fixed cost, all in rows of 128 bytes.
+int pick_pair_width(int M, int N, bool f32_out, int single_bn) {
+  if (M <= BM) return 0;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const long long fixed = 64;
+  const long long tiles1 = (long long)((M + BM - 1) / BM) * ((N + single_bn - 1) / single_bn);
+  long long best_cost = g_use_pairs >= 2 ? (1ll << 60)
+                                         : ((tiles1 + sms - 1) / sms) * (BM + single_bn + fixed);
+  int best = 0;
+  const int cand_f32[] = {128, 96}, cand_bf16[] = {256, 192, 128};
+  const int* cand = f32_out ? cand_f32 : cand_bf16;
+  const int n_cand = f32_out ? 2 : 3;
+  const int pairs = sms / 2;
+  for (int i = 0; i < n_cand; ++i) {
+    const int bn = cand[i];
+    if (N < bn && i + 1 < n_cand) continue;               // wider than the output: try a narrower one
+    const long long tiles2 = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn);
+    const long long cost = ((tiles2 + pairs - 1) / pairs) * (BM + bn / 2 + fixed);
+    if (cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
 }  // namespace
 
 // 1 if the tensor-core kernel takes this product.
 NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, int K) {
   return x_dtype == NB_BF16 && w_dtype == NB_BF16 && K % 8 == 0 && M >= 1 && N >= 1 && K >= 8 &&
          (M + BM - 1) / BM <= 65535;
+}
+
+// 1: pairs of CTAs (`cta_group::2`, 256-row tiles) where the cost model prefers them; 2: for
+// every product of more than 128 rows that has a paired kernel; 0 (the default): single CTAs.
+NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
+  g_use_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+  return 0;
 }
 
 // Reads (and clears) the error flag that a timed-out wait raises; synchronises the device.
@@ -518,6 +638,24 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   const bool tma_epi = ((long long)N * esize) % 16 == 0 && (residual == nullptr || residual == out);
   const int bn = pick_tile_width(M, N, out_dtype == NB_F32, tma_epi);
   int rc;
+  // Pairs of CTAs on 256-row tiles bring less into each SM per flop (half of the weight tile
+  // each); they are taken when that outweighs the coarser tiles (see pick_pair_width).
+  const int pair_bn = (tma_epi && g_use_pairs) ? pick_pair_width(M, N, out_dtype == NB_F32, bn) : 0;
+  if (pair_bn) {
+    rc = NB_ERR_BAD_ARG;
+    if (out_dtype == NB_F32) {
+      if (pair_bn == 128) rc = launch<128, 1, float, 1>(X, W, bias, residual, out, M, N, K, act, stream);
+      else if (pair_bn == 96) rc = launch<96, 1, float, 1>(X, W, bias, residual, out, M, N, K, act, stream);
+    } else if (out_dtype == NB_BF16) {
+      if (pair_bn == 256) rc = launch<256, 1, bf16, 1>(X, W, bias, residual, out, M, N, K, act, stream);
+      else if (pair_bn == 192) rc = launch<192, 1, bf16, 1>(X, W, bias, residual, out, M, N, K, act, stream);
+      else if (pair_bn == 128) rc = launch<128, 1, bf16, 1>(X, W, bias, residual, out, M, N, K, act, stream);
+    }
+    NB_REQUIRE(rc != NB_ERR_BAD_ARG, NB_ERR_BAD_ARG, "gemm_tcgen05: no paired kernel of width %d", pair_bn);
+    if (rc) return rc;
+    NB_CHECK_LAUNCH("gemm_tcgen05");
+    return 0;
+  }
 #define NB_TC(BN_, EPI_, T_) rc = launch<BN_, EPI_, T_>(X, W, bias, residual, out, M, N, K, act, stream)
   if (out_dtype == NB_F32) {
     if (tma_epi) {

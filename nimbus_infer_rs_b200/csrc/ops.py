@@ -82,6 +82,14 @@ class CudaBackend:
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
         # the kernel before it (programmatic dependent launch)
         self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "0") == "1")
+        # NIMBUS_B200_PAIRS=1: large products on pairs of CTAs (measured no faster; off)
+        self.set_pairs(os.environ.get("NIMBUS_B200_PAIRS", "0") == "1")
+
+    def set_pairs(self, mode) -> None:
+        """Large products on pairs of CTAs sharing 256-row tiles (`cta_group::2`): 0/False off,
+        1/True where the cost model prefers them, 2 wherever a paired kernel exists."""
+        self.pairs = int(mode)
+        self.lib.nb_gemm_tcgen05_use_pairs(self.pairs)
 
     def set_overlap(self, on: bool) -> None:
         self.lib.nb_set_overlap((1 if on else 0))

@@ -60,6 +60,43 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// ---- pairs of CTAs (a cluster of two, `cta_group::2`)
+// The address, in the cluster's shared window, of what `addr` is in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// A tile load of one CTA of a pair whose bytes are counted on a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+// One arrival on the barrier at this offset in both CTAs of the pair, once the MMAs issued so
+// far are done.
+__device__ __forceinline__ void tc05_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar),
+      "h"((unsigned short)3)
+      : "memory");
+}
+// D (256 rows: 128 in each CTA's tensor memory) += A (each CTA's 128 rows) * B (each CTA's half
+// of the N rows), operands at the same shared-memory offsets in both CTAs.
+__device__ __forceinline__ void tc05_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                   uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+      "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
 }

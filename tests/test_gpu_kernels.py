@@ -447,11 +447,15 @@ def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
                                      (2048, 768, 3072), (1000, 3072, 768), (256, 50257, 768),
                                      (2048, 96, 320), (4096, 4096, 1600), (77, 1001, 2000),
                                      (2048, 1536, 256), (640, 800, 128),
-                                     (64, 768, 3072), (100, 2304, 768), (17, 776, 520)])
-def test_tensor_core_product(ops, M, N, K):
+                                     (64, 768, 3072), (100, 2304, 768), (17, 776, 520),
+                                     (2048, 2304, 768), (700, 1000, 256)])
+@pytest.mark.parametrize("pairs", [False, True])
+def test_tensor_core_product(ops, M, N, K, pairs):
     """The tcgen05 kernel (bf16, more than 64 rows) against float64: tile edges in M, N and K,
     all tile widths (64, 96, 128, 192, 256), every epilogue, products of at most 128 rows (one
     row tile); and no wait may have timed out."""
+    if pairs and M <= 128:
+        pytest.skip("pairs of CTAs take products of more than 128 rows")
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
@@ -459,6 +463,14 @@ def test_tensor_core_product(ops, M, N, K):
     ref0 = x.double() @ w.double().t()
     tol = 3e-6 * float(ref0.abs().max()) * math.sqrt(K / 64)
     out = torch.empty(M, N, device=DEV)
+    ops.set_pairs(2 if pairs else 0)       # 256-row tiles on pairs of CTAs (cta_group::2)
+    try:
+        _check_tensor_core_product(ops, x, w, bias, ref0, tol, out, M, N)
+    finally:
+        ops.set_pairs(0)
+
+
+def _check_tensor_core_product(ops, x, w, bias, ref0, tol, out, M, N):
     ops.linear(x, w, None, out)
     err = (out.double() - ref0).abs()
     assert err.max() <= tol, f"worst element {err.argmax().item() // N, err.argmax().item() % N}"
