@@ -117,8 +117,9 @@ class DecodeSession:
     def _capture(self) -> None:
         eng = self.engine
         before = eng.ops.launches
+        from .step_graphs import no_collection
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with no_collection(), torch.cuda.graph(graph):
             self._device_step()
         self._graph_launches = eng.ops.launches - before
         eng.ops.launches = before

@@ -15,7 +15,10 @@ plain launches: the same kernels run on the same data.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from collections import OrderedDict
+from contextlib import contextmanager
 
 import torch
 
@@ -31,9 +34,26 @@ def _kv_range(n: int, longest: int) -> int:
     return min(r, longest)
 
 
+@contextmanager
+def no_collection():
+    """No cyclic garbage collection inside: while a stream is being recorded, nothing may free
+    CUDA graphs or device memory, and a collection could do just that to objects of an engine
+    that is no longer used."""
+    was_enabled = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
 class StepGraphs:
     def __init__(self, engine, capacity: int = 8, max_logit_bytes: int = 256 << 20):
-        self.engine = engine
+        # the engine owns this object: a plain reference back would make a cycle, and the
+        # engine's graphs would then be freed whenever the collector runs
+        self.engine = weakref.proxy(engine)
         self.capacity = int(capacity)
         self.max_logit_bytes = int(max_logit_bytes)
         self._graphs: OrderedDict = OrderedDict()
@@ -91,7 +111,7 @@ class StepGraphs:
         layout = p.on_device(buf, max_kv_len=self.kv_bound(p))
         before = eng.ops.launches
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with no_collection(), torch.cuda.graph(graph):
             ctx = StepContext(eng.rt, eng.ops, layout, eng.model.position, eng.cache)
             logits = eng.model.forward(ctx)
         entry = {"graph": graph, "buf": buf, "logits": logits,

@@ -116,7 +116,10 @@ def test_step_shapes_that_share_a_recording():
 
     assert [_kv_range(n, 1024) for n in (1, 64, 65, 128, 129, 1000, 5000)] == \
         [64, 64, 128, 128, 256, 1024, 1024]
-    g = StepGraphs(SimpleNamespace(spec=SimpleNamespace(max_seq_len=1024, vocab_size=100)))
+    class Owner:                              # stands for the engine; held weakly
+        spec = SimpleNamespace(max_seq_len=1024, vocab_size=100)
+    owner = Owner()
+    g = StepGraphs(owner)
     a = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [0, 10])
     b = pack_step([(5, [9, 9, 9], [0]), (2, [7], [0])], [30, 3])          # other slots, tokens, places
     c = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [100, 10])        # a longer sequence
