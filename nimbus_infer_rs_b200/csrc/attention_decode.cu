@@ -306,8 +306,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                   // [2 stages][K | V][64][ROW]
-  float* w_acc = reinterpret_cast<float*>(smem_raw + (size_t)4 * STILE * sizeof(bf16));  // [WARPS][GH][HD]
+  // the warps' partial results, after the last page has been read: over the page tiles
+  // (more CTAs fit on an SM that way)
+  float* w_acc = reinterpret_cast<float*>(smem_raw);                 // [WARPS][GH][HD]
   float* w_ml = w_acc + WARPS * GH * HD;                             // [WARPS][GH][2]
+  static_assert((size_t)(WARPS * GH * HD + WARPS * GH * 2) * sizeof(float) <=
+                    (size_t)4 * STILE * sizeof(bf16), "partial results must fit in the page tiles");
   __shared__ int s_last;
 
   nb_launch_dependents();
@@ -535,8 +539,7 @@ int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, cons
                const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
                int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
                int k_col, int v_col, cudaStream_t stream) {
-  const size_t smem = (size_t)4 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16) +
-                      (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
+  const size_t smem = (size_t)4 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
   auto kern = attention_decode_mma_kernel<HD, TOut>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
