@@ -558,11 +558,13 @@ int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {
   return best;
 }
 
-// Off by default: measured on GPT-2 124M and XL prefill (2 x 1024 tokens) the paired tiles are
-// no faster than single CTAs (1.26 against 1.21 ms, 10.3 against 10.3 ms): the products are a
-// wave or two of tiles, and the cluster's start-up and its barriers cost what the lighter
-// loads save.
-int g_use_pairs = 0;   // 0 off, 1 where the cost model prefers them, 2 wherever a paired kernel exists
+// What a large product is bound by is the 64 bytes per clock an SM can take in: a 128 x 256
+// tile brings 48 KB per K block for 512 clocks of MMAs.  In a pair each CTA brings half of the
+// weight tile (32 KB), which measures 1.36 against 1.20 PFLOP/s at 8192 x 6400 x 1600.  A
+// product of a wave or two of tiles is no faster in pairs, or slower (12.3 -> 13.4 us at
+// 2048 x 2304 x 768): the cluster's start-up and its barriers cost more than the lighter
+// loads save; pairs are taken from three waves of single-CTA tiles on.
+int g_use_pairs = 1;   // 0 off, 1 where the cost model prefers them, 2 wherever a paired kernel exists
 
 // Width of 256-row tiles for pairs of CTAs, or 0 if single CTAs with `single_bn` are better.
 // Cost of a shape: waves over the SMs (or pairs of SMs) x what a CTA brings in per K block
@@ -578,6 +580,7 @@ int pick_pair_width(int M, int N, bool f32_out, int single_bn) {
   }
   const long long fixed = 64;
   const long long tiles1 = (long long)((M + BM - 1) / BM) * ((N + single_bn - 1) / single_bn);
+  if (g_use_pairs < 2 && tiles1 < 3ll * sms) return 0;
   long long best_cost = g_use_pairs >= 2 ? (1ll << 60)
                                          : ((tiles1 + sms - 1) / sms) * (BM + single_bn + fixed);
   int best = 0;
@@ -603,8 +606,8 @@ NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, 
          (M + BM - 1) / BM <= 65535;
 }
 
-// 1: pairs of CTAs (`cta_group::2`, 256-row tiles) where the cost model prefers them; 2: for
-// every product of more than 128 rows that has a paired kernel; 0 (the default): single CTAs.
+// 1 (the default): pairs of CTAs (`cta_group::2`, 256-row tiles) where the cost model prefers
+// them; 2: for every product of more than 128 rows that has a paired kernel; 0: single CTAs.
 NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
   g_use_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return 0;

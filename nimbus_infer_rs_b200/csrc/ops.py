@@ -82,8 +82,9 @@ class CudaBackend:
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
         # the kernel before it (programmatic dependent launch)
         self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "0") == "1")
-        # NIMBUS_B200_PAIRS=1: large products on pairs of CTAs (measured no faster; off)
-        self.set_pairs(os.environ.get("NIMBUS_B200_PAIRS", "0") == "1")
+        # NIMBUS_B200_PAIRS=0/1/2: large products on pairs of CTAs: never / where the cost
+        # model prefers them (products of three waves of tiles and more) / wherever possible
+        self.set_pairs(int(os.environ.get("NIMBUS_B200_PAIRS", "1") or 1))
 
     def set_pairs(self, mode) -> None:
         """Large products on pairs of CTAs sharing 256-row tiles (`cta_group::2`): 0/False off,

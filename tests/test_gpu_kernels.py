@@ -467,7 +467,7 @@ def test_tensor_core_product(ops, M, N, K, pairs):
     try:
         _check_tensor_core_product(ops, x, w, bias, ref0, tol, out, M, N)
     finally:
-        ops.set_pairs(0)
+        ops.set_pairs(1)
 
 
 def _check_tensor_core_product(ops, x, w, bias, ref0, tol, out, M, N):
