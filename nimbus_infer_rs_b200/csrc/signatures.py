@@ -24,6 +24,7 @@ SIGNATURES = {
     "nb_gemm_tcgen05_supported": "iiiii",
     "nb_gemm_tcgen05_error": "",
     "nb_gemm_tcgen05_use_pairs": "i",
+    "nb_gemm_tcgen05_use_splitk": "i",
     "nb_gemm_tcgen05": "pppppiiiiip",
     "nb_abi_version": "",
     "nb_set_overlap": "i",

@@ -448,12 +448,13 @@ def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
                                      (2048, 96, 320), (4096, 4096, 1600), (77, 1001, 2000),
                                      (2048, 1536, 256), (640, 800, 128),
                                      (64, 768, 3072), (100, 2304, 768), (17, 776, 520),
-                                     (2048, 2304, 768), (700, 1000, 256)])
+                                     (2048, 2304, 768), (700, 1000, 256),
+                                     (40, 520, 1600), (96, 136, 6400)])
 @pytest.mark.parametrize("pairs", [False, True])
 def test_tensor_core_product(ops, M, N, K, pairs):
     """The tcgen05 kernel (bf16, more than 64 rows) against float64: tile edges in M, N and K,
     all tile widths (64, 96, 128, 192, 256), every epilogue, products of at most 128 rows (one
-    row tile); and no wait may have timed out."""
+    row tile), K cut among a cluster of CTAs (few rows, long K), pairs of CTAs; and no wait may have timed out."""
     if pairs and M <= 128:
         pytest.skip("pairs of CTAs take products of more than 128 rows")
     torch.manual_seed(M + N + K)
