@@ -842,7 +842,9 @@ int pick_pair_width(int M, int N, bool f32_out, int single_bn) {
   }
   const long long fixed = 64;
   const long long tiles1 = (long long)((M + BM - 1) / BM) * ((N + single_bn - 1) / single_bn);
-  if (g_use_pairs < 2 && tiles1 < 3ll * sms) return 0;
+  // measured: pairs pay from three waves of single-CTA tiles on, for narrow outputs (fewer
+  // than 1024 columns) from six
+  if (g_use_pairs < 2 && (tiles1 < 3ll * sms || (N < 1024 && tiles1 < 6ll * sms))) return 0;
   long long best_cost = g_use_pairs >= 2 ? (1ll << 60)
                                          : ((tiles1 + sms - 1) / sms) * (BM + single_bn + fixed);
   int best = 0;
