@@ -362,6 +362,24 @@ class CudaBackend:
         self._call("nb_sample_temperature", _ptr(logits), (n), (v),
                    (temperature), _ptr(u), _ptr(out), self._stream())
 
+    def top_candidates(self, logits, n_keep, temp):
+        """The ``n_keep`` largest logits of every row with their indices (plus ties at the
+        threshold, up to ``n_keep + 32``), the row maximum and the f64 sum of
+        ``exp((x - max) / temp)`` over the row.  Returns ``(values [n, cap] f32, indices
+        [n, cap] i32, counts [n] i32, stats [n, 2] f64)`` on the device; a count of -1 marks a
+        row with a NaN, a count above ``cap`` ties that did not fit."""
+        _check(logits, "logits", torch.float32, 2)
+        n, v = logits.shape
+        cap = n_keep + 32
+        dev = logits.device
+        vals = torch.empty((n, cap), dtype=torch.float32, device=dev)
+        idx = torch.empty((n, cap), dtype=torch.int32, device=dev)
+        counts = torch.empty(n, dtype=torch.int32, device=dev)
+        stats = torch.empty((n, 2), dtype=torch.float64, device=dev)
+        self._call("nb_top_candidates", _ptr(logits), n, v, n_keep, cap, float(temp), _ptr(vals),
+                   _ptr(idx), _ptr(counts), _ptr(stats), self._stream())
+        return vals, idx, counts, stats
+
     def repetition_penalty(self, logits, history, history_len, penalty):
         _check(logits, "logits", torch.float32, 2)
         _check(history, "history", torch.int32, 2)

@@ -192,7 +192,125 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, float tem
   }
 }
 
+// The n_keep largest logits of a row, with their indices: what top-k and top-p filtering can
+// ever keep (src/sampler.rs:103-160 only ever keep the largest), so that the host's float64
+// sampler works on a thousand candidates instead of the vocabulary.  One CTA per row finds the
+// n_keep-th largest value by radix selection on order-preserving keys (three passes over the
+// row, 11 + 11 + 10 bits), then writes out every element that is not smaller (in any order;
+// ties at the threshold may make them more than n_keep: the count says how many, and what does
+// not fit in `cap` is not written).  It also leaves the row's maximum and, in f64, the sum of
+// exp((x - max) / temp) over the whole row: the softmax denominator the top-p rule needs.
+// A NaN in the row gives count -1 (the caller then takes the full path).
+constexpr int CAND_THREADS = 1024;
+
+__device__ __forceinline__ unsigned int order_key(float v) {
+  if (v == 0.0f) v = 0.0f;                              // -0 and +0 compare equal
+  const unsigned int b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(CAND_THREADS)
+top_candidates_kernel(const float* __restrict__ logits, int vocab, int n_keep, int cap, double temp,
+                      float* __restrict__ out_val, int* __restrict__ out_idx,
+                      int* __restrict__ out_count, double* __restrict__ out_stats) {
+  __shared__ unsigned int hist[2048];
+  __shared__ unsigned int s_prefix, s_mask, s_remaining, s_count, s_nan;
+  __shared__ float s_maxf[CAND_THREADS / 32];
+  __shared__ double s_sum[CAND_THREADS / 32];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  if (tid == 0) { s_prefix = 0u; s_mask = 0u; s_remaining = (unsigned)n_keep; s_count = 0u; s_nan = 0u; }
+  __syncthreads();
+
+  // maximum, NaN check
+  float mx = -INFINITY;
+  bool nan = false;
+  for (int i = tid; i < vocab; i += CAND_THREADS) {
+    const float v = row[i];
+    nan |= (v != v);
+    mx = fmaxf(mx, v);
+  }
+  mx = nb_warp_max(mx);
+  if (nan) s_nan = 1u;
+  if ((tid & 31) == 0) s_maxf[tid >> 5] = mx;
+  __syncthreads();
+  if (s_nan) {
+    if (tid == 0) out_count[r] = -1;
+    return;
+  }
+  mx = s_maxf[0];
+  for (int w = 1; w < CAND_THREADS / 32; ++w) mx = fmaxf(mx, s_maxf[w]);
+  // sum of exp((x - max) / temp) in f64
+  double sum = 0.0;
+  const double mxd = (double)mx / temp;
+  for (int i = tid; i < vocab; i += CAND_THREADS) sum += exp((double)row[i] / temp - mxd);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((tid & 31) == 0) s_sum[tid >> 5] = sum;
+
+  // radix selection of the n_keep-th largest key
+  const int shifts[3] = {21, 10, 0};
+  const int bits[3] = {11, 11, 10};
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = shifts[pass];
+    const unsigned int nb = 1u << bits[pass];
+    for (int i = tid; i < 2048; i += CAND_THREADS) hist[i] = 0u;
+    __syncthreads();
+    const unsigned int prefix = s_prefix, mask = s_mask;
+    for (int i = tid; i < vocab; i += CAND_THREADS) {
+      const unsigned int k = order_key(row[i]);
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & (nb - 1u)], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {   // from the largest bin down: the bin that holds the element we look for
+      unsigned int need = s_remaining, b = nb;
+      while (b > 0u) {
+        --b;
+        if (hist[b] >= need) break;
+        need -= hist[b];
+      }
+      s_remaining = need;
+      s_prefix = prefix | (b << shift);
+      s_mask = mask | ((nb - 1u) << shift);
+    }
+    __syncthreads();
+  }
+  const unsigned int threshold = s_prefix;
+  for (int i = tid; i < vocab; i += CAND_THREADS) {
+    const float v = row[i];
+    if (order_key(v) >= threshold) {
+      const unsigned int pos = atomicAdd(&s_count, 1u);
+      if ((int)pos < cap) {
+        out_val[(size_t)r * cap + pos] = v;
+        out_idx[(size_t)r * cap + pos] = i;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int w = 0; w < CAND_THREADS / 32; ++w) total += s_sum[w];
+    out_count[r] = (int)s_count;
+    out_stats[2 * r] = (double)mx;
+    out_stats[2 * r + 1] = total;
+  }
+}
+
 }  // namespace
+
+// n_keep <= cap.  out_val / out_idx: [n_rows, cap]; out_count: [n_rows]; out_stats: [n_rows, 2]
+// (maximum, sum of exp((x - max) / temp)).  Fewer than n_keep elements in a row: all of them.
+NB_EXPORT int nb_top_candidates(const float* logits, int n_rows, int vocab, int n_keep, int cap,
+                                double temp, float* out_val, int* out_idx, int* out_count,
+                                double* out_stats, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0 && n_keep >= 1 && cap >= n_keep && temp > 0.0, NB_ERR_BAD_ARG,
+             "top_candidates: bad sizes vocab=%d keep=%d cap=%d", vocab, n_keep, cap);
+  top_candidates_kernel<<<n_rows, CAND_THREADS, 0, stream>>>(logits, vocab, n_keep, cap, temp, out_val,
+                                                             out_idx, out_count, out_stats);
+  NB_CHECK_LAUNCH("top_candidates");
+  return 0;
+}
 
 NB_EXPORT int nb_repetition_penalty(float* logits, int n_rows, int vocab, const int* history,
                                     int history_stride, const int* history_len, float penalty,

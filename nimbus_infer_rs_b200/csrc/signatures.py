@@ -34,6 +34,7 @@ SIGNATURES = {
     "nb_kv_append": "piiiipppppiiiiip",
     "nb_advance_decode": "ppppip",
     "nb_repetition_penalty": "piipipfp",
+    "nb_top_candidates": "piiiidppppp",
     "nb_argmax_split": "piipppip",
     "nb_argmax": "piipp",
     "nb_sample_temperature": "piifppp",

@@ -40,17 +40,30 @@ class DecodeSession:
         host[:n] = first_tokens
         host[n:2 * n] = [engine.cache.lens[s] for s in slots]
         host[2 * n:] = slots
-        buf = torch.from_numpy(host).to(dev)
+        # The device buffers and the recorded step are kept by the engine between batches of
+        # the same size and sampling mode: a new batch fills the buffers again and replays the
+        # graph it finds, instead of recording one of its own.
+        self._key = (n, self.params.greedy, float(self.params.temperature) if not self.params.greedy else 0.0)
+        kept = engine.decode_states.pop(self._key, None) if self.use_graph else None
+        if kept is not None:
+            self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u = kept["buffers"]
+            self._buf.copy_(torch.from_numpy(host), non_blocking=False)
+            self._graph, self._graph_launches, self.logits = kept["graph"], kept["launches"], kept["logits"]
+            self._steps = 1 if self._graph is not None else 0
+        else:
+            self._buf = torch.from_numpy(host).to(dev)
+            self.next_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
+            self.want_rows = torch.arange(n, dtype=torch.int32, device=dev)
+            self.cu_rows = torch.arange(n + 1, dtype=torch.int32, device=dev)
+            self.u = torch.zeros(n, dtype=torch.float64, device=dev)
+            self.logits = None
+            self._graph = None
+            self._graph_launches = 0
+            self._steps = 0
+        buf = self._buf
         self.tokens, self.row_pos, self.row_slot = buf[:n], buf[n:2 * n], buf[2 * n:]
-        self.next_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
-        self.want_rows = torch.arange(n, dtype=torch.int32, device=dev)
-        self.cu_rows = torch.arange(n + 1, dtype=torch.int32, device=dev)
-        self.u = torch.zeros(n, dtype=torch.float64, device=dev)
-        self.logits = None
-        self._graph = None
         self._stage = None
         self._out_stage = None
-        self._steps = 0
         if self.params.repetition_penalty != 1.0 or (
                 not self.params.greedy and (self.params.top_k > 0 or self.params.top_p < 1.0)):
             raise ValueError("a decode session selects tokens greedily or by temperature only")
@@ -143,6 +156,19 @@ class DecodeSession:
         if self.live[index]:
             self.live[index] = False
             self.row_slot[index:index + 1].fill_(-1)
+
+    def close(self) -> None:
+        """The batch is over: the buffers and the recorded step go back to the engine for the
+        next batch of this size."""
+        if self.use_graph and self._graph is not None and self._buf is not None:
+            self.engine.decode_states[self._key] = {
+                "buffers": (self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u),
+                "graph": self._graph, "launches": self._graph_launches, "logits": self.logits,
+                # scratch buffers of the kernel library that the graph points into
+                "scratch": self.engine.ops.scratch_refs() if hasattr(self.engine.ops, "scratch_refs") else None}
+            while len(self.engine.decode_states) > 8:
+                self.engine.decode_states.pop(next(iter(self.engine.decode_states)))
+        self._buf = None
 
     @property
     def n_live(self) -> int:

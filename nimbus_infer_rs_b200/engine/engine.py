@@ -48,6 +48,8 @@ class Engine:
         # keeps every step on plain launches)
         self.step_graphs = StepGraphs(self) if (
             self.graph_safe and self.rt.device.type == "cuda") else None
+        # buffers and recorded steps of finished decode sessions, by batch size and sampling mode
+        self.decode_states: dict = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod

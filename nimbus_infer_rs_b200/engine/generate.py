@@ -100,6 +100,7 @@ def run_batch(engine, prompts: list[list[int]], indices: list[int], params: Samp
                 engine.free_slot(slots.pop(s.index))
         return nxt
 
+    session = None
     try:
         # the prompts, in one step; logits of each last token
         logits = engine.step([(slots[s.index], prompts[s.index], [s.prompt_len - 1]) for s in live])
@@ -130,6 +131,8 @@ def run_batch(engine, prompts: list[list[int]], indices: list[int], params: Samp
                 logits = engine.step([(slots[s.index], [tok], [0]) for s, tok in nxt])
                 nxt = take(live, sampler.sample(logits, [seq_samplers[s.index] for s in live]))
     finally:
+        if session is not None:
+            session.close()
         for slot in slots.values():
             engine.free_slot(slot)
     return results

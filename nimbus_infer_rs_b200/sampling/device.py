@@ -35,14 +35,53 @@ class BatchSampler:
         p = self.params
         return (not p.greedy) and (p.top_k > 0 or p.top_p < 1.0)
 
+    #: candidates the device hands to the host's sampler when top-k / top-p is on
+    N_CANDIDATES = 1024
+
+    def _filtered(self, logits: torch.Tensor, seqs: list[SequenceSampler]) -> list[int]:
+        """top-k / top-p sampling: the reference's float64 sampler on the host.  Both filters
+        only keep the largest logits, so the device first picks each row's largest thousand
+        (with the row's softmax denominator) and the host decides among them; a row whose cut
+        does not fall among them, or that has a NaN, is brought over whole.  With a repetition
+        penalty the logits of the generated tokens come along, wherever they rank."""
+        p = self.params
+        n, vocab = logits.shape
+        fast = logits.is_cuda and hasattr(self.ops, "top_candidates")
+        out: list[int | None] = [None] * n
+        if fast:
+            temp = max(float(np.float32(p.temperature)), 1e-6)
+            keep = min(self.N_CANDIDATES, vocab)
+            vals, idx, counts, stats = self.ops.top_candidates(logits, keep, temp)
+            gen = [None] * n
+            if p.repetition_penalty != 1.0:
+                gen = [np.array(sorted({t for t in s.generated if 0 <= t < vocab}), dtype=np.int64)
+                       for s in seqs]
+                flat = np.concatenate([g + i * vocab for i, g in enumerate(gen)]) if n else gen
+                gen_vals = logits.reshape(-1)[torch.from_numpy(flat).to(logits.device)].cpu().numpy() \
+                    if len(flat) else np.zeros(0, np.float32)
+                ends = np.cumsum([len(g) for g in gen])
+            vals, idx = vals.cpu().numpy(), idx.cpu().numpy()
+            counts, stats = counts.cpu().numpy(), stats.cpu().numpy()
+            for i, s in enumerate(seqs):
+                g_idx = g_vals = None
+                if gen[i] is not None and len(gen[i]):
+                    g_idx, g_vals = gen[i], gen_vals[ends[i] - len(gen[i]):ends[i]]
+                out[i] = host_sampler.sample_from_candidates(
+                    vals[i], idx[i], int(counts[i]), float(stats[i, 0]), float(stats[i, 1]), p,
+                    s.rng, keep, vocab, g_idx, g_vals)
+        for i, s in enumerate(seqs):
+            if out[i] is None:
+                row = logits[i].detach().to("cpu").numpy()
+                out[i] = host_sampler.sample(row, p, s.generated, s.rng)
+        return out
+
     def sample(self, logits: torch.Tensor, seqs: list[SequenceSampler]) -> list[int]:
         """``logits`` fp32 [n, vocab] (may be modified), one row per entry of ``seqs``."""
         p = self.params
         n = logits.shape[0]
         assert n == len(seqs)
         if self.needs_host():
-            rows = logits.detach().to("cpu").numpy()
-            out = [host_sampler.sample(rows[i], p, s.generated, s.rng) for i, s in enumerate(seqs)]
+            out = self._filtered(logits, seqs)
         else:
             if p.repetition_penalty != 1.0 and any(s.generated for s in seqs):
                 width = max(len(s.generated) for s in seqs)

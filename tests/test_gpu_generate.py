@@ -93,3 +93,39 @@ def test_command_line(model_dirs):
     r = _cli("bench", "--model", str(model_dirs["A"]), "--prefill", "16", "--decode", "4", "--runs", "1")
     assert r.returncode == 0, r.stderr
     assert json.loads(r.stdout)["decode_tokens"] == 4
+
+
+def test_top_k_and_top_p_from_the_largest_logits_equal_the_whole_row(model_dirs):
+    """With top-k / top-p on, the device hands the host each row's largest logits; the tokens
+    must be the ones the host's sampler picks from whole rows, draw for draw."""
+    from nimbus_infer_rs_b200.csrc import ops as ops_mod
+    from nimbus_infer_rs_b200.sampling import BatchSampler, SequenceSampler
+    from nimbus_infer_rs_b200.sampling import host as host_sampler
+    ops = ops_mod.backend()
+    torch.manual_seed(11)
+    fast_rows = 0
+    for kw in (dict(temperature=0.8, top_k=40), dict(temperature=1.0, top_p=0.9),
+               dict(temperature=1.3, top_k=200, top_p=0.6), dict(temperature=0.5, top_p=0.0),
+               dict(temperature=1.0, top_p=0.999), dict(temperature=0.9, top_k=5000),
+               dict(temperature=0.8, top_k=40, repetition_penalty=1.3),
+               dict(temperature=1.1, top_p=0.5, repetition_penalty=0.8)):
+        p = SamplingParams(seed=3, **kw)
+        logits = torch.randn(6, 50257, device="cuda:0") * 4.0
+        logits[0, 100:140] = logits[0].max()                 # ties
+        a = [SequenceSampler(p, i) for i in range(6)]
+        b = [SequenceSampler(p, i) for i in range(6)]
+        for i in range(6):                                   # a history: the row's best tokens and others
+            hist = logits[i].topk(3 + i).indices.tolist() + [7, 7, 50000 - i]
+            a[i].generated, b[i].generated = list(hist), list(hist)
+        got = BatchSampler(p, ops, logits.device).sample(logits.clone(), a)
+        rows = logits.cpu().numpy()
+        want = [host_sampler.sample(rows[i], p, b[i].generated, b[i].rng) for i in range(6)]
+        assert got == want, kw
+        assert [s.rng.next_f64() for s in a] == [s.rng.next_f64() for s in b]   # same draws used
+        vals, idx, counts, stats = ops.top_candidates(logits, 1024, max(p.temperature, 1e-6))
+        for i in range(6):
+            r = host_sampler.sample_from_candidates(
+                vals[i].cpu().numpy(), idx[i].cpu().numpy(), int(counts[i]), float(stats[i, 0]),
+                float(stats[i, 1]), p, SequenceSampler(p, i).rng, 1024)
+            fast_rows += r is not None
+    assert fast_rows >= 18                                   # most rows never leave the device whole

@@ -327,6 +327,43 @@ def test_kv_append_writes_only_its_rows(ops, dtype, hd):
     assert torch.equal(kv.k, expect_k) and torch.equal(kv.v, expect_v)
 
 
+@pytest.mark.parametrize("vocab, n_keep", [(50257, 1024), (513, 64), (40, 64), (3000, 1)])
+def test_the_largest_logits_of_a_row(ops, vocab, n_keep):
+    """The candidates kernel: every element not smaller than the n_keep-th largest, the row
+    maximum and the f64 softmax denominator; ties at the threshold; a NaN row; fewer elements
+    than asked for."""
+    torch.manual_seed(vocab)
+    logits = torch.randn(5, vocab, device=DEV) * 3.0
+    logits[1, :7] = logits[1].max()                                  # ties at the top
+    if vocab > n_keep + 40:
+        thr = logits[2].sort(descending=True).values[n_keep - 1]
+        logits[2, logits[2].argsort()[:50]] = thr                    # 50 more ties at the threshold
+    logits[3, 5] = float("nan")
+    logits[4, 1::2] = float("-inf")
+    temp = 0.7
+    keep = min(n_keep, vocab)
+    vals, idx, counts, stats = ops.top_candidates(logits, keep, temp)
+    vals, idx, counts, stats = vals.cpu(), idx.cpu(), counts.cpu(), stats.cpu()
+    cap = vals.shape[1]
+    for r in range(5):
+        row = logits[r].cpu()
+        if r == 3:
+            assert counts[r] == -1
+            continue
+        thr = row.sort(descending=True).values[keep - 1]
+        want = set(torch.nonzero(row >= thr).flatten().tolist())
+        assert counts[r] == len(want)
+        if len(want) <= cap:
+            got = idx[r, :counts[r]].tolist()
+            assert set(got) == want and len(got) == len(want)
+            assert torch.equal(vals[r, :counts[r]], row[idx[r, :counts[r]].long()])
+        else:
+            assert r == 2
+        assert stats[r, 0] == row.max().double()
+        ref = torch.exp(row.double() / temp - row.max().double() / temp).sum()
+        assert abs(stats[r, 1] - ref) <= 1e-12 * ref
+
+
 def test_argmax_first_maximum(ops):
     torch.manual_seed(3)
     logits = torch.randn(9, 50257, device=DEV)

@@ -80,3 +80,53 @@ def test_params_defaults_and_validation():     # src/sampler.rs:17-29
     assert not p.greedy and SamplingParams(temperature=0.0).greedy
     with pytest.raises(ValueError):
         SamplingParams(top_k=-1).validate()
+
+
+def test_the_largest_logits_decide_as_the_whole_row_does():
+    """top-k / top-p from a row's largest logits only (what the device hands over) must pick
+    the token the whole row picks, or say that it cannot (None), never something else."""
+    from nimbus_infer_rs_b200.sampling import host
+    rng = np.random.default_rng(0)
+    decided = 0
+    for trial in range(300):
+        V = int(rng.integers(40, 3000))
+        logits = (rng.standard_normal(V) * float(rng.choice([0.5, 2.0, 8.0]))).astype(np.float32)
+        if trial % 5 == 0:
+            logits[rng.integers(0, V, 4)] = logits.max()              # ties at the top
+        k = int(rng.choice([0, 1, 5, 50, 300]))
+        p = float(rng.choice([1.0, 0.9, 0.5, 0.1, 0.0]))
+        T = float(rng.choice([0.7, 1.0, 1.5]))
+        if k == 0 and p >= 1.0:
+            continue
+        pen = float(rng.choice([1.0, 1.3, 0.7, 2.5]))                 # a penalty moves generated tokens
+        gen = [int(t) for t in rng.integers(0, V, int(rng.integers(0, 30)))]
+        if trial % 3 == 0:
+            gen.append(int(np.argmax(logits)))
+        params = SamplingParams(temperature=T, top_k=k, top_p=p, repetition_penalty=pen)
+        n_keep = min(128, V)
+        temp = max(float(np.float32(T)), 1e-6)
+        thr = np.sort(logits)[::-1][n_keep - 1]
+        sel = rng.permutation(np.nonzero(logits >= thr)[0])           # in any order
+        cap = n_keep + 32
+        vals, idx = np.zeros(cap, np.float32), np.zeros(cap, np.int32)
+        vals[:min(len(sel), cap)], idx[:min(len(sel), cap)] = logits[sel][:cap], sel[:cap]
+        mx = float(logits.max())
+        total = float(np.sum(np.exp(logits.astype(np.float64) / temp - mx / temp)))
+        whole = host.sample(logits, params, gen, Xoshiro256pp(trial))
+        r = Xoshiro256pp(trial)
+        g = np.array(sorted(set(gen)), dtype=np.int64)
+        few = host.sample_from_candidates(vals, idx, len(sel), mx, total, params, r, n_keep, V,
+                                          g if pen != 1.0 else None, logits[g] if pen != 1.0 else None)
+        if few is None:
+            assert r.next_f64() == Xoshiro256pp(trial).next_f64()     # nothing was drawn
+        else:
+            assert few == whole, (trial, V, k, p, T)
+            decided += 1
+    assert decided > 120
+    # not plain numbers, too many ties, k beyond the candidates: the whole row has to decide
+    assert host.sample_from_candidates(np.zeros(4, np.float32), np.zeros(4, np.int32), -1, 0.0, 1.0,
+                                       SamplingParams(top_k=2), Xoshiro256pp(1), 4) is None
+    assert host.sample_from_candidates(np.zeros(4, np.float32), np.zeros(4, np.int32), 9, 0.0, 1.0,
+                                       SamplingParams(top_k=2), Xoshiro256pp(1), 4) is None
+    assert host.sample_from_candidates(np.zeros(4, np.float32), np.arange(4, dtype=np.int32), 4, 0.0,
+                                       4.0, SamplingParams(top_k=9), Xoshiro256pp(1), 4) is None
