@@ -2,8 +2,9 @@
 
 Greedy decoding, temperature sampling and the repetition penalty run as kernels; the random
 number of each draw comes from the sequence's own host generator so that results do not
-depend on batching.  With top-k or top-p filtering on, the batch's logits are brought to the
-host and the float64 restatement of the reference's sampler decides (sampling/host.py).
+depend on batching.  With top-k or top-p filtering on, a kernel picks each row's largest
+logits and the float64 restatement of the reference's sampler decides among them on the host
+(sampling/host.py); a row that these cannot settle is brought to the host whole.
 """
 from __future__ import annotations
 
