@@ -530,6 +530,18 @@ int launch_f32(const void* X, const float* gamma, const float* beta, float eps, 
 
 }  // namespace
 
+// Whether nb_gemm_skinny can apply the LayerNorm of the rows itself (bf16 weights): at most 16
+// rows that fit in shared memory in one piece and are short enough for the registers of the
+// threads that share a row.  Else the caller normalises the rows first.
+NB_EXPORT int nb_gemm_skinny_norm_supported(int M, int N, int K) {
+  if (M < 1 || M > 16 || N < 1 || K < 8 || K % 8) return 0;
+  const int warps = (K > 1024 || M > 4) ? 8 : 4;   // as dispatch_bf16 picks them
+  const int unit = 32 * warps;
+  const int kseg = ((K + unit - 1) / unit) * unit;
+  if (kseg > (96 * 1024) / (M * (int)sizeof(bf16))) return 0;
+  return K <= 8 * norm_threads_per_row(warps * 32, M) * 8;
+}
+
 // M <= 64.  gamma != nullptr asks for LayerNorm of the rows first (X must then be fp32).
 // bf16 weights need K % 8 == 0 and 16-byte aligned rows; `residual` may alias `out` (fp32).
 NB_EXPORT int nb_gemm_skinny(const void* X, int x_dtype, const float* gamma, const float* beta,

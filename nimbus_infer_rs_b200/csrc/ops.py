@@ -163,10 +163,11 @@ class CudaBackend:
         # few rows: the weight-streaming kernel; from 17 rows on the tensor-core kernel streams
         # weights faster (TMA ring), where it applies
         skinny = (M <= FUSED_NORM_MAX_ROWS or (M <= SKINNY_MAX_ROWS and not tensor_core)) \
-            and (w.dtype == torch.float32 or K % 8 == 0)
+            and (K * 32 <= 220 * 1024 if w.dtype == torch.float32 else K % 8 == 0)
         if skinny:
             if norm is not None and (M > FUSED_NORM_MAX_ROWS or N > FUSED_NORM_MAX_COLS
-                                     or w.dtype != torch.bfloat16):
+                                     or w.dtype != torch.bfloat16
+                                     or not self.lib.nb_gemm_skinny_norm_supported(M, N, K)):
                 h = torch.empty((M, K), device=x.device, dtype=norm[3])
                 self.layernorm(x, norm[0], norm[1], norm[2], h)
                 x, norm = h, None

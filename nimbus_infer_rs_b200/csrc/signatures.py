@@ -21,6 +21,7 @@ SIGNATURES = {
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",
+    "nb_gemm_skinny_norm_supported": "iii",
     "nb_gemm_tcgen05_supported": "iiiii",
     "nb_gemm_tcgen05_error": "",
     "nb_gemm_tcgen05_use_pairs": "i",

@@ -422,7 +422,8 @@ def test_repetition_penalty(ops):
 
 
 @pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 2304, 768), (17, 100, 96), (64, 768, 3072),
-                                     (40, 1001, 1600), (3, 77, 100), (130, 257, 72)])
+                                     (40, 1001, 1600), (3, 77, 100), (130, 257, 72),
+                                     (8, 520, 3072), (16, 96, 4096), (2, 72, 8192), (11, 264, 1600)])
 @pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
 def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
     """LayerNorm fused into the product (few rows) or run before it (many rows) must both
