@@ -64,9 +64,17 @@ def cmd_generate(args) -> int:
         max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
         top_p=args.top_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
         stop_tokens=[int(x) for x in args.stop.split(",")] if args.stop else [])
+    on_token = None
+    if args.stream:   # ids as they are produced (the reference streams text, src/main.rs:157-167)
+        many = len(prompts) > 1
+
+        def on_token(request, token, step):
+            print(f"{request}:{token}" if many else token, end=" ", flush=True)
     t0 = time.perf_counter()
-    out = engine.generate(prompts, params)
+    out = engine.generate(prompts, params, on_token=on_token)
     dt = time.perf_counter() - t0
+    if args.stream:
+        print(flush=True)
     n = sum(len(o) for o in out)
     if args.json:
         if len(prompts) == 1:   # src/main.rs:176-182
@@ -187,6 +195,7 @@ def main(argv=None) -> int:
     g.add_argument("--repetition-penalty", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=None)
     g.add_argument("--stop", default="")
+    g.add_argument("--stream", action="store_true", help="print token ids as they are produced")
     g.add_argument("--json", action="store_true")
     g.set_defaults(fn=cmd_generate)
 

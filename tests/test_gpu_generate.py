@@ -80,6 +80,12 @@ def test_command_line(model_dirs):
     out = json.loads(r.stdout)
     assert out["prompt_tokens"] == 3 and out["generated_ids"] == P.greedy_generate(W, [5, 17, 3], 6)
     assert "tok/s]" in r.stderr
+    r = _cli("generate", "--model", str(model_dirs["A"]), "--ids", "5,17,3", "--max-new-tokens", "6",
+             "--dtype", "float32", "--stream")
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.strip().splitlines()     # the ids as they came, then the whole list
+    assert [int(t) for t in lines[0].split()] == out["generated_ids"]
+    assert json.loads(lines[1]) == out["generated_ids"]
     r = _cli("logits", "--model", str(model_dirs["A"]), "--ids", "5,17,3", "--dtype", "float32")
     probe = json.loads(r.stdout)
     ref = P.forward_logits(W, [5, 17, 3])[-1]
