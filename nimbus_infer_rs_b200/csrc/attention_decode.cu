@@ -314,7 +314,6 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
                     (size_t)4 * STILE * sizeof(bf16), "partial results must fit in the page tiles");
   __shared__ int s_last;
 
-  nb_launch_dependents();
   nb_grid_dependency_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -459,6 +458,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     __syncthreads();   // the stage is free for the copy after next
   }
 
+  nb_launch_dependents();   // the pages are read: the next kernel may be set up
   // row sums over the lanes that share a head (different keys), then the warps
 #pragma unroll
   for (int off = 4; off < 32; off <<= 1) {

@@ -55,9 +55,13 @@ void nb_set_error(const char* fmt, ...);
 // Programmatic dependent launch.  A kernel launched through nb_launch with overlap enabled
 // may start while the kernel before it in the stream is still running; it must execute
 // nb_grid_dependency_wait() before it reads anything an earlier kernel wrote or writes
-// anything at all (before that point it may only fetch constants: weights, biases).  Every
-// kernel calls nb_launch_dependents() early so that its successor can be set up meanwhile.
-// Without the launch attribute both instructions do nothing.
+// anything at all (before that point it may only fetch constants: weights, biases), and it
+// must do so in every CTA, also in one that has nothing to do: a grid that ended without
+// waiting would let its own successor run ahead of the kernel before it.  A kernel calls
+// nb_launch_dependents() once its own loads are in (the products and the decode attention: at
+// the start of the kernel the successor's loads compete with its own and the chain gets
+// slower) so that its successor is set up while it finishes.  Without the launch attribute
+// both instructions do nothing.
 // ---------------------------------------------------------------------------------
 bool nb_overlap_enabled();
 

@@ -79,9 +79,9 @@ class CudaBackend:
         self._prefill_scr = {}
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
-        # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and weight fetch overlap the tail of
-        # the kernel before it (programmatic dependent launch)
-        self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "0") == "1")
+        # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and first weight fetch overlap the tail
+        # of the kernel before it (programmatic dependent launch; on by default)
+        self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "1") != "0")
         # NIMBUS_B200_PAIRS=0/1/2: large products on pairs of CTAs: never / where the cost
         # model prefers them (products of three waves of tiles and more) / wherever possible
         self.set_pairs(int(os.environ.get("NIMBUS_B200_PAIRS", "1") or 1))
