@@ -139,7 +139,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   const int q0 = tile * TILE_Q;
   const int slot = seq_slot[s];
-  if (q0 >= n_q || slot < 0) return;          // the whole CTA leaves: nothing is allocated yet
+  // (a CTA that leaves waits for the kernel before this one all the same: a grid that ended
+  // early would let the kernel after it overtake that one)
+  if (q0 >= n_q || slot < 0) {                // the whole CTA leaves: nothing is allocated yet
+    nb_grid_dependency_wait();
+    return;
+  }
   const int pos0 = seq_pos0[s];
   const int kvh = h / group;
   const int rows_here = min(TILE_Q, n_q - q0);
@@ -150,7 +155,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   // partial results in `part`, and the one that finishes last adds them up.
   const int p_first = first_key / PAGE_TOKENS, p_last = last_pos / PAGE_TOKENS + 1;
   const int n_splits = (p_last - p_first + chunk_pages - 1) / chunk_pages;
-  if (split >= n_splits) return;
+  if (split >= n_splits) {
+    nb_grid_dependency_wait();
+    return;
+  }
   const int p_begin = p_first + split * chunk_pages, p_end = min(p_last, p_begin + chunk_pages);
   const int nb = (p_end - p_begin + 1) / 2;             // turns of two pages
   // turn i takes pages p_begin + 2i and, if it is still in the run, the next one
@@ -184,6 +192,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // The batch layout and the block table are older than the kernel before this one; the rows
+  // of queries, keys and values are its work.  Under a programmatic launch everything above
+  // ran while it was finishing.
+  nb_grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {   // ------------------------------------------------------ TMA producer
@@ -250,6 +262,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       if (stored) bulk_wait_all();   // the stores have left shared memory and reached the cache
+      nb_launch_dependents();        // all loads are on their way: the next kernel may be set up
     }
   } else if (warp == 1) {
     if (lane == 0) {   // ------------------------------------------------------ MMA issuer
@@ -568,10 +581,10 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
     configured = true;
   }
   dim3 grid(((max_q_len + TILE_Q - 1) / TILE_Q) * max_splits, n_heads, n_seqs);
-  kern<<<grid, TC_THREADS, L::TOTAL, stream>>>(mq, mk, mv, mn, append, k_col, v_col, q_col, cu_rows, seq_slot, seq_pos0,
-                                               block_table, max_pages, n_kv_heads,
-                                               n_heads / n_kv_heads, (TOut*)out, out_stride, scale,
-                                               window, max_splits, chunk_pages, part, counters);
+  NB_CUDA(nb_launch(kern, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, mq, mk, mv, mn, append, k_col,
+                    v_col, q_col, cu_rows, seq_slot, seq_pos0, block_table, max_pages, n_kv_heads,
+                    n_heads / n_kv_heads, (TOut*)out, out_stride, scale, window, max_splits,
+                    chunk_pages, part, counters));
   return 0;
 }
 

@@ -148,6 +148,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Barriers and tensor memory are set up; what the kernel before this one wrote (the rows of
+  // X, the residual) is touched from here on.  Under a programmatic launch the set-up above
+  // ran while that kernel was finishing.
+  nb_grid_dependency_wait();
 
   // The CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the shared-memory
   // ring runs on across tiles, and while the epilogue drains one accumulator the MMAs of the
@@ -179,6 +183,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
       }
+      // every load of this CTA is on its way: the next kernel may be set up while the last
+      // products and the epilogue run
+      nb_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {   // ------------------------------------------ MMA issuer
@@ -783,8 +790,8 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     return 0;
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
-  kern<<<grid, cta_threads(BN, EPI), smem, stream>>>(mx, mw, mo, bias, residual, (TOut*)out, M, N, K,
-                                                      act, tiles_n, (int)num_tiles, a_rows * BK * 2);
+  NB_CUDA(nb_launch(kern, dim3(grid), dim3(cta_threads(BN, EPI)), (size_t)smem, stream, mx, mw, mo, bias,
+                    residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2));
   return 0;
 }
 
