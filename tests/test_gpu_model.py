@@ -283,3 +283,32 @@ def test_recorded_steps_are_dropped_least_recently_used_first(model_dirs):
         for eng in (e, plain):
             eng.free_slot(eng._s)
     assert len(e.step_graphs._graphs) == 1 and e.step_graphs.captures >= 3
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_kernels_that_start_before_their_predecessor_ends_change_nothing(model_dirs, name):
+    """With programmatic dependent launch a kernel is set up, and fetches weights, while the
+    kernel before it is finishing.  Whatever it reads of that kernel's work it must read after
+    its wait: a prompt, then eighty single-token steps (plain launches, recorded steps and
+    their replays, page boundaries), give the same bits with the overlap on and off."""
+    from nimbus_infer_rs_b200.csrc import ops as ops_mod
+    ops = ops_mod.backend()
+    was = ops.overlap
+    runs = {}
+    try:
+        for on in (True, False):
+            ops.set_overlap(on)
+            e = _engine(model_dirs, name, "bfloat16")
+            toks = random_tokens(e.spec.vocab_size, 150, seed=9)
+            slots = [e.alloc_slot(), e.alloc_slot()]
+            outs = [e.step([(slots[0], toks[:37], list(range(37))), (slots[1], toks[5:20], [14])])]
+            for i in range(80):
+                outs.append(e.step([(slots[0], [toks[37 + i]], [0]), (slots[1], [toks[20 + i]], [0])]))
+            runs[on] = torch.cat(outs).cpu()
+            for s in slots:
+                e.free_slot(s)
+    finally:
+        ops.set_overlap(was)
+    assert torch.equal(runs[True], runs[False])
+    ref = plain_logits(model_dirs[name], toks[:37])
+    assert_close(runs[True][:37], ref[:37], "bfloat16", f"{name} prompt")
