@@ -16,6 +16,20 @@ from .params import DEFAULT_SEED, SamplingParams
 from .rng import Xoshiro256pp, sequence_seed
 
 
+_POOL = None
+
+
+def _pool():
+    """Threads for the rows that the host's sampler takes whole (made on first use)."""
+    global _POOL
+    if _POOL is None:
+        import os
+        from concurrent.futures import ThreadPoolExecutor
+        _POOL = ThreadPoolExecutor(max_workers=max(2, min(16, os.cpu_count() or 2)),
+                                   thread_name_prefix="nimbus-sampler")
+    return _POOL
+
+
 class SequenceSampler:
     """Per-sequence sampling state: generator and generated history."""
 
@@ -70,10 +84,24 @@ class BatchSampler:
                 out[i] = host_sampler.sample_from_candidates(
                     vals[i], idx[i], int(counts[i]), float(stats[i, 0]), float(stats[i, 1]), p,
                     s.rng, keep, vocab, g_idx, g_vals)
-        for i, s in enumerate(seqs):
-            if out[i] is None:
-                row = logits[i].detach().to("cpu").numpy()
-                out[i] = host_sampler.sample(row, p, s.generated, s.rng)
+        todo = [i for i in range(n) if out[i] is None]
+        if todo:
+            # whole rows: one copy for all of them, then a thread per row (sorting 50,000 values
+            # takes milliseconds, numpy lets go of the interpreter lock meanwhile, and every
+            # sequence draws from its own generator)
+            sel = logits.detach() if len(todo) == n else logits.detach()[
+                torch.tensor(todo, device=logits.device)]
+            rows = sel.to("cpu").numpy()
+
+            def one(j):
+                i = todo[j]
+                return host_sampler.sample(rows[j], p, seqs[i].generated, seqs[i].rng)
+            if len(todo) == 1:
+                results = [one(0)]
+            else:
+                results = list(_pool().map(one, range(len(todo))))
+            for j, i in enumerate(todo):
+                out[i] = results[j]
         return out
 
     def sample(self, logits: torch.Tensor, seqs: list[SequenceSampler]) -> list[int]:
