@@ -130,3 +130,26 @@ def test_the_largest_logits_decide_as_the_whole_row_does():
                                        SamplingParams(top_k=2), Xoshiro256pp(1), 4) is None
     assert host.sample_from_candidates(np.zeros(4, np.float32), np.arange(4, dtype=np.int32), 4, 0.0,
                                        4.0, SamplingParams(top_k=9), Xoshiro256pp(1), 4) is None
+
+
+def test_whole_rows_sampled_side_by_side_equal_one_after_the_other():
+    """Rows that the host's sampler takes whole are handed to threads; every sequence has its
+    own generator and history, so the tokens must be the ones a plain loop picks, draw for
+    draw and step after step."""
+    import torch
+    from nimbus_infer_rs_b200.sampling import BatchSampler, SequenceSampler
+    params = SamplingParams(temperature=0.9, top_p=0.8, top_k=7, repetition_penalty=1.3, seed=5)
+    n, vocab = 6, 301
+    g = np.random.default_rng(3)
+    sampler = BatchSampler(params, ops=None, device="cpu")
+    seqs = [SequenceSampler(params, i) for i in range(n)]
+    plain = [SequenceSampler(params, i) for i in range(n)]
+    for step in range(5):
+        logits = g.normal(size=(n, vocab)).astype(np.float32) * 3
+        got = sampler.sample(torch.from_numpy(logits.copy()), seqs)
+        want = []
+        for i in range(n):
+            t = H.sample(logits[i], params, plain[i].generated, plain[i].rng)
+            plain[i].generated.append(int(t))
+            want.append(int(t))
+        assert got == want, step
