@@ -363,6 +363,16 @@ class CudaBackend:
         self._call("nb_sample_temperature", _ptr(logits), (n), (v),
                    (temperature), _ptr(u), _ptr(out), self._stream())
 
+    def sample_top_k(self, logits, k, temperature, u, out):
+        """Top-k sampling (no top-p) on the device: ``out[r]`` is drawn with ``u[r]`` among the
+        row's ``k`` largest logits (ties at the k-th included); -1 marks a row with a NaN."""
+        _check(logits, "logits", torch.float32, 2)
+        _check(u, "u", torch.float64, 1)
+        _check(out, "out", torch.int32, 1)
+        n, v = logits.shape
+        self._call("nb_sample_top_k", _ptr(logits), n, v, int(k), float(temperature), _ptr(u),
+                   _ptr(out), self._stream())
+
     def top_candidates(self, logits, n_keep, temp):
         """The ``n_keep`` largest logits of every row with their indices (plus ties at the
         threshold, up to ``n_keep + 32``), the row maximum and the f64 sum of

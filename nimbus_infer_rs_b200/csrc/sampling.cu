@@ -296,6 +296,130 @@ top_candidates_kernel(const float* __restrict__ logits, int vocab, int n_keep, i
   }
 }
 
+// Top-k sampling wholly on the device (src/sampler.rs:103-116 then :181-215, top-p off): the
+// k-th largest logit of the row is found by the same radix selection, everything below it is
+// left out (ties at the threshold stay in, as in the reference), and the draw walks the
+// cumulative sum of exp((x - max) / temp) over what is left in index order, in f64, with the
+// u[r] that the sequence's own generator gave.  Each thread owns a contiguous piece of the
+// vocabulary.  A row with a NaN gives -1 (the caller decides on the host).
+__global__ void __launch_bounds__(CAND_THREADS)
+sample_top_k_kernel(const float* __restrict__ logits, int vocab, int k, float temperature,
+                    const double* __restrict__ u, int* __restrict__ out) {
+  __shared__ unsigned int hist[2048];
+  __shared__ unsigned int s_prefix, s_mask, s_remaining, s_nan;
+  __shared__ float s_maxf[CAND_THREADS / 32];
+  __shared__ double s_red[CAND_THREADS];
+  __shared__ int s_choice;
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  if (tid == 0) { s_prefix = 0u; s_mask = 0u; s_remaining = (unsigned)k; s_nan = 0u; s_choice = -1; }
+  __syncthreads();
+
+  float mx = -INFINITY;
+  bool nan = false;
+  for (int i = tid; i < vocab; i += CAND_THREADS) {
+    const float v = row[i];
+    nan |= (v != v);
+    mx = fmaxf(mx, v);
+  }
+  mx = nb_warp_max(mx);
+  if (nan) s_nan = 1u;
+  if ((tid & 31) == 0) s_maxf[tid >> 5] = mx;
+  __syncthreads();
+  if (s_nan) {
+    if (tid == 0) out[r] = -1;
+    return;
+  }
+  mx = s_maxf[0];
+  for (int w = 1; w < CAND_THREADS / 32; ++w) mx = fmaxf(mx, s_maxf[w]);
+  if (!isfinite(mx)) {   // all -inf, or a +inf: the reference takes the first maximum
+    if (tid == 0) {
+      int best = 0;
+      for (int i = 1; i < vocab; ++i)
+        if (row[i] > row[best]) best = i;
+      out[r] = best;
+    }
+    return;
+  }
+
+  unsigned int threshold = 0u;   // keys at or above it are kept; 0 keeps everything
+  if (k < vocab) {
+    const int shifts[3] = {21, 10, 0};
+    const int bits[3] = {11, 11, 10};
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = shifts[pass];
+      const unsigned int nb = 1u << bits[pass];
+      for (int i = tid; i < 2048; i += CAND_THREADS) hist[i] = 0u;
+      __syncthreads();
+      const unsigned int prefix = s_prefix, mask = s_mask;
+      for (int i = tid; i < vocab; i += CAND_THREADS) {
+        const unsigned int key = order_key(row[i]);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & (nb - 1u)], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {   // from the largest bin down: the bin that holds the k-th largest
+        unsigned int need = s_remaining, b = nb;
+        while (b > 0u) {
+          --b;
+          if (hist[b] >= need) break;
+          need -= hist[b];
+        }
+        s_remaining = need;
+        s_prefix = prefix | (b << shift);
+        s_mask = mask | ((nb - 1u) << shift);
+      }
+      __syncthreads();
+    }
+    threshold = s_prefix;
+  }
+
+  const double temp = fmax((double)temperature, 1e-6);
+  const double mxd = (double)mx / temp;
+  const int per = (vocab + CAND_THREADS - 1) / CAND_THREADS;
+  const int i0 = min(tid * per, vocab), i1 = min(i0 + per, vocab);
+  double seg = 0.0;
+  for (int i = i0; i < i1; ++i)
+    if (order_key(row[i]) >= threshold) seg += exp((double)row[i] / temp - mxd);
+  s_red[tid] = seg;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int t = 0; t < CAND_THREADS; ++t) total += s_red[t];
+    if (!isfinite(total) || total <= 0.0) {
+      s_choice = -2;   // the reference returns token 0
+    } else {
+      double rem = u[r] * total;
+      int t = 0;
+      while (t < CAND_THREADS - 1 && rem - s_red[t] > 0.0) { rem -= s_red[t]; ++t; }   // whole pieces
+      s_choice = t;
+      s_red[0] = rem;
+    }
+  }
+  __syncthreads();
+  if (s_choice == -2) {
+    if (tid == 0) out[r] = 0;
+    return;
+  }
+  if (tid == s_choice) {
+    double rem = s_red[0];
+    int pick = -1, last_kept = -1;
+    for (int i = i0; i < vocab; ++i) {   // may run past the piece on rounding
+      if (order_key(row[i]) < threshold) continue;
+      last_kept = i;
+      rem -= exp((double)row[i] / temp - mxd);
+      if (rem <= 0.0) { pick = i; break; }
+    }
+    if (pick < 0) {   // rounding left a remainder after the last token: the last one kept
+      pick = last_kept;
+      for (int i = i0 - 1; pick < 0 && i >= 0; --i)
+        if (order_key(row[i]) >= threshold) pick = i;
+    }
+    out[r] = pick;
+  }
+}
+
 }  // namespace
 
 // n_keep <= cap.  out_val / out_idx: [n_rows, cap]; out_count: [n_rows]; out_stats: [n_rows, 2]
@@ -309,6 +433,18 @@ NB_EXPORT int nb_top_candidates(const float* logits, int n_rows, int vocab, int 
   top_candidates_kernel<<<n_rows, CAND_THREADS, 0, stream>>>(logits, vocab, n_keep, cap, temp, out_val,
                                                              out_idx, out_count, out_stats);
   NB_CHECK_LAUNCH("top_candidates");
+  return 0;
+}
+
+// 1 <= k; k >= vocab keeps the whole row.  u: one f64 in [0, 1) per row; out: the token, or -1
+// for a row with a NaN.
+NB_EXPORT int nb_sample_top_k(const float* logits, int n_rows, int vocab, int k, float temperature,
+                              const double* u, int* out, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0 && k >= 1, NB_ERR_BAD_ARG, "sample_top_k: bad sizes vocab=%d k=%d", vocab, k);
+  NB_CUDA(nb_launch(sample_top_k_kernel, dim3(n_rows), dim3(CAND_THREADS), 0, stream, logits, vocab, k,
+                    temperature, u, out));
+  NB_CHECK_LAUNCH("sample_top_k");
   return 0;
 }
 

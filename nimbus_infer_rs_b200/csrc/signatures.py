@@ -39,6 +39,7 @@ SIGNATURES = {
     "nb_argmax_split": "piipppip",
     "nb_argmax": "piipp",
     "nb_sample_temperature": "piifppp",
+    "nb_sample_top_k": "piiifppp",
 }
 
 _CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}

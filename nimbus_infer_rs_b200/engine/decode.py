@@ -43,7 +43,9 @@ class DecodeSession:
         # The device buffers and the recorded step are kept by the engine between batches of
         # the same size and sampling mode: a new batch fills the buffers again and replays the
         # graph it finds, instead of recording one of its own.
-        self._key = (n, self.params.greedy, float(self.params.temperature) if not self.params.greedy else 0.0)
+        self._key = (n, self.params.greedy,
+                     float(self.params.temperature) if not self.params.greedy else 0.0,
+                     int(self.params.top_k) if not self.params.greedy else 0)
         kept = engine.decode_states.pop(self._key, None) if self.use_graph else None
         if kept is not None:
             self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u = kept["buffers"]
@@ -65,8 +67,10 @@ class DecodeSession:
         self._stage = None
         self._out_stage = None
         if self.params.repetition_penalty != 1.0 or (
-                not self.params.greedy and (self.params.top_k > 0 or self.params.top_p < 1.0)):
-            raise ValueError("a decode session selects tokens greedily or by temperature only")
+                not self.params.greedy and (self.params.top_p < 1.0 or (
+                    self.params.top_k > 0 and not hasattr(engine.ops, "sample_top_k")))):
+            raise ValueError("a decode session selects tokens greedily, by temperature or among "
+                             "the k largest logits only")
 
     # ------------------------------------------------------------------ one step
     def _layout(self) -> BatchLayout:
@@ -86,6 +90,9 @@ class DecodeSession:
         self.logits = eng.model.forward(ctx)
         if self.params.greedy:
             eng.ops.argmax(self.logits, self.next_tokens)
+        elif self.params.top_k > 0:
+            eng.ops.sample_top_k(self.logits, self.params.top_k, float(self.params.temperature),
+                                 self.u, self.next_tokens)
         else:
             eng.ops.sample_temperature(self.logits, float(self.params.temperature), self.u,
                                        self.next_tokens)
@@ -149,7 +156,11 @@ class DecodeSession:
             self._out_np = self._out_stage.numpy()
         self._out_stage.copy_(self.next_tokens, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return self._out_np.tolist()
+        tokens = self._out_np.tolist()
+        if self.params.top_k > 0 and not self.params.greedy and any(
+                t < 0 for t, alive in zip(tokens, self.live) if alive):
+            raise ValueError("a row of logits holds a NaN: no token can be drawn from it")
+        return tokens
 
     def retire(self, index: int) -> None:
         """Sequence ``index`` of the session has ended: its row becomes padding."""

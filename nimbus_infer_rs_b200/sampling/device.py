@@ -1,8 +1,8 @@
 """Token selection for a batch of logits on the device.
 
-Greedy decoding, temperature sampling and the repetition penalty run as kernels; the random
-number of each draw comes from the sequence's own host generator so that results do not
-depend on batching.  With top-k or top-p filtering on, a kernel picks each row's largest
+Greedy decoding, temperature sampling, top-k sampling and the repetition penalty run as
+kernels; the random number of each draw comes from the sequence's own host generator so that
+results do not depend on batching.  With top-p filtering on, a kernel picks each row's largest
 logits and the float64 restatement of the reference's sampler decides among them on the host
 (sampling/host.py); a row that these cannot settle is brought to the host whole.
 """
@@ -30,6 +30,16 @@ def _pool():
     return _POOL
 
 
+class _Drawn:
+    """A generator that hands out one number that was drawn before."""
+
+    def __init__(self, value: float):
+        self.value = value
+
+    def next_f64(self) -> float:
+        return self.value
+
+
 class SequenceSampler:
     """Per-sequence sampling state: generator and generated history."""
 
@@ -47,8 +57,12 @@ class BatchSampler:
         self.device = device
 
     def needs_host(self) -> bool:
+        """Top-p needs the host's float64 sampler; top-k alone is a kernel (where the backend
+        has it)."""
         p = self.params
-        return (not p.greedy) and (p.top_k > 0 or p.top_p < 1.0)
+        if p.greedy:
+            return False
+        return p.top_p < 1.0 or (p.top_k > 0 and not hasattr(self.ops, "sample_top_k"))
 
     #: candidates the device hands to the host's sampler when top-k / top-p is on
     N_CANDIDATES = 1024
@@ -126,10 +140,17 @@ class BatchSampler:
             if p.greedy:
                 self.ops.argmax(logits, ids)
             else:
-                u = torch.tensor([s.rng.next_f64() for s in seqs], dtype=torch.float64)
-                self.ops.sample_temperature(logits, float(p.temperature),
-                                            u.to(logits.device), ids)
+                us = [s.rng.next_f64() for s in seqs]
+                u = torch.tensor(us, dtype=torch.float64).to(logits.device)
+                if p.top_k > 0:
+                    self.ops.sample_top_k(logits, p.top_k, float(p.temperature), u, ids)
+                else:
+                    self.ops.sample_temperature(logits, float(p.temperature), u, ids)
             out = ids.to("cpu").tolist()
+            for i, t in enumerate(out):
+                if t < 0:   # a row with a NaN: the host decides, with the number already drawn
+                    row = logits[i].detach().to("cpu").numpy()
+                    out[i] = host_sampler.sample(row, p, [], _Drawn(us[i]))
         for s, t in zip(seqs, out):
             s.generated.append(int(t))
         return [int(t) for t in out]

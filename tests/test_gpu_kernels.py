@@ -413,6 +413,43 @@ def test_temperature_sampling_matches_the_host_sampler(ops):
     assert int(o) == 0
 
 
+@pytest.mark.parametrize("V, k", [(1000, 1), (1000, 40), (777, 776), (777, 777), (513, 5000),
+                                  (50257, 50), (4099, 2000)])
+def test_top_k_sampling_matches_the_host_sampler(ops, V, k):
+    """Top-k sampling on the device against the float64 sampler of the host, draw for draw:
+    ties at the k-th value, rows with -inf entries, k at and beyond the vocabulary, tiny and
+    large temperatures; a row with a NaN is handed back (-1)."""
+    from nimbus_infer_rs_b200.sampling import SamplingParams, Xoshiro256pp
+    from nimbus_infer_rs_b200.sampling import host as H
+    torch.manual_seed(V + k)
+    n = 24
+    logits = torch.randn(n, V, device=DEV) * 3
+    logits[1, 5:25] = logits[1].max()                       # ties at the top
+    kth = logits[2].topk(min(k, V)).values[-1]
+    logits[2, :7] = kth                                     # ties at the threshold
+    logits[3, ::3] = -float("inf")
+    logits[4] = torch.round(logits[4])                      # many equal values
+    logits[5, 10] = 0.0
+    logits[5, 11] = -0.0
+    for temp in (0.7, 1.0, 1e-9, 30.0):
+        rngs = [Xoshiro256pp(7 + i) for i in range(n)]
+        u = torch.tensor([r.next_f64() for r in rngs], dtype=torch.float64, device=DEV)
+        out = torch.empty(n, device=DEV, dtype=torch.int32)
+        ops.sample_top_k(logits, k, temp, u, out)
+        rngs = [Xoshiro256pp(7 + i) for i in range(n)]
+        p = SamplingParams(temperature=temp, top_k=k)
+        want = [H.sample(logits[i].cpu().numpy(), p, [], rngs[i]) for i in range(n)]
+        assert out.cpu().tolist() == want, temp
+    bad = logits[:2].clone()
+    bad[1, 3] = float("nan")
+    out = torch.empty(2, device=DEV, dtype=torch.int32)
+    ops.sample_top_k(bad, k, 1.0, torch.tensor([0.5, 0.5], dtype=torch.float64, device=DEV), out)
+    assert int(out[1]) == -1 and int(out[0]) >= 0
+    ops.sample_top_k(torch.full((1, 9), -float("inf"), device=DEV), k, 1.0,
+                     torch.tensor([0.3], dtype=torch.float64, device=DEV), out[:1])
+    assert int(out[0]) == 0
+
+
 def test_repetition_penalty(ops):
     logits = torch.tensor([[2.0, -2.0, 1.0, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
     hist = torch.tensor([[0, 1, 1, 0], [3, -1, -1, -1]], device=DEV, dtype=torch.int32)
