@@ -373,6 +373,21 @@ class CudaBackend:
         self._call("nb_sample_top_k", _ptr(logits), n, v, int(k), float(temperature), _ptr(u),
                    _ptr(out), self._stream())
 
+    def top_p_max_k(self) -> int:
+        """The largest top-k that :meth:`sample_top_p` takes together with top-p."""
+        return int(self.lib.nb_sample_top_p_max_k())
+
+    def sample_top_p(self, logits, k, top_p, temperature, u, out):
+        """Top-p sampling (with top-k ``k``, 0 = off) on the device.  ``out[r]`` is the token,
+        -1 for a row with a NaN, -2 for a row whose cut lies beyond the thousand largest logits
+        (a flat distribution): those the caller settles on the host."""
+        _check(logits, "logits", torch.float32, 2)
+        _check(u, "u", torch.float64, 1)
+        _check(out, "out", torch.int32, 1)
+        n, v = logits.shape
+        self._call("nb_sample_top_p", _ptr(logits), n, v, int(k), float(top_p), float(temperature),
+                   _ptr(u), _ptr(out), self._stream())
+
     def top_candidates(self, logits, n_keep, temp):
         """The ``n_keep`` largest logits of every row with their indices (plus ties at the
         threshold, up to ``n_keep + 32``), the row maximum and the f64 sum of

@@ -420,6 +420,239 @@ sample_top_k_kernel(const float* __restrict__ logits, int vocab, int k, float te
   }
 }
 
+// Top-p sampling, with or without top-k (k <= TOPP_KEEP), on the device
+// (src/sampler.rs:103-160, then :181-215).  The reference sorts the row in descending order
+// (ties by index), walks the cumulative probability and drops a token when the mass before it
+// minus its own exceeds p; both filters keep a prefix of that order.  Here the TOPP_KEEP largest
+// logits are picked out by radix selection, sorted in shared memory (bitonic, value descending
+// and index ascending in one 64-bit key), and one thread walks them as the reference does, in
+// f64 and in the same order.  The last token kept defines the kept set for the whole row (a
+// larger key, or the same value and no larger index), over which the draw then runs in index
+// order as in the kernels above.  When the cut cannot be settled from the candidates (a flat
+// distribution: more than TOPP_KEEP tokens survive) the row gets -2 and the caller decides on the
+// host; a row with a NaN gets -1.
+constexpr int TOPP_KEEP = 1024;
+constexpr int TOPP_CAP = 2048;    // candidates the sort has room for (ties at the threshold)
+
+__device__ __forceinline__ unsigned long long cand_key(float v, int i) {
+  return ((unsigned long long)order_key(v) << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+}
+__device__ __forceinline__ float key_value(unsigned long long c) {
+  const unsigned int k = (unsigned int)(c >> 32);
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+__global__ void __launch_bounds__(CAND_THREADS)
+sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float top_p, float temperature,
+                    const double* __restrict__ u, int* __restrict__ out) {
+  __shared__ unsigned int hist[2048];
+  __shared__ unsigned long long cand[TOPP_CAP];
+  __shared__ unsigned int s_prefix, s_mask, s_remaining, s_nan, s_count;
+  __shared__ float s_maxf[CAND_THREADS / 32];
+  __shared__ double s_red[CAND_THREADS];
+  __shared__ unsigned long long s_last_kept;
+  __shared__ int s_choice;
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const int n_keep = min(TOPP_KEEP, vocab);
+  if (tid == 0) {
+    s_prefix = 0u; s_mask = 0u; s_remaining = (unsigned)n_keep; s_nan = 0u; s_count = 0u;
+    s_choice = -1;
+  }
+  __syncthreads();
+
+  float mx = -INFINITY;
+  bool nan = false;
+  for (int i = tid; i < vocab; i += CAND_THREADS) {
+    const float v = row[i];
+    nan |= (v != v);
+    mx = fmaxf(mx, v);
+  }
+  mx = nb_warp_max(mx);
+  if (nan) s_nan = 1u;
+  if ((tid & 31) == 0) s_maxf[tid >> 5] = mx;
+  __syncthreads();
+  if (s_nan) {
+    if (tid == 0) out[r] = -1;
+    return;
+  }
+  mx = s_maxf[0];
+  for (int w = 1; w < CAND_THREADS / 32; ++w) mx = fmaxf(mx, s_maxf[w]);
+  if (!isfinite(mx)) {   // all -inf, or a +inf: the reference takes the first maximum
+    if (tid == 0) {
+      int best = 0;
+      for (int i = 1; i < vocab; ++i)
+        if (row[i] > row[best]) best = i;
+      out[r] = best;
+    }
+    return;
+  }
+  const double temp = fmax((double)temperature, 1e-6);
+  const double mxd = (double)mx / temp;
+
+  // the softmax denominator over the whole row (used when top-k is off)
+  double sum = 0.0;
+  for (int i = tid; i < vocab; i += CAND_THREADS) sum += exp((double)row[i] / temp - mxd);
+  s_red[tid] = sum;
+
+  // the n_keep-th largest key, then every element that is not smaller into `cand`
+  {
+    const int shifts[3] = {21, 10, 0};
+    const int bits[3] = {11, 11, 10};
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = shifts[pass];
+      const unsigned int nb = 1u << bits[pass];
+      for (int i = tid; i < 2048; i += CAND_THREADS) hist[i] = 0u;
+      __syncthreads();
+      const unsigned int prefix = s_prefix, mask = s_mask;
+      for (int i = tid; i < vocab; i += CAND_THREADS) {
+        const unsigned int key = order_key(row[i]);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & (nb - 1u)], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned int need = s_remaining, b = nb;
+        while (b > 0u) {
+          --b;
+          if (hist[b] >= need) break;
+          need -= hist[b];
+        }
+        s_remaining = need;
+        s_prefix = prefix | (b << shift);
+        s_mask = mask | ((nb - 1u) << shift);
+      }
+      __syncthreads();
+    }
+  }
+  const unsigned int threshold = s_prefix;
+  for (int i = tid; i < TOPP_CAP; i += CAND_THREADS) cand[i] = 0ull;
+  __syncthreads();
+  for (int i = tid; i < vocab; i += CAND_THREADS) {
+    const float v = row[i];
+    if (order_key(v) >= threshold) {
+      const unsigned int pos = atomicAdd(&s_count, 1u);
+      if (pos < (unsigned)TOPP_CAP) cand[pos] = cand_key(v, i);
+    }
+  }
+  __syncthreads();
+  const int n = (int)s_count;
+  if (n > TOPP_CAP) {   // more ties at the threshold than the sort has room for
+    if (tid == 0) out[r] = -2;
+    return;
+  }
+  // bitonic sort, descending (empty places are zero: they end up last)
+  for (int size = 2; size <= TOPP_CAP; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = tid; t < TOPP_CAP / 2; t += CAND_THREADS) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool down = (lo & size) == 0;   // this run is sorted descending
+        const unsigned long long a = cand[lo], b = cand[hi];
+        if ((a < b) == down) {
+          cand[lo] = b;
+          cand[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  if (tid == 0) {
+    double row_sum = 0.0;
+    for (int t = 0; t < CAND_THREADS; ++t) row_sum += s_red[t];
+    // the universe the probabilities are taken over: the row, or what top-k leaves of it
+    int m = n;
+    bool complete = (n == vocab);   // every token of the universe is among the candidates
+    double S = row_sum;
+    if (k > 0 && k < vocab) {
+      const int kk = min(k, n);
+      const unsigned int kth = (unsigned int)(cand[kk - 1] >> 32);
+      m = kk;
+      while (m < n && (unsigned int)(cand[m] >> 32) == kth) ++m;   // ties at the k-th stay
+      complete = true;   // all of them are at or above the candidates' threshold: none is missing
+      S = 0.0;
+      for (int j = 0; j < m; ++j) S += exp((double)key_value(cand[j]) / temp - mxd);
+    }
+    int kept = -1;
+    if (!(S > 0.0) || !isfinite(S)) {
+      kept = -3;   // the reference's draw returns token 0 when the total is not a positive number
+    } else if (top_p <= 0.0f) {
+      kept = 1;    // the first maximum alone
+    } else {
+      const double p = (double)top_p;
+      double cum = 0.0, prob = 0.0;
+      for (int j = 0; j < m; ++j) {
+        prob = exp((double)key_value(cand[j]) / temp - mxd) / S;
+        if (cum - prob > p) { kept = j; break; }
+        cum += prob;
+      }
+      if (kept < 0) {
+        // nobody among the candidates is dropped.  A token outside them weighs no more than the
+        // last candidate: it is dropped for sure if even that weight would be.
+        if (complete || cum - prob > p) kept = m;
+        else kept = -2;
+      }
+    }
+    if (kept == -2) {
+      out[r] = -2;
+      s_choice = -3;
+    } else if (kept == -3) {
+      out[r] = 0;
+      s_choice = -3;
+    } else {
+      s_last_kept = cand[kept - 1];
+    }
+  }
+  __syncthreads();
+  if (s_choice == -3) return;
+  const unsigned long long last_kept = s_last_kept;
+
+  const int per = (vocab + CAND_THREADS - 1) / CAND_THREADS;
+  const int i0 = min(tid * per, vocab), i1 = min(i0 + per, vocab);
+  double seg = 0.0;
+  for (int i = i0; i < i1; ++i)
+    if (cand_key(row[i], i) >= last_kept) seg += exp((double)row[i] / temp - mxd);
+  __syncthreads();
+  s_red[tid] = seg;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int t = 0; t < CAND_THREADS; ++t) total += s_red[t];
+    if (!isfinite(total) || total <= 0.0) {
+      s_choice = -2;
+    } else {
+      double rem = u[r] * total;
+      int t = 0;
+      while (t < CAND_THREADS - 1 && rem - s_red[t] > 0.0) { rem -= s_red[t]; ++t; }
+      s_choice = t;
+      s_red[0] = rem;
+    }
+  }
+  __syncthreads();
+  if (s_choice == -2) {
+    if (tid == 0) out[r] = 0;
+    return;
+  }
+  if (tid == s_choice) {
+    double rem = s_red[0];
+    int pick = -1, last = -1;
+    for (int i = i0; i < vocab; ++i) {
+      if (cand_key(row[i], i) < last_kept) continue;
+      last = i;
+      rem -= exp((double)row[i] / temp - mxd);
+      if (rem <= 0.0) { pick = i; break; }
+    }
+    if (pick < 0) {
+      pick = last;
+      for (int i = i0 - 1; pick < 0 && i >= 0; --i)
+        if (cand_key(row[i], i) >= last_kept) pick = i;
+    }
+    out[r] = pick;
+  }
+}
+
 }  // namespace
 
 // n_keep <= cap.  out_val / out_idx: [n_rows, cap]; out_count: [n_rows]; out_stats: [n_rows, 2]
@@ -445,6 +678,22 @@ NB_EXPORT int nb_sample_top_k(const float* logits, int n_rows, int vocab, int k,
   NB_CUDA(nb_launch(sample_top_k_kernel, dim3(n_rows), dim3(CAND_THREADS), 0, stream, logits, vocab, k,
                     temperature, u, out));
   NB_CHECK_LAUNCH("sample_top_k");
+  return 0;
+}
+
+// The most top-k that nb_sample_top_p takes together with top-p (0 = top-k off).
+NB_EXPORT int nb_sample_top_p_max_k() { return TOPP_KEEP; }
+
+// k = 0: top-p alone; else 1 <= k <= nb_sample_top_p_max_k().  out: the token; -1 for a row with
+// a NaN, -2 for a row whose cut lies beyond the candidates (the caller decides on the host).
+NB_EXPORT int nb_sample_top_p(const float* logits, int n_rows, int vocab, int k, float top_p,
+                              float temperature, const double* u, int* out, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(vocab > 0 && k >= 0 && k <= TOPP_KEEP, NB_ERR_BAD_ARG,
+             "sample_top_p: bad sizes vocab=%d k=%d (at most %d)", vocab, k, TOPP_KEEP);
+  NB_CUDA(nb_launch(sample_top_p_kernel, dim3(n_rows), dim3(CAND_THREADS), 0, stream, logits, vocab, k,
+                    top_p, temperature, u, out));
+  NB_CHECK_LAUNCH("sample_top_p");
   return 0;
 }
 

@@ -40,6 +40,8 @@ SIGNATURES = {
     "nb_argmax": "piipp",
     "nb_sample_temperature": "piifppp",
     "nb_sample_top_k": "piiifppp",
+    "nb_sample_top_p": "piiiffppp",
+    "nb_sample_top_p_max_k": "",
 }
 
 _CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}

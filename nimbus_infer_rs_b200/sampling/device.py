@@ -2,9 +2,11 @@
 
 Greedy decoding, temperature sampling, top-k sampling and the repetition penalty run as
 kernels; the random number of each draw comes from the sequence's own host generator so that
-results do not depend on batching.  With top-p filtering on, a kernel picks each row's largest
-logits and the float64 restatement of the reference's sampler decides among them on the host
-(sampling/host.py); a row that these cannot settle is brought to the host whole.
+results do not depend on batching.  Top-p sampling is a kernel as well; it hands back the rows
+whose cut lies beyond their thousand largest logits (and rows with a NaN), and those the float64
+restatement of the reference's sampler settles on the host (sampling/host.py), with the number
+that was already drawn.  The older way (the device picks each row's largest logits, the host
+decides among them) is kept for logits on the host and for a top-k beyond the kernel's room.
 """
 from __future__ import annotations
 
@@ -63,6 +65,13 @@ class BatchSampler:
         if p.greedy:
             return False
         return p.top_p < 1.0 or (p.top_k > 0 and not hasattr(self.ops, "sample_top_k"))
+
+    def _device_top_p(self) -> bool:
+        """Top-p (with a top-k the kernel has room for) is decided on the device; rows it cannot
+        settle come back marked."""
+        p = self.params
+        return (not p.greedy) and p.top_p < 1.0 and hasattr(self.ops, "sample_top_p") \
+            and p.top_k <= self.ops.top_p_max_k()
 
     #: candidates the device hands to the host's sampler when top-k / top-p is on
     N_CANDIDATES = 1024
@@ -123,7 +132,7 @@ class BatchSampler:
         p = self.params
         n = logits.shape[0]
         assert n == len(seqs)
-        if self.needs_host():
+        if self.needs_host() and not (logits.is_cuda and self._device_top_p()):
             out = self._filtered(logits, seqs)
         else:
             if p.repetition_penalty != 1.0 and any(s.generated for s in seqs):
@@ -142,15 +151,29 @@ class BatchSampler:
             else:
                 us = [s.rng.next_f64() for s in seqs]
                 u = torch.tensor(us, dtype=torch.float64).to(logits.device)
-                if p.top_k > 0:
+                if p.top_p < 1.0:
+                    self.ops.sample_top_p(logits, p.top_k, float(np.float32(p.top_p)),
+                                          float(p.temperature), u, ids)
+                elif p.top_k > 0:
                     self.ops.sample_top_k(logits, p.top_k, float(p.temperature), u, ids)
                 else:
                     self.ops.sample_temperature(logits, float(p.temperature), u, ids)
             out = ids.to("cpu").tolist()
-            for i, t in enumerate(out):
-                if t < 0:   # a row with a NaN: the host decides, with the number already drawn
-                    row = logits[i].detach().to("cpu").numpy()
-                    out[i] = host_sampler.sample(row, p, [], _Drawn(us[i]))
+            todo = [i for i, t in enumerate(out) if t < 0]
+            if todo:
+                # rows the kernel handed back (a NaN; a cut beyond the largest thousand logits):
+                # the host decides on the whole row, with the number already drawn and the
+                # penalty already applied; a thread per row
+                sel = logits.detach() if len(todo) == n else logits.detach()[
+                    torch.tensor(todo, device=logits.device)]
+                rows = sel.to("cpu").numpy()
+                plain = SamplingParams(temperature=p.temperature, top_k=p.top_k, top_p=p.top_p)
+
+                def one(j):
+                    return host_sampler.sample(rows[j], plain, [], _Drawn(us[todo[j]]))
+                results = [one(0)] if len(todo) == 1 else list(_pool().map(one, range(len(todo))))
+                for j, i in enumerate(todo):
+                    out[i] = results[j]
         for s, t in zip(seqs, out):
             s.generated.append(int(t))
         return [int(t) for t in out]

@@ -450,6 +450,50 @@ def test_top_k_sampling_matches_the_host_sampler(ops, V, k):
     assert int(out[0]) == 0
 
 
+@pytest.mark.parametrize("V, k, top_p", [(1000, 0, 0.9), (1000, 40, 0.5), (777, 0, 0.0), (513, 0, 0.3),
+                                         (50257, 0, 0.9), (50257, 1024, 0.95), (4099, 7, 0.999),
+                                         (300, 299, 0.7), (50257, 0, 0.5)])
+def test_top_p_sampling_matches_the_host_sampler(ops, V, k, top_p):
+    """Top-p (and top-k with it) on the device against the float64 sampler of the host, draw for
+    draw: peaked rows (the cut among the first few tokens), ties across the cut, rows with -inf,
+    a flat row (handed back: -2, unless the vocabulary is small enough to be listed whole) and a
+    row with a NaN (-1)."""
+    from nimbus_infer_rs_b200.sampling import SamplingParams, Xoshiro256pp
+    from nimbus_infer_rs_b200.sampling import host as H
+    torch.manual_seed(V + k)
+    n = 24
+    logits = torch.randn(n, V, device=DEV) * 4
+    logits[1, 5:25] = logits[1].max()                       # ties at the top, across the cut
+    logits[2, 100:103] = logits[2].max() + 6.0              # three tokens hold nearly all the mass
+    logits[3, ::3] = -float("inf")
+    logits[4] = torch.round(logits[4])                      # many equal values
+    logits[5] = logits[5] * 0.001                           # flat
+    logits[6, 7] = logits[6].max() + 30.0                   # one token alone
+    handed_back = 0
+    for temp in (0.7, 1.0, 2.5):
+        rngs = [Xoshiro256pp(7 + i) for i in range(n)]
+        u = torch.tensor([r.next_f64() for r in rngs], dtype=torch.float64, device=DEV)
+        out = torch.empty(n, device=DEV, dtype=torch.int32)
+        ops.sample_top_p(logits, k, top_p, temp, u, out)
+        got = out.cpu().tolist()
+        rngs = [Xoshiro256pp(7 + i) for i in range(n)]
+        p = SamplingParams(temperature=temp, top_k=k, top_p=top_p)
+        for i in range(n):
+            want = H.sample(logits[i].cpu().numpy(), p, [], rngs[i])
+            if got[i] == -2:
+                handed_back += 1
+                continue
+            assert got[i] == want, (temp, i)
+    assert handed_back <= 3 * n // 2                        # most rows are settled on the device
+    if V <= 1024 or (0 < k <= 1024):
+        assert handed_back == 0                             # the universe is listed whole
+    bad = logits[:2].clone()
+    bad[1, 3] = float("nan")
+    out = torch.empty(2, device=DEV, dtype=torch.int32)
+    ops.sample_top_p(bad, k, top_p, 1.0, torch.tensor([0.5, 0.5], dtype=torch.float64, device=DEV), out)
+    assert int(out[1]) == -1 and int(out[0]) != -1
+
+
 def test_repetition_penalty(ops):
     logits = torch.tensor([[2.0, -2.0, 1.0, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
     hist = torch.tensor([[0, 1, 1, 0], [3, -1, -1, -1]], device=DEV, dtype=torch.int32)
