@@ -445,7 +445,8 @@ __device__ __forceinline__ float key_value(unsigned long long c) {
 __global__ void __launch_bounds__(CAND_THREADS)
 sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float top_p, float temperature,
                     const double* __restrict__ u, int* __restrict__ out) {
-  __shared__ unsigned int hist[2048];
+  __shared__ double weight[TOPP_CAP];   // exp((x - max) / temp) of the sorted candidates ...
+  unsigned int* hist = reinterpret_cast<unsigned int*>(weight);   // ... after the histograms
   __shared__ unsigned long long cand[TOPP_CAP];
   __shared__ unsigned int s_prefix, s_mask, s_remaining, s_nan, s_count;
   __shared__ float s_maxf[CAND_THREADS / 32];
@@ -559,6 +560,9 @@ sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float to
     }
   }
 
+  // the candidates' weights, by everybody: the walk below is then additions only
+  for (int j = tid; j < n; j += CAND_THREADS) weight[j] = exp((double)key_value(cand[j]) / temp - mxd);
+  __syncthreads();
   if (tid == 0) {
     double row_sum = 0.0;
     for (int t = 0; t < CAND_THREADS; ++t) row_sum += s_red[t];
@@ -573,7 +577,7 @@ sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float to
       while (m < n && (unsigned int)(cand[m] >> 32) == kth) ++m;   // ties at the k-th stay
       complete = true;   // all of them are at or above the candidates' threshold: none is missing
       S = 0.0;
-      for (int j = 0; j < m; ++j) S += exp((double)key_value(cand[j]) / temp - mxd);
+      for (int j = 0; j < m; ++j) S += weight[j];
     }
     int kept = -1;
     if (!(S > 0.0) || !isfinite(S)) {
@@ -584,7 +588,7 @@ sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float to
       const double p = (double)top_p;
       double cum = 0.0, prob = 0.0;
       for (int j = 0; j < m; ++j) {
-        prob = exp((double)key_value(cand[j]) / temp - mxd) / S;
+        prob = weight[j] / S;
         if (cum - prob > p) { kept = j; break; }
         cum += prob;
       }
