@@ -45,7 +45,8 @@ class DecodeSession:
         # graph it finds, instead of recording one of its own.
         self._key = (n, self.params.greedy,
                      float(self.params.temperature) if not self.params.greedy else 0.0,
-                     int(self.params.top_k) if not self.params.greedy else 0)
+                     int(self.params.top_k) if not self.params.greedy else 0,
+                     float(self.params.top_p) if not self.params.greedy else 1.0)
         kept = engine.decode_states.pop(self._key, None) if self.use_graph else None
         if kept is not None:
             self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u = kept["buffers"]
@@ -66,11 +67,15 @@ class DecodeSession:
         self.tokens, self.row_pos, self.row_slot = buf[:n], buf[n:2 * n], buf[2 * n:]
         self._stage = None
         self._out_stage = None
-        if self.params.repetition_penalty != 1.0 or (
-                not self.params.greedy and (self.params.top_p < 1.0 or (
-                    self.params.top_k > 0 and not hasattr(engine.ops, "sample_top_k")))):
-            raise ValueError("a decode session selects tokens greedily, by temperature or among "
-                             "the k largest logits only")
+        p = self.params
+        on_device = p.greedy or (
+            (p.top_p >= 1.0 or (hasattr(engine.ops, "sample_top_p")
+                                and p.top_k <= engine.ops.top_p_max_k()))
+            and (p.top_k == 0 or hasattr(engine.ops, "sample_top_k")))
+        if p.repetition_penalty != 1.0 or not on_device:
+            raise ValueError("a decode session selects tokens with the sampling kernels only "
+                             "(no repetition penalty; top-k within the top-p kernel's room)")
+        self.last_u: list[float] = []
 
     # ------------------------------------------------------------------ one step
     def _layout(self) -> BatchLayout:
@@ -90,6 +95,9 @@ class DecodeSession:
         self.logits = eng.model.forward(ctx)
         if self.params.greedy:
             eng.ops.argmax(self.logits, self.next_tokens)
+        elif self.params.top_p < 1.0:
+            eng.ops.sample_top_p(self.logits, self.params.top_k, float(np.float32(self.params.top_p)),
+                                 float(self.params.temperature), self.u, self.next_tokens)
         elif self.params.top_k > 0:
             eng.ops.sample_top_k(self.logits, self.params.top_k, float(self.params.temperature),
                                  self.u, self.next_tokens)
@@ -122,6 +130,7 @@ class DecodeSession:
             us = [self.seq_samplers[i].rng.next_f64() if alive else 0.0
                   for i, alive in enumerate(self.live)]
             self.u.copy_(torch.tensor(us, dtype=torch.float64), non_blocking=False)
+            self.last_u = us
         if not self.use_graph or self._steps == 0:
             self._device_step()            # the first step runs plainly and warms the kernels
         else:
@@ -157,9 +166,26 @@ class DecodeSession:
         self._out_stage.copy_(self.next_tokens, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         tokens = self._out_np.tolist()
-        if self.params.top_k > 0 and not self.params.greedy and any(
-                t < 0 for t, alive in zip(tokens, self.live) if alive):
-            raise ValueError("a row of logits holds a NaN: no token can be drawn from it")
+        if any(t < 0 for t, alive in zip(tokens, self.live) if alive):
+            tokens = self._settle_on_host(tokens)
+        return tokens
+
+    def _settle_on_host(self, tokens: list[int]) -> list[int]:
+        """Rows the sampling kernel handed back (a cut of top-p beyond the row's largest
+        thousand logits; a NaN): the host's sampler decides on the whole row with the number
+        that was drawn for this step.  The device keeps the mark in ``next_tokens``, so the
+        next step must be given its tokens from the host."""
+        from ..sampling import host as host_sampler
+        from ..sampling.device import _Drawn, _pool
+        todo = [i for i, t in enumerate(tokens) if t < 0 and self.live[i]]
+        rows = self.logits.detach()[torch.tensor(todo, device=self.logits.device)].to("cpu").numpy()
+
+        def one(j):
+            return int(host_sampler.sample(rows[j], self.params, [], _Drawn(self.last_u[todo[j]])))
+        results = [one(0)] if len(todo) == 1 else list(_pool().map(one, range(len(todo))))
+        for j, i in enumerate(todo):
+            tokens[i] = results[j]
+        self.host_settled = getattr(self, "host_settled", 0) + 1
         return tokens
 
     def retire(self, index: int) -> None:

@@ -59,19 +59,14 @@ class BatchSampler:
         self.device = device
 
     def needs_host(self) -> bool:
-        """Top-p needs the host's float64 sampler; top-k alone is a kernel (where the backend
-        has it)."""
+        """True if no kernel of the backend selects tokens with these options (a top-k beyond
+        the top-p kernel's room; a stand-in backend without the sampling kernels)."""
         p = self.params
         if p.greedy:
             return False
-        return p.top_p < 1.0 or (p.top_k > 0 and not hasattr(self.ops, "sample_top_k"))
-
-    def _device_top_p(self) -> bool:
-        """Top-p (with a top-k the kernel has room for) is decided on the device; rows it cannot
-        settle come back marked."""
-        p = self.params
-        return (not p.greedy) and p.top_p < 1.0 and hasattr(self.ops, "sample_top_p") \
-            and p.top_k <= self.ops.top_p_max_k()
+        if p.top_p < 1.0:
+            return not (hasattr(self.ops, "sample_top_p") and p.top_k <= self.ops.top_p_max_k())
+        return p.top_k > 0 and not hasattr(self.ops, "sample_top_k")
 
     #: candidates the device hands to the host's sampler when top-k / top-p is on
     N_CANDIDATES = 1024
@@ -132,7 +127,7 @@ class BatchSampler:
         p = self.params
         n = logits.shape[0]
         assert n == len(seqs)
-        if self.needs_host() and not (logits.is_cuda and self._device_top_p()):
+        if self.needs_host() or (not logits.is_cuda and not p.greedy and (p.top_k > 0 or p.top_p < 1.0)):
             out = self._filtered(logits, seqs)
         else:
             if p.repetition_penalty != 1.0 and any(s.generated for s in seqs):

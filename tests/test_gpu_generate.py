@@ -135,3 +135,33 @@ def test_top_k_and_top_p_from_the_largest_logits_equal_the_whole_row(model_dirs)
                 float(stats[i, 1]), p, SequenceSampler(p, i).rng, 1024)
             fast_rows += r is not None
     assert fast_rows >= 18                                   # most rows never leave the device whole
+
+
+@pytest.mark.parametrize("vocab", [512, 2500])
+def test_top_p_inside_the_decode_session_equals_the_host_sampler(vocab):
+    """Generation with top-p runs in the decode session (the sampling kernel inside the recorded
+    step).  With a vocabulary of 512 the kernel lists every token and settles each row; with
+    2,500 tokens and random weights the distribution is flat, the cut lies beyond the 1024
+    largest logits and the rows are handed back to the host each step.  Both ways the tokens are
+    the ones the host's sampler draws from the same logits."""
+    from nimbus_infer_rs_b200 import GPT2Config
+    from nimbus_infer_rs_b200.sampling import BatchSampler
+    # (one page of context, so that the session's step and a plain step run the same kernels on
+    # the same shapes and give the same bits)
+    cfg = GPT2Config.from_json(dict(model_type="gpt2", vocab_size=vocab, n_positions=64, n_embd=64,
+                                    n_layer=2, n_head=4, n_inner=128, layer_norm_epsilon=1e-5,
+                                    activation_function="gelu_new"))
+    e = Engine.random(cfg, seed=4, dtype="bfloat16", cache_tokens=1024)
+    prompts = [[5, 17, 3, 9], [11, 2], [7] * 9]
+    for kw in (dict(temperature=0.9, top_p=0.8), dict(temperature=1.2, top_k=50, top_p=0.95)):
+        p = SamplingParams(max_new_tokens=20, seed=5, **kw)
+        assert not BatchSampler(p, e.ops, e.rt.device).needs_host()
+        in_session = e.generate(prompts, p)
+        orig = BatchSampler.needs_host
+        BatchSampler.needs_host = lambda self: True          # the host decides every token
+        try:
+            on_host = e.generate(prompts, p)
+        finally:
+            BatchSampler.needs_host = orig
+        assert in_session == on_host, kw
+        assert [len(x) for x in in_session] == [20, 20, 20]
