@@ -76,6 +76,7 @@ class DecodeSession:
             raise ValueError("a decode session selects tokens with the sampling kernels only "
                              "(no repetition penalty; top-k within the top-p kernel's room)")
         self.last_u: list[float] = []
+        self._sampled = False      # a step of this session has selected tokens
 
     # ------------------------------------------------------------------ one step
     def _layout(self) -> BatchLayout:
@@ -117,6 +118,11 @@ class DecodeSession:
         grow = [(s, 1) for s, alive in zip(self.slots, self.live) if alive]
         if not grow:
             return
+        if tokens is None and self._sampled and not self.params.greedy and (
+                self.params.top_k > 0 or self.params.top_p < 1.0):
+            # the kernel may have handed a row back (a mark instead of a token on the device)
+            raise ValueError("with top-k or top-p a step takes its tokens from the host: pass "
+                             "what read_tokens() returned")
         if tokens is not None:
             if self._stage is None:
                 self._stage = torch.empty(self.n, dtype=torch.int32,
@@ -140,6 +146,7 @@ class DecodeSession:
             self._graph.replay()
             eng.ops.launches = launches + self._graph_launches
         self._steps += 1
+        self._sampled = True
         for s, _ in grow:
             cache.advance(s, 1)
 
