@@ -406,6 +406,15 @@ class CudaBackend:
                    _ptr(idx), _ptr(counts), _ptr(stats), self._stream())
         return vals, idx, counts, stats
 
+    def history_append(self, history, history_len, tokens, row_slot):
+        """history[r, history_len[r]] <- tokens[r], history_len[r] += 1 for live rows (a decode
+        session's record of what each sequence has generated)."""
+        _check(history, "history", torch.int32, 2)
+        for t, n in ((history_len, "history_len"), (tokens, "tokens"), (row_slot, "row_slot")):
+            _check(t, n, torch.int32, 1)
+        self._call("nb_history_append", _ptr(history), history.shape[1], _ptr(history_len),
+                   _ptr(tokens), _ptr(row_slot), tokens.numel(), self._stream())
+
     def repetition_penalty(self, logits, history, history_len, penalty):
         _check(logits, "logits", torch.float32, 2)
         _check(history, "history", torch.int32, 2)

@@ -33,6 +33,22 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
   }
 }
 
+// A decode session keeps each sequence's generated tokens on the device: the token a live row
+// runs in this step (the one selected in the step before) goes to the end of its history.
+__global__ void history_append_kernel(int* __restrict__ history, int history_stride,
+                                      int* __restrict__ history_len, const int* __restrict__ tokens,
+                                      const int* __restrict__ row_slot, int n) {
+  nb_launch_dependents();
+  nb_grid_dependency_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n || row_slot[i] < 0) return;
+  const int len = history_len[i];
+  if (len < history_stride) {
+    history[(size_t)i * history_stride + len] = tokens[i];
+    history_len[i] = len + 1;
+  }
+}
+
 // First index of the maximum: an element replaces the best only if it is strictly greater
 // (src/sampler.rs:173-179), so NaN never wins and ties go to the lower index.
 __global__ void __launch_bounds__(THREADS)
@@ -698,6 +714,17 @@ NB_EXPORT int nb_sample_top_p(const float* logits, int n_rows, int vocab, int k,
   NB_CUDA(nb_launch(sample_top_p_kernel, dim3(n_rows), dim3(CAND_THREADS), 0, stream, logits, vocab, k,
                     top_p, temperature, u, out));
   NB_CHECK_LAUNCH("sample_top_p");
+  return 0;
+}
+
+// history: [n_rows, history_stride]; a row whose history is full is left as it is.
+NB_EXPORT int nb_history_append(int* history, int history_stride, int* history_len, const int* tokens,
+                                const int* row_slot, int n_rows, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(history_stride >= 1, NB_ERR_BAD_ARG, "history_append: no room (stride %d)", history_stride);
+  NB_CUDA(nb_launch(history_append_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, history,
+                    history_stride, history_len, tokens, row_slot, n_rows));
+  NB_CHECK_LAUNCH("history_append");
   return 0;
 }
 

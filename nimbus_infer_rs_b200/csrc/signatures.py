@@ -35,6 +35,7 @@ SIGNATURES = {
     "nb_kv_append": "piiiipppppiiiiip",
     "nb_advance_decode": "ppppip",
     "nb_repetition_penalty": "piipipfp",
+    "nb_history_append": "pipppip",
     "nb_top_candidates": "piiiidppppp",
     "nb_argmax_split": "piipppip",
     "nb_argmax": "piipp",

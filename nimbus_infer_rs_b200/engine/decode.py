@@ -46,12 +46,14 @@ class DecodeSession:
         self._key = (n, self.params.greedy,
                      float(self.params.temperature) if not self.params.greedy else 0.0,
                      int(self.params.top_k) if not self.params.greedy else 0,
-                     float(self.params.top_p) if not self.params.greedy else 1.0)
+                     float(self.params.top_p) if not self.params.greedy else 1.0,
+                     float(self.params.repetition_penalty))
         kept = engine.decode_states.pop(self._key, None) if self.use_graph else None
         if kept is not None:
             self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u = kept["buffers"]
             self._buf.copy_(torch.from_numpy(host), non_blocking=False)
             self._graph, self._graph_launches, self.logits = kept["graph"], kept["launches"], kept["logits"]
+            self.hist, self.hist_len = kept["history"]
             self._steps = 1 if self._graph is not None else 0
         else:
             self._buf = torch.from_numpy(host).to(dev)
@@ -63,6 +65,12 @@ class DecodeSession:
             self._graph = None
             self._graph_launches = 0
             self._steps = 0
+            self.hist = self.hist_len = None
+            if self.params.repetition_penalty != 1.0:
+                # what each sequence has generated, for the penalty: the token a row runs is
+                # appended on the device at the start of every step
+                self.hist = torch.zeros((n, engine.spec.max_seq_len), dtype=torch.int32, device=dev)
+                self.hist_len = torch.zeros(n, dtype=torch.int32, device=dev)
         buf = self._buf
         self.tokens, self.row_pos, self.row_slot = buf[:n], buf[n:2 * n], buf[2 * n:]
         self._stage = None
@@ -72,9 +80,18 @@ class DecodeSession:
             (p.top_p >= 1.0 or (hasattr(engine.ops, "sample_top_p")
                                 and p.top_k <= engine.ops.top_p_max_k()))
             and (p.top_k == 0 or hasattr(engine.ops, "sample_top_k")))
-        if p.repetition_penalty != 1.0 or not on_device:
+        if not on_device or (p.repetition_penalty != 1.0 and not hasattr(engine.ops, "history_append")):
             raise ValueError("a decode session selects tokens with the sampling kernels only "
-                             "(no repetition penalty; top-k within the top-p kernel's room)")
+                             "(top-k within the top-p kernel's room)")
+        if self.hist is not None:
+            # tokens generated before this session, all but the one each row runs first
+            self.hist_len.zero_()
+            for i in range(n):
+                before = list(seq_samplers[i].generated[:-1]) if seq_samplers is not None else []
+                if before:
+                    before = before[-self.hist.shape[1]:]
+                    self.hist[i, :len(before)] = torch.tensor(before, dtype=torch.int32)
+                    self.hist_len[i:i + 1].fill_(len(before))
         self.last_u: list[float] = []
         self._sampled = False      # a step of this session has selected tokens
 
@@ -93,7 +110,12 @@ class DecodeSession:
     def _device_step(self) -> None:
         eng = self.engine
         ctx = StepContext(eng.rt, eng.ops, self._layout(), eng.model.position, eng.cache)
+        if self.hist is not None:
+            eng.ops.history_append(self.hist, self.hist_len, self.tokens, self.row_slot)
         self.logits = eng.model.forward(ctx)
+        if self.hist is not None:
+            eng.ops.repetition_penalty(self.logits, self.hist, self.hist_len,
+                                       float(self.params.repetition_penalty))
         if self.params.greedy:
             eng.ops.argmax(self.logits, self.next_tokens)
         elif self.params.top_p < 1.0:
@@ -208,6 +230,7 @@ class DecodeSession:
             self.engine.decode_states[self._key] = {
                 "buffers": (self._buf, self.next_tokens, self.want_rows, self.cu_rows, self.u),
                 "graph": self._graph, "launches": self._graph_launches, "logits": self.logits,
+                "history": (self.hist, self.hist_len),
                 # scratch buffers of the kernel library that the graph points into
                 "scratch": self.engine.ops.scratch_refs() if hasattr(self.engine.ops, "scratch_refs") else None}
             while len(self.engine.decode_states) > 8:

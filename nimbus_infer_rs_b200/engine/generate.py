@@ -105,7 +105,8 @@ def run_batch(engine, prompts: list[list[int]], indices: list[int], params: Samp
         # the prompts, in one step; logits of each last token
         logits = engine.step([(slots[s.index], prompts[s.index], [s.prompt_len - 1]) for s in live])
         nxt = take(live, sampler.sample(logits, [seq_samplers[s.index] for s in live]))
-        if nxt and not sampler.needs_host() and params.repetition_penalty == 1.0:
+        if nxt and not sampler.needs_host() and (
+                params.repetition_penalty == 1.0 or hasattr(engine.ops, "history_append")):
             # token selection stays on the device: one captured step per token
             from .decode import DecodeSession
             members = [s for s, _ in nxt]

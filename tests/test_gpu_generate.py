@@ -153,10 +153,33 @@ def test_top_p_inside_the_decode_session_equals_the_host_sampler(vocab):
                                     activation_function="gelu_new"))
     e = Engine.random(cfg, seed=4, dtype="bfloat16", cache_tokens=1024)
     prompts = [[5, 17, 3, 9], [11, 2], [7] * 9]
+    from nimbus_infer_rs_b200.sampling import SequenceSampler
+
+    def step_by_step(p):
+        """Plain steps and the batch sampler: what generation did before there was a session."""
+        sampler = BatchSampler(p, e.ops, e.rt.device)
+        seqs = [SequenceSampler(p, i) for i in range(len(prompts))]
+        slots = [e.alloc_slot() for _ in prompts]
+        toks = sampler.sample(e.step([(s, pr, [len(pr) - 1]) for s, pr in zip(slots, prompts)]), seqs)
+        out = [[t] for t in toks]
+        for _ in range(p.max_new_tokens - 1):
+            toks = sampler.sample(e.step([(s, [t], [0]) for s, t in zip(slots, toks)]), seqs)
+            for o, t in zip(out, toks):
+                o.append(t)
+        for s in slots:
+            e.free_slot(s)
+        return out
+
+    # with a repetition penalty the session keeps each sequence's tokens on the device
+    for kw in (dict(temperature=0.0, repetition_penalty=1.7), dict(temperature=0.8, repetition_penalty=1.3),
+               dict(temperature=1.1, top_k=30, top_p=0.9, repetition_penalty=0.7)):
+        p = SamplingParams(max_new_tokens=20, seed=5, **kw)
+        assert e.generate(prompts, p) == step_by_step(p), kw
     for kw in (dict(temperature=0.9, top_p=0.8), dict(temperature=1.2, top_k=50, top_p=0.95)):
         p = SamplingParams(max_new_tokens=20, seed=5, **kw)
         assert not BatchSampler(p, e.ops, e.rt.device).needs_host()
         in_session = e.generate(prompts, p)
+        assert in_session == step_by_step(p), kw
         orig = BatchSampler.needs_host
         BatchSampler.needs_host = lambda self: True          # the host decides every token
         try:
