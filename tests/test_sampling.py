@@ -153,3 +153,31 @@ def test_whole_rows_sampled_side_by_side_equal_one_after_the_other():
             plain[i].generated.append(int(t))
             want.append(int(t))
         assert got == want, step
+
+
+def test_which_options_the_sampling_kernels_take():
+    """The batch sampler asks the host only where the backend has no kernel for the options:
+    top-p with a top-k beyond the kernel's room, or a backend without the sampling kernels."""
+    from nimbus_infer_rs_b200.sampling import BatchSampler
+
+    class WithKernels:
+        def sample_top_k(self, *a): pass
+        def sample_top_p(self, *a): pass
+        def top_p_max_k(self): return 1024
+
+    class Without:
+        pass
+
+    def needs(ops, **kw):
+        return BatchSampler(SamplingParams(**kw), ops, "cpu").needs_host()
+    full, bare = WithKernels(), Without()
+    assert not needs(full, temperature=0.0, top_k=5, top_p=0.5)          # greedy: argmax
+    assert not needs(full, temperature=0.7)
+    assert not needs(full, temperature=0.7, top_k=40)
+    assert not needs(full, temperature=0.7, top_p=0.9)
+    assert not needs(full, temperature=0.7, top_k=1024, top_p=0.9, repetition_penalty=1.2)
+    assert needs(full, temperature=0.7, top_k=1025, top_p=0.9)
+    assert not needs(full, temperature=0.7, top_k=5000)                  # top-k alone: any k
+    assert not needs(bare, temperature=0.7)
+    assert needs(bare, temperature=0.7, top_k=40)
+    assert needs(bare, temperature=0.7, top_p=0.9)
