@@ -188,13 +188,14 @@ class DecodeSession:
         """The tokens selected by the last step, on the host (waits for the step): one copy
         into pinned memory on the step's stream, then a wait for that stream."""
         if self.next_tokens.device.type != "cuda":
-            return self.next_tokens.tolist()
-        if self._out_stage is None:
-            self._out_stage = torch.empty(self.n, dtype=torch.int32, pin_memory=True)
-            self._out_np = self._out_stage.numpy()
-        self._out_stage.copy_(self.next_tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        tokens = self._out_np.tolist()
+            tokens = self.next_tokens.tolist()
+        else:
+            if self._out_stage is None:
+                self._out_stage = torch.empty(self.n, dtype=torch.int32, pin_memory=True)
+                self._out_np = self._out_stage.numpy()
+            self._out_stage.copy_(self.next_tokens, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            tokens = self._out_np.tolist()
         if any(t < 0 for t, alive in zip(tokens, self.live) if alive):
             tokens = self._settle_on_host(tokens)
         return tokens

@@ -98,6 +98,36 @@ class CpuBackend:
         idx = (c < r).sum(-1).clamp(max=logits.shape[1] - 1)
         out.copy_(idx.to(torch.int32))
 
+    # The sampling kernels' stand-ins draw with the host's sampler and the number they are given.
+    # `hand_back`: mark every row as the top-p kernel marks a row it cannot settle (-2).
+    hand_back = False
+
+    def _draw(self, logits, u, out, **kw):
+        from nimbus_infer_rs_b200.sampling import SamplingParams
+        from nimbus_infer_rs_b200.sampling import host as H
+        from nimbus_infer_rs_b200.sampling.device import _Drawn
+        p = SamplingParams(**kw)
+        for r in range(logits.shape[0]):
+            out[r] = int(H.sample(logits[r].numpy(), p, [], _Drawn(float(u[r]))))
+
+    def sample_top_k(self, logits, k, temperature, u, out):
+        self._draw(logits, u, out, temperature=temperature, top_k=k)
+
+    def top_p_max_k(self):
+        return 1024
+
+    def sample_top_p(self, logits, k, top_p, temperature, u, out):
+        if self.hand_back:
+            out.fill_(-2)
+        else:
+            self._draw(logits, u, out, temperature=temperature, top_k=k, top_p=top_p)
+
+    def history_append(self, history, history_len, tokens, row_slot):
+        for r in range(tokens.numel()):
+            if int(row_slot[r]) >= 0 and int(history_len[r]) < history.shape[1]:
+                history[r, int(history_len[r])] = tokens[r]
+                history_len[r] += 1
+
     def repetition_penalty(self, logits, history, history_len, penalty):
         for r in range(logits.shape[0]):
             for tok in set(history[r, :int(history_len[r])].tolist()):

@@ -105,6 +105,37 @@ def test_temperature_sampling_is_seeded_and_independent_of_batch_mates(engine_b)
     assert c != alone
 
 
+def test_rows_the_sampling_kernel_hands_back_are_settled_from_the_steps_logits(engine_b, cpu_backend):
+    """Top-p and a repetition penalty inside the decode session: the session keeps each
+    sequence's tokens for the penalty, and a row that the top-p kernel marks instead of
+    settling is decided by the host from the step's logits with the number drawn for it.
+    Marked or not, in the session or step by step, the tokens are the same."""
+    from nimbus_infer_rs_b200.sampling import BatchSampler, SequenceSampler
+    prompts = [[5, 17, 3], [9], [1, 2, 3, 4, 5, 6, 7]]
+    p = SamplingParams(max_new_tokens=9, temperature=0.9, top_k=50, top_p=0.8,
+                       repetition_penalty=1.4, seed=11, stop_tokens=[])
+    settled = engine_b.generate(prompts, p)
+    cpu_backend.hand_back = True
+    try:
+        handed_back = engine_b.generate(prompts, p)
+    finally:
+        cpu_backend.hand_back = False
+    assert handed_back == settled and [len(x) for x in settled] == [9, 9, 9]
+    # step by step, with the batch sampler (what generation does without a session)
+    sampler = BatchSampler(p, engine_b.ops, engine_b.rt.device)
+    seqs = [SequenceSampler(p, i) for i in range(3)]
+    slots = [engine_b.alloc_slot() for _ in prompts]
+    toks = sampler.sample(engine_b.step([(s, pr, [len(pr) - 1]) for s, pr in zip(slots, prompts)]), seqs)
+    out = [[t] for t in toks]
+    for _ in range(8):
+        toks = sampler.sample(engine_b.step([(s, [t], [0]) for s, t in zip(slots, toks)]), seqs)
+        for o, t in zip(out, toks):
+            o.append(t)
+    for s in slots:
+        engine_b.free_slot(s)
+    assert out == settled
+
+
 def test_step_shapes_that_share_a_recording():
     """The key under which a step's launches are recorded: its numbers of rows, sequences and
     wanted places, its longest chunk, whether it is one token each, and the power-of-two range
