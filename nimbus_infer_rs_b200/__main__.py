@@ -4,13 +4,17 @@
     python -m nimbus_infer_rs_b200 bench    --model DIR [--prefill N] [--decode N] [--runs R]
     python -m nimbus_infer_rs_b200 logits   --model DIR --ids 1,2,3
     python -m nimbus_infer_rs_b200 inspect  --model DIR
-    python -m nimbus_infer_rs_b200 random   --out DIR --config CONFIG.json --seed S
+    python -m nimbus_infer_rs_b200 random   --out DIR (--config CONFIG.json | --preset NAME) --seed S
+
+Instead of ``--model DIR`` every command but ``random`` takes ``--random PRESET --seed-weights
+S``: a model of a named size (``gpt2`` = the reference's defaults, src/config.rs:45-66;
+``gpt2-medium``, ``gpt2-xl``, ``tiny-a``, ``tiny-b``) with seeded random weights, no file on disk.
 
 Flag names, meanings and defaults follow the reference where it has them (``--model``,
 ``--ids``, ``--max-new-tokens`` 64, ``--temperature`` 0 = greedy, ``--top-k`` 0, ``--top-p``
 1.0, ``--repetition-penalty`` 1.0, ``--seed``, ``--json``; ``--prefill`` 128, ``--decode`` 64,
 ``--runs`` 3).  Added: ``--dtype bfloat16|float32``, ``--stop ID,ID``, ``;`` between the id
-lists of a batch, ``--batch``.  There is no tokenizer, so ``--prompt TEXT`` is refused as the
+lists of a batch, ``--batch``, ``--keep-stored-dtype`` / ``--cast-weights``.  There is no tokenizer, so ``--prompt TEXT`` is refused as the
 reference refuses it for a checkpoint without one (src/engine.rs:245-251); ``--quant``
 accepts only ``fp32``.
 """
@@ -39,17 +43,33 @@ def _parse_ids(text: str) -> list[list[int]]:
 
 
 def _common(ap):
-    ap.add_argument("--model", required=True, help="folder with config.json and the weight file")
+    ap.add_argument("--model", help="folder with config.json and the weight file")
+    ap.add_argument("--random", metavar="PRESET",
+                    help="instead of --model: a model of a named size with seeded random weights "
+                         "(gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b); nothing is read from disk")
+    ap.add_argument("--seed-weights", type=int, default=0, help="seed of --random's weights")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--quant", default="fp32", help="only fp32 (no quantized weights here)")
+    g = ap.add_mutually_exclusive_group()
+    g.add_argument("--keep-stored-dtype", action="store_true",
+                   help="bfloat16 runs: matrices stored in 32-bit stay so (and run on the fp32 "
+                        "kernels) even when the file holds no bf16 matrix at all")
+    g.add_argument("--cast-weights", action="store_true",
+                   help="bfloat16 runs: round every matrix stored in 32-bit to bf16")
 
 
 def _load(args, **kw):
     from . import Engine
     if args.quant not in ("fp32", "f32", "none"):
         raise SystemExit(f"error: quant mode {args.quant!r} is not built (expected fp32)")
-    return Engine.load(args.model, dtype=args.dtype, device=args.device, **kw)
+    if (args.model is None) == (args.random is None):
+        raise SystemExit("error: pass --model DIR or --random PRESET")
+    if args.random is not None:
+        return Engine.random(args.random, seed=args.seed_weights, dtype=args.dtype,
+                             device=args.device, **kw)
+    cast = True if args.cast_weights else (False if args.keep_stored_dtype else None)
+    return Engine.load(args.model, dtype=args.dtype, device=args.device, cast_weights=cast, **kw)
 
 
 def cmd_generate(args) -> int:
@@ -97,6 +117,7 @@ def cmd_logits(args) -> int:
     engine = _load(args, cache_tokens=max(64, len(ids)))
     slot = engine.alloc_slot()
     logits = engine.step([(slot, ids, [len(ids) - 1])])[0].cpu()
+    engine.check_errors()
     engine.free_slot(slot)
     best = int(torch.argmax(logits))
     print(json.dumps({
@@ -167,15 +188,24 @@ def cmd_bench(args) -> int:
 
 
 def cmd_random(args) -> int:
-    from .config import load_json, resolve_architecture
+    from .config import load_json, load_preset, resolve_architecture
     from .weights import write_random_model
     import torch
-    obj = load_json(args.config)
-    arch = resolve_architecture(obj)
-    cfg = arch.config_cls.from_json(obj)
-    d = write_random_model(args.out, cfg, args.seed, std=args.std, bias_std=args.bias_std,
+    if (args.config is None) == (args.preset is None):
+        raise SystemExit("error: pass --config CONFIG.json or --preset NAME")
+    if args.preset is not None:
+        arch, cfg, opts = load_preset(args.preset)
+    else:
+        obj = load_json(args.config)
+        arch = resolve_architecture(obj)
+        cfg, opts = arch.config_cls.from_json(obj), {}
+    if args.std is not None:
+        opts["std"] = args.std
+    if args.bias_std is not None:
+        opts["bias_std"] = args.bias_std
+    d = write_random_model(args.out, cfg, args.seed, **opts,
                            dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
-    print(json.dumps({"wrote": str(d), "n_params": cfg.n_params(args.bias_std > 0)}))
+    print(json.dumps({"wrote": str(d), "n_params": cfg.n_params(opts.get("bias_std", 0.0) > 0)}))
     return 0
 
 
@@ -219,10 +249,12 @@ def main(argv=None) -> int:
 
     r = sub.add_parser("random")
     r.add_argument("--out", required=True)
-    r.add_argument("--config", required=True, help="a config.json to take the sizes from")
+    r.add_argument("--config", help="a config.json to take the sizes from")
+    r.add_argument("--preset", help="or a named size: gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b")
     r.add_argument("--seed", type=int, default=0)
-    r.add_argument("--std", type=float, default=0.02)
-    r.add_argument("--bias-std", type=float, default=0.0)
+    r.add_argument("--std", type=float, default=None, help="spread of the matrices (0.02)")
+    r.add_argument("--bias-std", type=float, default=None,
+                   help="spread of the linear biases (0: none are written)")
     r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     r.set_defaults(fn=cmd_random)
 

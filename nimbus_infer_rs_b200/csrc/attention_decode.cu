@@ -50,7 +50,6 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
   float* w_ml = w_acc + WARPS * G * HD;                            // [WARPS][G][2]
   __shared__ int s_last;
 
-  nb_launch_dependents();
   nb_grid_dependency_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -177,6 +176,7 @@ attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
     __syncthreads();   // the stage is free for the copy after next
   }
 
+  nb_launch_dependents();   // the pages are read: the next kernel may be set up
   // merge the key rows a warp handled side by side (lanes with equal `part`)
 #pragma unroll
   for (int gh = 0; gh < G; ++gh) {
@@ -387,21 +387,33 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     __syncthreads();
     bf16* kt = tiles + (size_t)stage * 2 * STILE;
     bf16* vt = kt + STILE;
-    if (append && p == pos / PAGE_TOKENS) {
-      // this step's own key and value belong at token `pos` of this page: into the staged
-      // tile and into the cache
-      const int in_page = pos % PAGE_TOKENS;
-      const int page_id = table[p];
+    const bool own_page = append && p == pos / PAGE_TOKENS;
+    const int tail_row = kv_len - p * PAGE_TOKENS;   // first row of the page that holds no key yet
+    if (own_page || tail_row < PAGE_TOKENS) {        // uniform over the CTA
       constexpr int CPR = HD / 8;
-      for (int i = tid; i < 2 * CPR; i += THREADS) {
-        const bool is_v = i >= CPR;
-        const int c = (is_v ? i - CPR : i) * 8;
-        const uint4 val = *reinterpret_cast<const uint4*>(
-            qrow + (is_v ? v_col : k_col) + (size_t)kvh * HD + c);
-        *reinterpret_cast<uint4*>((is_v ? vt : kt) + in_page * ROW + c) = val;
-        bf16* cache = (bf16*)(is_v ? kv.v : kv.k);
-        *reinterpret_cast<uint4*>(cache + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE +
-                                  in_page * HD + c) = val;
+      if (own_page) {
+        // this step's own key and value belong at token `pos` of this page: into the staged
+        // tile and into the cache
+        const int in_page = pos % PAGE_TOKENS;
+        const int page_id = table[p];
+        for (int i = tid; i < 2 * CPR; i += THREADS) {
+          const bool is_v = i >= CPR;
+          const int c = (is_v ? i - CPR : i) * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(
+              qrow + (is_v ? v_col : k_col) + (size_t)kvh * HD + c);
+          *reinterpret_cast<uint4*>((is_v ? vt : kt) + in_page * ROW + c) = val;
+          bf16* cache = (bf16*)(is_v ? kv.v : kv.k);
+          *reinterpret_cast<uint4*>(cache + ((size_t)page_id * kv.n_kv_heads + kvh) * TILE +
+                                    in_page * HD + c) = val;
+        }
+      }
+      // Rows of the page after the sequence's last key hold whatever an earlier owner of the
+      // page left there.  Their probabilities are zero, but zero times a non-finite value is
+      // not: the value rows are cleared in the staged copy (a masked score needs no such care,
+      // it is replaced, not multiplied).
+      for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += THREADS) {
+        const int row = tail_row + i / CPR, c = (i % CPR) * 8;
+        *reinterpret_cast<uint4*>(vt + row * ROW + c) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncthreads();
     }
@@ -694,11 +706,21 @@ void* g_static_ptr[MAX_DEVICES] = {nullptr};
 
 // The array's device address on the current device.  In host code the name
 // `g_static_scratch` is only a handle for the runtime, never an address a kernel may use.
-int static_scratch_address(unsigned char** out) {
+int static_scratch_address(unsigned char** out, cudaStream_t stream) {
   int dev = -1;
   NB_CUDA(cudaGetDevice(&dev));
   NB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, NB_ERR_UNSUPPORTED,
              "attention_decode_static: device index %d is beyond %d", dev, MAX_DEVICES);
+  // the address below is the current device's copy of the array: a stream of another device
+  // would run the kernel there, on memory it does not own
+  int stream_dev = dev;
+  if (stream != nullptr && cudaStreamGetDevice(stream, &stream_dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    stream_dev = dev;
+  }
+  NB_REQUIRE(stream_dev == dev, NB_ERR_BAD_ARG,
+             "attention_decode_static: the stream belongs to device %d, the current device is %d",
+             stream_dev, dev);
   std::lock_guard<std::mutex> lock(g_static_mutex);
   if (g_static_ptr[dev] == nullptr) {
     void* p = nullptr;
@@ -735,7 +757,7 @@ NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride,
              n_rows, n_heads, n_splits, head_dim, cnt_b + ml_b + acc_b,
              (long long)NB_STATIC_SCRATCH_BYTES);
   unsigned char* base = nullptr;
-  const int rc = static_scratch_address(&base);
+  const int rc = static_scratch_address(&base, stream);
   if (rc) return rc;
   // the array keeps what the last call left; the counters are the only part that must start
   // at zero (a launch that ran to its end leaves them so, an interrupted one may not)

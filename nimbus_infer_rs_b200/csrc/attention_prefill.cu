@@ -132,7 +132,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     }
     __syncthreads();
     const bf16* kt = kv_s + (size_t)stage * 2 * PAGE_TOKENS * ROW;
-    const bf16* vt = kt + PAGE_TOKENS * ROW;
+    bf16* vt = kv_s + (size_t)stage * 2 * PAGE_TOKENS * ROW + PAGE_TOKENS * ROW;
+    // Rows of the last page after the newest key hold whatever an earlier owner of the page
+    // left there.  Their probabilities are zero, but zero times a non-finite value is not: the
+    // value rows are cleared in the staged copy (masked scores are replaced, not multiplied).
+    const int tail_row = last_pos + 1 - p * PAGE_TOKENS;
+    if (tail_row < PAGE_TOKENS) {   // uniform over the CTA
+      constexpr int CPR = HD / 8;
+      for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += THREADS) {
+        const int r = tail_row + i / CPR, c = (i % CPR) * 8;
+        *reinterpret_cast<uint4*>(vt + r * ROW + c) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncthreads();
+    }
 
     // scores of 16 rows x 64 keys
     float sc[8][4];

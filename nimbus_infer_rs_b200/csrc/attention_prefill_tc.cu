@@ -39,7 +39,6 @@ constexpr int TILE_Q = 128;
 constexpr int PAGE_TOKENS = 64;
 constexpr int TC_THREADS = 320;   // producer, MMA issuer, eight softmax warps
 
-__device__ int g_attn_error_flag = 0;
 
 // kind::f16 instruction descriptor with an MN-major B operand (bit 16)
 __host__ __device__ constexpr uint32_t instr_desc_bf16_b_mn(int m, int n) {
@@ -105,7 +104,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const int* __restrict__ seq_pos0, const int* __restrict__ block_table,
                             int max_pages, int n_kv_heads, int group, TOut* __restrict__ out,
                             int out_stride, float scale, int window, int max_splits,
-                            int chunk_pages, float* __restrict__ part, int* __restrict__ counters) {
+                            int chunk_pages, float* __restrict__ part, int* __restrict__ counters,
+                            int* err_word) {
   using L = AttnSmem<HD>;
   constexpr int HB = L::HB;
   extern __shared__ unsigned char smem_dyn[];
@@ -161,6 +161,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   const int p_begin = p_first + split * chunk_pages, p_end = min(p_last, p_begin + chunk_pages);
   const int nb = (p_end - p_begin + 1) / 2;             // turns of two pages
+  const int tail_row = last_pos % PAGE_TOKENS + 1;      // first row of the last page without a key
   // turn i takes pages p_begin + 2i and, if it is still in the run, the next one
   auto two_pages = [&](int i) { return p_begin + 2 * i + 1 < p_end; };
   const int* table = block_table + (size_t)slot * max_pages;
@@ -444,6 +445,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           tc05_st_32x32b_x32(lane_addr + L::S_COL + b * (2 * PAGE_TOKENS) + half * 32, pk);
           tc05_wait_st();
         }
+        if (j == nb - 1 && p_end == p_last && tail_row < PAGE_TOKENS) {
+          // Rows of the sequence's last page after its newest key hold whatever an earlier
+          // owner of the page left there (or, read from the step's rows, a neighbour's keys).
+          // Their probabilities are zero, but zero times a non-finite value is not: the eight
+          // softmax warps clear those value rows in the staged page before the value product
+          // may start (it waits for all of them at p_full).  A row is 128 bytes inside each
+          // 64-column box, whatever the swizzle does within it.
+          unsigned char* vpage = gen + L::Q_BYTES + (j % L::STAGES) * L::STAGE_BYTES + L::K_BYTES +
+                                 ((p_end - 1) - (p_begin + 2 * j)) * L::PAGE_BOX;
+          const int sm_tid = (warp - 2) * 32 + lane;
+          for (int i = sm_tid; i < (PAGE_TOKENS - tail_row) * 8 * HB; i += 256) {
+            const int box = i / ((PAGE_TOKENS - tail_row) * 8), rem = i % ((PAGE_TOKENS - tail_row) * 8);
+            *reinterpret_cast<uint4*>(vpage + box * (2 * L::PAGE_BOX) + (tail_row + rem / 8) * 128 +
+                                      (rem % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
         tc05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(b));
@@ -540,7 +558,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   if (*abort_flag) {
     if (tid == 0) {
-      atomicExch(&g_attn_error_flag, 1);
+      nb_report_timeout(err_word);
       // let TMA copies that are still in flight land before the shared memory goes away
       const long long t0 = clock64();
       while (clock64() - t0 < 4000000LL) {
@@ -554,6 +572,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                  "r"((uint32_t)L::TMEM_COLS)
                  : "memory");
   }
+}
+
+// The word of pinned host memory in which this kernel reports a wait that ran out.
+int* error_word() {
+  int* w = nb_error_words();
+  return w ? w + NB_ERRW_ATTENTION_PREFILL_TC : nullptr;
 }
 
 template <int HD, typename TOut>
@@ -584,7 +608,7 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
   NB_CUDA(nb_launch(kern, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, mq, mk, mv, mn, append, k_col,
                     v_col, q_col, cu_rows, seq_slot, seq_pos0, block_table, max_pages, n_kv_heads,
                     n_heads / n_kv_heads, (TOut*)out, out_stride, scale, window, max_splits,
-                    chunk_pages, part, counters));
+                    chunk_pages, part, counters, error_word()));
   return 0;
 }
 
@@ -601,15 +625,21 @@ NB_EXPORT int nb_attention_prefill_tc_supported(int dtype, int head_dim, int n_h
   return head_dim == 64 || head_dim == 128;
 }
 
-// Reads (and clears) the error flag that a timed-out wait raises; synchronises the device.
+// Waits for the device, then reads (and lowers) the word that a timed-out wait of this kernel
+// raises.
 NB_EXPORT int nb_attention_prefill_tc_error() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_attn_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_attn_error_flag, &zero, sizeof(int));
-  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  volatile int* w = error_word();
+  if (w == nullptr) return 0;
+  const int v = *w;
+  if (v) *w = 0;
   return v;
+}
+
+// Clock cycles a wait of this kernel may take before it gives up (default 4e9).
+NB_EXPORT int nb_attention_prefill_tc_set_wait_budget(long long cycles) {
+  NB_REQUIRE(cycles >= 0, NB_ERR_BAD_ARG, "wait budget must not be negative");
+  return set_wait_budget(cycles);
 }
 
 // Floats of scratch per (sequence, head, 128-row tile, split) when the pages of a tile are cut

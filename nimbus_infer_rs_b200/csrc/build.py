@@ -132,6 +132,10 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             _log(f"compiling {len(srcs)} CUDA sources for sm_100a into {d} (first call only)")
         obj_dir = d / "obj"
         obj_dir.mkdir(parents=True, exist_ok=True)
+        stems = {src.stem for src in srcs}
+        for old in obj_dir.glob("*.o"):            # objects whose source is gone
+            if old.stem not in stems:
+                old.unlink(missing_ok=True)
 
         done = threading.Event()
 

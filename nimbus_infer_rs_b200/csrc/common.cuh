@@ -52,6 +52,25 @@ void nb_set_error(const char* fmt, ...);
   } while (0)
 
 // ---------------------------------------------------------------------------------
+// Error words: a kernel whose bounded wait ran out says so in a word of pinned host memory
+// that is mapped into the device's address space (one word per kernel family, see below).
+// The kernel writes it with a plain store and a system-wide fence before it ends, so a host
+// that has waited for the stream reads it with a plain load: no copy, no extra
+// synchronisation.  nb_error_words() allocates the page on first use (host memory, never
+// device memory) and returns nullptr if that fails; kernels given nullptr still give up their
+// waits and return, they only cannot say so.
+// ---------------------------------------------------------------------------------
+enum NbErrorWord : int { NB_ERRW_GEMM_TCGEN05 = 0, NB_ERRW_ATTENTION_PREFILL_TC = 1, NB_ERRW_PROBE = 2, NB_ERRW_COUNT = 16 };
+int* nb_error_words();
+
+__device__ __forceinline__ void nb_report_timeout(int* err_word) {
+  if (err_word != nullptr) {
+    *reinterpret_cast<volatile int*>(err_word) = 1;
+    __threadfence_system();
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched through nb_launch with overlap enabled
 // may start while the kernel before it in the stream is still running; it must execute
 // nb_grid_dependency_wait() before it reads anything an earlier kernel wrote or writes

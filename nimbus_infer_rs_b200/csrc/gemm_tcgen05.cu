@@ -40,7 +40,6 @@ __host__ __device__ constexpr int acc_stride(int bn) {
   return bn <= 64 ? 64 : (bn <= 128 ? 128 : 256);
 }
 __host__ __device__ constexpr int cta_threads(int bn, int epi) { return 64 + 32 * epi_warps(bn, epi); }
-__device__ int g_error_flag = 0;
 
 // One CTA per SM walks over tiles; two accumulators in tensor memory let the epilogue of one
 // tile overlap the main loop of the next.  EPI 1 adds a staging area for the epilogue: 4 KB
@@ -71,7 +70,7 @@ __global__ void __launch_bounds__(cta_threads(BN, EPI))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
                     const float* residual, TOut* out, int M, int N, int K, int act, int tiles_n,
-                    int num_tiles, int a_box_bytes) {
+                    int num_tiles, int a_box_bytes, int* err_word) {
   using L = SmemLayout<BN, EPI, (int)sizeof(TOut), PAIR>;
   constexpr int EW = L::EPI_WARPS;
   constexpr int ACC = acc_stride(BN);
@@ -442,7 +441,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (*abort_flag) {
     if (tid == 0) {
-      atomicExch(&g_error_flag, 1);
+      nb_report_timeout(err_word);
       // let TMA copies that are still in flight land before the shared memory goes away
       const long long t0 = clock64();
       while (clock64() - t0 < 4000000LL) {
@@ -540,7 +539,7 @@ template <int SPLIT, typename TOut>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                            const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
-                           int K, int act, int kb_per, int a_box_bytes) {
+                           int K, int act, int kb_per, int a_box_bytes, int* err_word) {
   using L = SplitSmem<SPLIT>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -676,7 +675,7 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
   __syncthreads();
   if (*abort_flag) {
     if (tid == 0) {
-      atomicExch(&g_error_flag, 1);
+      nb_report_timeout(err_word);
       const long long t0 = clock64();
       while (clock64() - t0 < 4000000LL) {
       }
@@ -688,6 +687,29 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
                  "r"((uint32_t)SK_BN)
                  : "memory");
+  }
+}
+
+// The word of pinned host memory in which these kernels report a wait that ran out.
+int* error_word() {
+  int* w = nb_error_words();
+  return w ? w + NB_ERRW_GEMM_TCGEN05 : nullptr;
+}
+
+// A wait that nothing ends: one thread waits, with the same bounded wait as the kernels above,
+// on a barrier that never gets its arrival, and reports the time-out the way they do.  It is
+// how a test sees the limit work without any kernel being made to stall.
+__global__ void wait_probe_kernel(int* err_word, int* status) {
+  __shared__ __align__(8) unsigned long long bar_mem;
+  __shared__ int abort_mem;
+  const uint32_t bar = smem_u32(&bar_mem);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    abort_mem = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    const bool ok = mbar_wait(bar, 0u, &abort_mem);
+    if (!ok) nb_report_timeout(err_word);
+    *status = ok ? 1 : 2;
   }
 }
 
@@ -723,7 +745,7 @@ int launch_splitk(const void* X, const void* W, const float* bias, const float* 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, bias, residual, (TOut*)out, M, N, K, act, kb_per,
-                             a_rows * BK * 2));
+                             a_rows * BK * 2, error_word()));
   return 0;
 }
 
@@ -786,12 +808,13 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
-                               (int)num_tiles, a_rows * BK * 2));
+                               (int)num_tiles, a_rows * BK * 2, error_word()));
     return 0;
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
   NB_CUDA(nb_launch(kern, dim3(grid), dim3(cta_threads(BN, EPI)), (size_t)smem, stream, mx, mw, mo, bias,
-                    residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2));
+                    residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2,
+                    error_word()));
   return 0;
 }
 
@@ -890,15 +913,32 @@ NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
   return 0;
 }
 
-// Reads (and clears) the error flag that a timed-out wait raises; synchronises the device.
+// Waits for the device, then reads (and lowers) the word that a timed-out wait of these kernels
+// raises.
 NB_EXPORT int nb_gemm_tcgen05_error() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_error_flag, &zero, sizeof(int));
-  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  volatile int* w = error_word();
+  if (w == nullptr) return 0;
+  const int v = *w;
+  if (v) *w = 0;
   return v;
+}
+
+// Clock cycles a wait of these kernels may take before it gives up (default 4e9, about two
+// seconds).  Takes effect for kernels launched after the call.
+NB_EXPORT int nb_gemm_tcgen05_set_wait_budget(long long cycles) {
+  NB_REQUIRE(cycles >= 0, NB_ERR_BAD_ARG, "wait budget must not be negative");
+  return set_wait_budget(cycles);
+}
+
+// Runs the bounded wait on a barrier that nothing completes: `status` (device int) receives 2
+// when the wait gave up after the budget (and the probe's error word is raised), 1 if it came
+// back complete.
+NB_EXPORT int nb_wait_probe(int* status, cudaStream_t stream) {
+  int* w = nb_error_words();
+  wait_probe_kernel<<<1, 32, 0, stream>>>(w ? w + NB_ERRW_PROBE : nullptr, status);
+  NB_CHECK_LAUNCH("wait_probe");
+  return 0;
 }
 
 NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, const float* residual,

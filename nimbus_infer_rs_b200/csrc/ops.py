@@ -192,14 +192,41 @@ class CudaBackend:
                    (dtype_code(out.dtype)), (M), (N), (K), (act),
                    self._stream())
 
+    # A kernel whose bounded wait on a barrier ran out says so in a word of pinned host memory
+    # (one per kernel family); its results are not valid.
+    _ERROR_WORDS = {0: "gemm_tcgen05", 1: "attention_prefill_tc", 2: "wait_probe"}
+
+    def raise_device_errors(self) -> None:
+        """Raise if a kernel that has finished reported a timed-out wait.  Reads host memory
+        only: call it where the host has already waited for the work it hands out (logits
+        copied to the host, sampled tokens read back)."""
+        mask = self.lib.nb_device_errors(1)
+        if mask:
+            names = [self._ERROR_WORDS.get(i, f"word {i}") for i in range(16) if mask >> i & 1]
+            raise KernelError(f"{', '.join(names)}: a wait on a shared-memory barrier ran out of "
+                              "time; results of the steps since the last check are not valid")
+
     def check_device_errors(self) -> None:
-        """Raise if a kernel reported a timed-out wait (synchronises the device)."""
-        if self.lib.nb_gemm_tcgen05_error() != 0:
-            raise KernelError("gemm_tcgen05: a wait on a shared-memory barrier ran out of time; "
-                              "the results of that product are not valid")
-        if self.lib.nb_attention_prefill_tc_error() != 0:
-            raise KernelError("attention_prefill_tc: a wait on a shared-memory barrier ran out of "
-                              "time; the results of that attention are not valid")
+        """Wait for the device, then raise if a kernel reported a timed-out wait."""
+        torch.cuda.synchronize(self._device_index)
+        self.raise_device_errors()
+
+    def set_wait_budget(self, cycles: int | None) -> None:
+        """Clock cycles a wait on a barrier may take in the tensor-core kernels before the
+        kernel gives up and reports it (``None``: the default, about two seconds)."""
+        cycles = 4_000_000_000 if cycles is None else int(cycles)
+        for fn in ("nb_gemm_tcgen05_set_wait_budget", "nb_attention_prefill_tc_set_wait_budget"):
+            rc = getattr(self.lib, fn)(cycles)
+            if rc != 0:
+                raise KernelError(f"{fn} failed ({rc}): "
+                                  + self.lib.nb_last_error().decode("utf-8", "replace"))
+
+    def wait_probe(self) -> int:
+        """Run the kernels' bounded wait on a barrier that nothing completes; returns 2 if it
+        gave up after the budget (the error word is then raised), 1 if it came back complete."""
+        status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{self._device_index}")
+        self._call("nb_wait_probe", _ptr(status), self._stream())
+        return int(status.item())
 
     # -- cache and attention ----------------------------------------------------------
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):

@@ -18,7 +18,41 @@ void nb_set_error(const char* fmt, ...) {
 
 NB_EXPORT const char* nb_last_error() { return g_error; }
 
-NB_EXPORT int nb_abi_version() { return 2; }
+NB_EXPORT int nb_abi_version() { return 3; }
+
+// ---------------------------------------------------------------------------------
+// error words (see common.cuh)
+// ---------------------------------------------------------------------------------
+#include <mutex>
+static int* g_error_words = nullptr;
+int* nb_error_words() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, NB_ERRW_COUNT * sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) ==
+        cudaSuccess) {
+      for (int i = 0; i < NB_ERRW_COUNT; ++i) static_cast<volatile int*>(p)[i] = 0;
+      g_error_words = static_cast<int*>(p);
+    } else {
+      (void)cudaGetLastError();
+    }
+  });
+  return g_error_words;
+}
+// Bit i is set if error word i is raised.  No synchronisation: the caller has waited for the
+// work it asks about.  `clear` != 0 lowers the words that were read as raised.
+NB_EXPORT int nb_device_errors(int clear) {
+  volatile int* w = nb_error_words();
+  if (w == nullptr) return 0;
+  int mask = 0;
+  for (int i = 0; i < NB_ERRW_COUNT; ++i) {
+    if (w[i] != 0) {
+      mask |= 1 << i;
+      if (clear) w[i] = 0;
+    }
+  }
+  return mask;
+}
 
 // Whether kernels are launched so that they may overlap the tail of their predecessor.
 static int g_overlap = 0;

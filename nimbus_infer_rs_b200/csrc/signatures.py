@@ -1,5 +1,5 @@
 """Argument types of the library's ``extern "C"`` entry points, one letter per argument:
-``p`` pointer or stream, ``i`` int, ``f`` float, ``d`` double.  With these declared, the
+``p`` pointer or stream, ``i`` int, ``l`` long long, ``f`` float, ``d`` double.  With these declared, the
 callers pass plain Python numbers and addresses, which ctypes converts without a wrapper
 object per argument (a prefill step makes about a hundred calls, and the host must keep ahead
 of the GPU).  ``tests/test_signatures.py`` derives the same table from the CUDA sources."""
@@ -17,6 +17,7 @@ SIGNATURES = {
     "nb_attention_prefill": "piiippppppiiiiipiifiiip",
     "nb_attention_prefill_tc_supported": "iiiiiiiii",
     "nb_attention_prefill_tc_error": "",
+    "nb_attention_prefill_tc_set_wait_budget": "l",
     "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippiiip",
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
@@ -24,6 +25,9 @@ SIGNATURES = {
     "nb_gemm_skinny_norm_supported": "iii",
     "nb_gemm_tcgen05_supported": "iiiii",
     "nb_gemm_tcgen05_error": "",
+    "nb_gemm_tcgen05_set_wait_budget": "l",
+    "nb_wait_probe": "pp",
+    "nb_device_errors": "i",
     "nb_gemm_tcgen05_use_pairs": "i",
     "nb_gemm_tcgen05_use_splitk": "i",
     "nb_gemm_tcgen05": "pppppiiiiip",
@@ -45,7 +49,8 @@ SIGNATURES = {
     "nb_sample_top_p_max_k": "",
 }
 
-_CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}
+_CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double,
+          "l": ctypes.c_longlong}
 
 
 def declare(lib) -> None:

@@ -12,7 +12,14 @@
 
 namespace {
 
-constexpr long long WAIT_BUDGET = 4000000000LL;   // clock cycles (about two seconds)
+// Clock cycles a wait on a barrier may take (about two seconds by default); a value of this
+// translation unit, set from the host by set_wait_budget().
+__device__ long long g_wait_budget = 4000000000LL;
+
+int set_wait_budget(long long cycles) {
+  NB_CUDA(cudaMemcpyToSymbol(g_wait_budget, &cycles, sizeof(cycles)));
+  return 0;
+}
 
 // ---------------------------------------------------------------------------------- PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -37,15 +44,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false if the budget ran out or another role gave up.  A phase that is already
-// complete costs one try_wait; the clock and the abort flag are looked at once in 32 polls.
+// complete costs one try_wait; the clock and the abort flag are looked at after the second
+// failed poll and then once in 32 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
+  const long long budget = *reinterpret_cast<volatile long long*>(&g_wait_budget);
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 31u) != 0u) continue;
+    if ((polls++ & 31u) != 0u) continue;
     if (*abort_flag) return false;
-    if (clock64() - start > WAIT_BUDGET) {
+    if (clock64() - start > budget) {
       *abort_flag = 1;
       return false;
     }

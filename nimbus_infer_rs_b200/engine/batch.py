@@ -52,8 +52,11 @@ class PackedStep:
     is_decode: bool
     want_all_rows: bool
 
-    def on_device(self, dev: torch.Tensor, max_kv_len: int | None = None) -> BatchLayout:
-        """The layout over ``dev``, a device copy of ``buf``."""
+    def on_device(self, dev: torch.Tensor, max_kv_len: int | None = None,
+                  max_q_len: int | None = None) -> BatchLayout:
+        """The layout over ``dev``, a device copy of ``buf``.  ``max_kv_len`` / ``max_q_len``:
+        bounds to stand for the step's own longest sequence and longest chunk (launch shapes
+        are sized by them; every kernel reads the true lengths from ``dev``)."""
         o = self.offs
         parts = [dev[o[i]:o[i + 1]] for i in range(7)]
         return BatchLayout(
@@ -61,7 +64,7 @@ class PackedStep:
             tokens=parts[0], row_pos=parts[1], row_slot=parts[2], cu_rows=parts[3],
             seq_slot=parts[4], seq_pos0=parts[5], want_rows=parts[6], seq_lens=self.seq_lens,
             seq_pos0_host=self.seq_pos0_host, seq_slots_host=self.seq_slots_host,
-            max_q_len=self.max_q_len,
+            max_q_len=self.max_q_len if max_q_len is None else max_q_len,
             max_kv_len=self.max_kv_len if max_kv_len is None else max_kv_len,
             is_decode=self.is_decode, want_all_rows=self.want_all_rows)
 

@@ -147,11 +147,22 @@ class DecodeSession:
                              "what read_tokens() returned")
         if tokens is not None:
             if self._stage is None:
-                self._stage = torch.empty(self.n, dtype=torch.int32,
-                                          pin_memory=eng.rt.device.type == "cuda")
-                self._stage_np = self._stage.numpy()      # the same pinned memory
-            self._stage_np[:] = tokens
-            self.tokens.copy_(self._stage, non_blocking=True)
+                # two pinned buffers taken in turn, each with an event that says its last copy
+                # has left it: a step's tokens are never overwritten by the next step's while
+                # their copy to the device may still be waiting in the stream
+                cuda = eng.rt.device.type == "cuda"
+                self._stage = [torch.empty(self.n, dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
+                self._stage_np = [t.numpy() for t in self._stage]      # the same pinned memory
+                self._stage_done = [torch.cuda.Event() if cuda else None for _ in range(2)]
+                self._stage_turn = 0
+            i = self._stage_turn
+            self._stage_turn ^= 1
+            if self._stage_done[i] is not None:
+                self._stage_done[i].synchronize()     # returns at once if never recorded or done
+            self._stage_np[i][:] = tokens
+            self.tokens.copy_(self._stage[i], non_blocking=True)
+            if self._stage_done[i] is not None:
+                self._stage_done[i].record()
         if any(cache.lens[s] % PAGE == 0 or cache.lens[s] + 1 > cache.max_seq_len for s, _ in grow):
             cache.reserve(grow)            # a new page somewhere, or an error to raise
         if not self.params.greedy:
@@ -195,6 +206,7 @@ class DecodeSession:
                 self._out_np = self._out_stage.numpy()
             self._out_stage.copy_(self.next_tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            self.engine.ops.raise_device_errors()     # a kernel of the step gave up a wait
             tokens = self._out_np.tolist()
         if any(t < 0 for t, alive in zip(tokens, self.live) if alive):
             tokens = self._settle_on_host(tokens)

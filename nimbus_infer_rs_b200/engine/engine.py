@@ -24,7 +24,7 @@ from .batch import pack_step
 from .context import StepContext
 from .generate import plan_batches, run_batch, token_budget
 from .model import PRECISIONS, Model, Runtime
-from .step_graphs import StepGraphs
+from .step_graphs import StepGraphs, q_bound, row_padding
 
 
 class Engine:
@@ -55,9 +55,11 @@ class Engine:
     @classmethod
     def load(cls, model_dir: str | Path, dtype: str = "bfloat16", device: str = "cuda:0", *,
              cache_tokens: int | None = None, n_slots: int | None = None,
-             cast_weights: bool = False) -> "Engine":
+             cast_weights: bool | None = None) -> "Engine":
         """Load ``config.json`` and the weight file of ``model_dir``.  ``dtype``: ``bfloat16``
-        (the serving precision) or ``float32`` (everything in true 32-bit)."""
+        (the serving precision) or ``float32`` (everything in true 32-bit).  ``cast_weights``
+        (bfloat16 runs): ``True`` rounds matrices stored in 32-bit to bf16, ``False`` keeps
+        them as stored, ``None`` rounds them only if the file holds no bf16 matrix at all."""
         if dtype not in PRECISIONS:
             raise ValueError(f"dtype must be one of {sorted(PRECISIONS)}, got {dtype!r}")
         arch, config = load_config(model_dir)
@@ -76,13 +78,19 @@ class Engine:
                cache_tokens: int | None = None, n_slots: int | None = None,
                **random_options) -> "Engine":
         """A model with seeded random weights, loaded through the same by-name plan as a
-        weight file (nothing is written to disk).  ``config``: a typed configuration or a
-        config.json object."""
+        weight file (nothing is written to disk).  ``config``: a typed configuration, a
+        config.json object, or the name of a preset (``gpt2``, ``gpt2-medium``, ``gpt2-xl``,
+        ``tiny-a``, ``tiny-b``), whose own spread of the random values applies unless
+        ``random_options`` say otherwise."""
+        from ..config.presets import load_preset
         from ..config.registry import resolve_architecture
         from ..weights.loader import TensorDict
         if dtype not in PRECISIONS:
             raise ValueError(f"dtype must be one of {sorted(PRECISIONS)}, got {dtype!r}")
-        if isinstance(config, dict):
+        if isinstance(config, str):
+            arch, config, preset_options = load_preset(config)
+            random_options = {**preset_options, **random_options}
+        elif isinstance(config, dict):
             arch = resolve_architecture(config)
             config = arch.config_cls.from_json(config)
         else:
@@ -141,12 +149,17 @@ class Engine:
         entries = self._check_entries(entries)
         self.cache.reserve([(slot, len(toks)) for slot, toks, _ in entries])
         pos0 = [self.cache.lens[slot] for slot, _, _ in entries]
-        packed = pack_step(entries, pos0)
+        # with recordings on, a step's rows are padded so that steps of nearly the same size
+        # share one (padding rows change no result); the plain first run of a shape and its
+        # replays use the same padded layout and bounds, so they agree bit for bit
+        pad = row_padding(sum(len(t) for _, t, _ in entries)) if self.step_graphs else 1
+        packed = pack_step(entries, pos0, pad_rows_to=pad)
         done, logits = self.step_graphs.run(packed) if self.step_graphs else (False, None)
         if not done:
             layout = packed.on_device(
                 packed.copy_to(self.rt.device),
-                max_kv_len=self.step_graphs.kv_bound(packed) if self.step_graphs else None)
+                max_kv_len=self.step_graphs.kv_bound(packed) if self.step_graphs else None,
+                max_q_len=q_bound(packed.max_q_len) if self.step_graphs else None)
             ctx = StepContext(self.rt, self.ops, layout, self.model.position, self.cache)
             logits = self.model.forward(ctx)
         for slot, toks, _ in entries:
@@ -178,22 +191,65 @@ class Engine:
             res = run_batch(self, prompts, batch, params, sampler, seq_samplers, on_token)
             for i, ids in res.items():
                 out[i] = ids
+            self.check_errors()
         return out
+
+    def check_errors(self) -> None:
+        """Raise if a kernel of a step that has finished gave up a wait (its results are not
+        valid).  ``step`` hands out logits that are still being computed; whoever has waited
+        for them (copied them to the host, read sampled tokens) calls this before using them.
+        ``generate`` does so itself."""
+        self.ops.raise_device_errors()
 
     # ------------------------------------------------------------------ reports
     def inspect(self) -> dict:
-        """What the reference's ``inspect`` prints (src/main.rs:333-369)."""
-        c = self.config
+        """What the reference's ``inspect`` prints (src/main.rs:333-369), read off the model's
+        description: the kinds of its parts, what its mixers keep per token, and the element
+        types its weights are held in (a matrix held in float32 runs on the CUDA-core
+        kernels, also in a bfloat16 run)."""
+        spec = self.spec
+
+        def kinds(specs):
+            seen = []
+            for ps in specs:
+                if ps.kind not in seen:
+                    seen.append(ps.kind)
+            return seen[0] if len(seen) == 1 else seen
+
+        def arg(specs, key):
+            seen = []
+            for ps in specs:
+                v = ps.args.get(key)
+                if v is not None and v not in seen:
+                    seen.append(v)
+            return None if not seen else (seen[0] if len(seen) == 1 else seen)
+
+        mixers = [l.mixer for l in spec.layers]
+        ffns = [l.ffn for l in spec.layers]
+        kv_req, _ = self.model.storage_requests()
+        reqs = []
+        for r in kv_req.values():
+            if r not in reqs:
+                reqs.append(r)
+        one = (lambda vals: None if not vals else (vals[0] if len(set(vals)) == 1 else vals))
+        by_dtype: dict[str, int] = {}
+        for t in self.model.params.values():
+            if t is not None:
+                key = str(t.dtype).replace("torch.", "")
+                by_dtype[key] = by_dtype.get(key, 0) + t.numel() * t.element_size()
         return {
-            "name": getattr(c, "name", "model"), "architecture": self.spec.architecture,
+            "name": getattr(self.config, "name", "model"), "architecture": spec.architecture,
             "n_params": self.model.n_params(),
-            "weight_mb": round(sum(t.numel() * t.element_size() for t in self.model.params.values()
-                                   if t is not None) / 2 ** 20, 2),
+            "weight_mb": round(sum(by_dtype.values()) / 2 ** 20, 2),
+            "weight_mb_by_dtype": {k: round(v / 2 ** 20, 2) for k, v in sorted(by_dtype.items())},
             "kv_cache_mb": round(self.cache.bytes() / 2 ** 20, 2),
-            "vocab": self.spec.vocab_size, "layers": len(self.spec.layers),
-            "heads": getattr(c, "n_heads", None), "kv_heads": getattr(c, "n_kv_heads", None),
-            "d_model": self.spec.width, "head_dim": getattr(c, "head_dim", None),
-            "max_seq_len": self.spec.max_seq_len, "norm": "layernorm",
-            "activation": getattr(c, "activation", None), "pos": self.spec.position.kind,
+            "vocab": spec.vocab_size, "layers": len(spec.layers),
+            "heads": arg(mixers, "n_heads"), "kv_heads": one([r.n_kv_heads for r in reqs]),
+            "d_model": spec.width, "head_dim": one([r.head_dim for r in reqs]),
+            "max_seq_len": spec.max_seq_len, "norm": kinds([spec.final_norm]
+                                                           + [l.norm_mixer for l in spec.layers]
+                                                           + [l.norm_ffn for l in spec.layers]),
+            "mixer": kinds(mixers), "ffn": kinds(ffns), "activation": arg(ffns, "activation"),
+            "pos": spec.position.kind, "tie_head": spec.tie_head,
             "dtype": self.rt.precision, "cache_tokens": self.cache.cache_tokens,
         }

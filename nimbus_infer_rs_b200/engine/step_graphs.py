@@ -3,7 +3,8 @@
 Every kernel of a step reads the batch (tokens, positions, slots, block tables) from device
 memory, and no launch shape depends on anything but the step's *shape*: how many rows,
 sequences and wanted places it has, its longest chunk, and (for one-token steps) the range
-its longest sequence falls in.  So the launches of a step can be recorded once and replayed
+its longest sequence falls in.  Rows (beyond 64) and the longest chunk are rounded up to
+multiples of 64 and 128, so that prompts of nearly the same lengths fall into one shape.  So the launches of a step can be recorded once and replayed
 for every later step of the same shape, whatever its tokens, slots and lengths: the host then
 issues one graph launch instead of about a hundred kernel launches, and stays ahead of the
 GPU.  A shape is recorded when it comes for the second time (the first run is plain and has
@@ -32,6 +33,23 @@ def _kv_range(n: int, longest: int) -> int:
     while r < n:
         r *= 2
     return min(r, longest)
+
+
+ROW_BUCKET = 64      # steps of more rows than this are padded to a multiple of it
+Q_BUCKET = 128       # a step's longest chunk counts as the next multiple of this
+
+
+def row_padding(n_tokens: int) -> int:
+    """What a step's row count is rounded up to, so that steps of nearly the same size share
+    a recording: nothing for small steps (a decode step of a small batch), else a multiple of
+    64.  Padding rows are skipped by every kernel and change no result."""
+    return 1 if n_tokens <= ROW_BUCKET else ROW_BUCKET
+
+
+def q_bound(max_q_len: int) -> int:
+    """The chunk length that stands for ``max_q_len`` in the step's launches (grids over the
+    rows of a sequence are sized by it; CTAs beyond a sequence's rows leave at once)."""
+    return 1 if max_q_len <= 1 else -(-max_q_len // Q_BUCKET) * Q_BUCKET
 
 
 @contextmanager
@@ -73,7 +91,7 @@ class StepGraphs:
         # and values, so it is part of the shape
         from ..cache.paged import PAGE
         aligned = all(q % PAGE == 0 for q in p.seq_pos0_host)
-        return (p.n_rows, p.n_seqs, p.n_want, p.max_q_len, p.is_decode, p.want_all_rows,
+        return (p.n_rows, p.n_seqs, p.n_want, q_bound(p.max_q_len), p.is_decode, p.want_all_rows,
                 self.kv_bound(p), aligned)
 
     def run(self, p: PackedStep):
@@ -108,7 +126,7 @@ class StepGraphs:
         eng = self.engine
         buf = torch.empty(p.buf.size, dtype=torch.int32, device=eng.rt.device)
         p.copy_to(eng.rt.device, into=buf)
-        layout = p.on_device(buf, max_kv_len=self.kv_bound(p))
+        layout = p.on_device(buf, max_kv_len=self.kv_bound(p), max_q_len=q_bound(p.max_q_len))
         before = eng.ops.launches
         graph = torch.cuda.CUDAGraph()
         with no_collection(), torch.cuda.graph(graph):

@@ -8,9 +8,13 @@ and every wrong shape; only then does it read, combine, convert and upload.
 
 Element types: vectors (biases, norm weights) are held in fp32 and integer tables in int32.
 Matrices and embedding tables are held in fp32 when the run is ``float32``.  In a
-``bfloat16`` run they keep their stored type: bf16 stays bf16, and a tensor stored in 32-bit
-stays so (16-bit IEEE halves are widened to fp32, which loses nothing); such a matrix runs
-on the fp32 kernels.  ``cast_weights=True`` rounds them to bf16 instead.
+``bfloat16`` run a matrix stored in bf16 stays bf16, and a tensor stored in 32-bit stays so
+(16-bit IEEE halves are widened to fp32, which loses nothing) and runs on the fp32 kernels:
+whoever wrote a file with bf16 matrices and kept one tensor in 32-bit meant it.  A file that
+holds *no* bf16 matrix at all is a full-precision checkpoint (published GPT-2 files are);
+asking for a ``bfloat16`` run of it means rounding its matrices to bf16, and that is what
+happens unless ``cast_weights=False`` keeps the stored types.  ``cast_weights=True`` rounds
+every matrix to bf16.
 
 The reference finds ``weights.safetensors`` or ``model.safetensors`` in the model folder and
 reads tensors by name (src/engine.rs:74-79,110-225).
@@ -97,6 +101,12 @@ def find_weight_file(model_dir: str | Path) -> Path:
     raise FileNotFoundError(f"no weights.safetensors or model.safetensors in {d}")
 
 
+def stored_dtype(info) -> torch.dtype:
+    """Element type of a tensor as the source holds it (a file's header entry or a tensor)."""
+    dt = getattr(info, "torch_dtype", None)
+    return dt if dt is not None else info.dtype
+
+
 def target_dtype(role: str, stored: torch.dtype, precision: str, cast_weights: bool) -> torch.dtype:
     if role == VECTOR:
         return torch.float32
@@ -110,7 +120,10 @@ def target_dtype(role: str, stored: torch.dtype, precision: str, cast_weights: b
 
 
 def load_params(param_specs: dict[str, ParamSpec], plan: WeightPlan, file: SafeTensorsFile,
-                *, precision: str, device, cast_weights: bool = False) -> dict:
+                *, precision: str, device, cast_weights: bool | None = None) -> dict:
+    """``cast_weights``: in a ``bfloat16`` run, round matrices stored in 32-bit to bf16
+    (``True``), keep them as stored (``False``), or (``None``) round them only when the file
+    holds no bf16 matrix at all, i.e. is a full-precision checkpoint."""
     names = set(file.names())
     missing: list[str] = []
     wrong: list[str] = []
@@ -147,6 +160,10 @@ def load_params(param_specs: dict[str, ParamSpec], plan: WeightPlan, file: SafeT
     if missing or wrong or unexpected or other:
         raise WeightError(file.path, sorted(set(missing)), unexpected, wrong, other)
 
+    if cast_weights is None:
+        kinds = {stored_dtype(file.info(s.name)) for _, spec, recipe in todo
+                 if spec.role in (MATRIX, TABLE) for s in recipe.sources if s.name in names}
+        cast_weights = torch.bfloat16 not in kinds
     out: dict[str, torch.Tensor | None] = {p: None for p in param_specs}
     for path, spec, recipe in todo:
         tensors = [file.tensor(s.name) if s.name in names else None for s in recipe.sources]

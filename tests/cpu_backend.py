@@ -135,6 +135,9 @@ class CpuBackend:
                     v = logits[r, tok]
                     logits[r, tok] = v / penalty if v > 0 else v * penalty
 
+    def raise_device_errors(self):
+        pass
+
     def check_device_errors(self):
         pass
 

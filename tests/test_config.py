@@ -102,3 +102,23 @@ def test_spec_is_data_and_takes_its_numbers_from_config():
     assert spec.layers[2].mixer.args["scale"] == pytest.approx(32 ** -0.5 / 3)
     assert spec.layers[0].ffn.args == {"width": 96, "hidden": 320, "activation": ACT_ERF}
     assert spec.final_norm.args["eps"] == 1e-6 and not spec.tie_head
+
+
+def test_presets_are_config_files_read_through_the_registry():
+    from nimbus_infer_rs_b200.config import (load_preset, preset_json, preset_names,
+                                             preset_random_options)
+    assert set(preset_names()) >= {"gpt2", "gpt2-medium", "gpt2-xl", "tiny-a", "tiny-b"}
+    arch, cfg, opts = load_preset("gpt2")
+    assert arch.name == "gpt2" and opts == {"std": 0.02}
+    # the reference's defaults are this size (src/config.rs:45-66, docs/make_demo_svg.py:31)
+    assert cfg == GPT2Config.from_json({}).replace(name="gpt2")
+    assert cfg.n_params(with_linear_biases=True) == 124_439_808
+    assert load_preset("gpt2-medium")[1].n_params() == 354_823_168
+    assert load_preset("GPT2-XL")[1].n_params() == 1_557_611_200
+    _, b, opts = load_preset("tiny-b")
+    assert (b.n_layers, b.d_model, b.n_heads, b.d_mlp, b.vocab_size) == (3, 96, 3, 320, 1000)
+    assert not b.tie_embeddings and opts == {"std": 0.05, "bias_std": 0.02}
+    assert "random_weights" not in preset_json("tiny-a") and preset_random_options("tiny-a")["gamma_jitter"] == 0.02
+    for bad in ("gpt3", "../gpt2", ""):
+        with pytest.raises(ConfigError, match="no preset named"):
+            load_preset(bad)

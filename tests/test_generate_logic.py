@@ -154,8 +154,17 @@ def test_step_shapes_that_share_a_recording():
     a = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [0, 10])
     b = pack_step([(5, [9, 9, 9], [0]), (2, [7], [0])], [30, 3])          # other slots, tokens, places
     c = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [100, 10])        # a longer sequence
-    d = pack_step([(0, [1, 2], [1]), (1, [4, 5], [0])], [0, 10])          # another longest chunk
-    assert g.key(a) == g.key(b) and g.key(a) != g.key(c) and g.key(a) != g.key(d)
+    d = pack_step([(0, [1, 2], [1]), (1, [4, 5], [0])], [0, 10])          # other chunks, same total
+    assert g.key(a) == g.key(b) == g.key(d) and g.key(a) != g.key(c)
+    # chunks count in units of 128 rows, rows beyond 64 in units of 64
+    from nimbus_infer_rs_b200.engine.step_graphs import q_bound, row_padding
+    assert [q_bound(n) for n in (1, 2, 128, 129, 1000)] == [1, 128, 128, 256, 1024]
+    assert [row_padding(n) for n in (1, 64, 65, 2000)] == [1, 1, 64, 64]
+    long_a = pack_step([(0, [1] * 1000, [999]), (1, [2] * 990, [989])], [0, 0], pad_rows_to=64)
+    long_b = pack_step([(3, [1] * 1021, [1020]), (4, [2] * 985, [0])], [0, 0], pad_rows_to=64)
+    long_c = pack_step([(3, [1] * 1021, [1020]), (4, [2] * 985, [0])], [0, 10], pad_rows_to=64)
+    assert long_a.n_rows == long_b.n_rows == 2048 and g.key(long_a) == g.key(long_b)
+    assert g.key(long_c) != g.key(long_b)      # a chunk that starts inside the cache: other kernels
     assert g.kv_bound(c) == 128 and not a.is_decode
     e = pack_step([(0, [1], [0]), (1, [4], [0])], [70, 10])
     assert e.is_decode and e.want_all_rows and g.kv_bound(e) == 128
@@ -163,3 +172,24 @@ def test_step_shapes_that_share_a_recording():
     p = pack_step([(0, [1, 2, 3], [2]), (1, [4], [0])], [0, 10], pad_rows_to=8)
     assert p.n_rows == 8 and p.n_tokens == 4 and g.key(p) != g.key(a)
     assert list(p.buf[p.offs[0]:p.offs[1]]) == [1, 2, 3, 4, -1, -1, -1, -1]
+
+
+def test_a_preset_name_builds_a_model_with_no_file_on_disk(cpu_backend):
+    """``Engine.random("tiny-a")``: the preset's sizes and its spread of random values; the
+    report reads the kinds of the parts and the head counts off the model's description."""
+    e = Engine.random("tiny-a", seed=3, dtype="float32", device="cpu", cache_tokens=128)
+    again = Engine.random("tiny-a", seed=3, dtype="float32", device="cpu", cache_tokens=128)
+    other = Engine.random("tiny-a", seed=4, dtype="float32", device="cpu", cache_tokens=128)
+    w = "layers.1.ffn.fc.weight"
+    assert torch.equal(e.model.params[w], again.model.params[w])
+    assert not torch.equal(e.model.params[w], other.model.params[w])
+    assert e.model.params["layers.0.mixer.out.bias"].abs().max() > 0     # the preset's bias spread
+    info = e.inspect()
+    assert info["n_params"] == e.config.n_params() == 141_056
+    assert (info["layers"], info["heads"], info["kv_heads"], info["head_dim"]) == (2, 4, 4, 16)
+    assert (info["norm"], info["mixer"], info["ffn"], info["pos"]) == \
+        ("layernorm", "causal_attention", "dense_mlp", "learned_absolute")
+    assert info["activation"] == "gelu_tanh" and info["tie_head"]
+    assert set(info["weight_mb_by_dtype"]) == {"float32"}
+    out = e.generate([[1, 2, 3]], SamplingParams(max_new_tokens=4, temperature=0.0))
+    assert len(out[0]) == 4

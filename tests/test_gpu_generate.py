@@ -188,3 +188,138 @@ def test_top_p_inside_the_decode_session_equals_the_host_sampler(vocab):
             BatchSampler.needs_host = orig
         assert in_session == on_host, kw
         assert [len(x) for x in in_session] == [20, 20, 20]
+
+
+# ---------------------------------------------------------------------------------------------
+# The decode session: generation decodes through `DecodeSession` (fixed device buffers, the
+# step recorded in a CUDA graph, pages reserved between replays), not through `Engine.step`.
+# ---------------------------------------------------------------------------------------------
+def _session_prompts(e, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    V = e.spec.vocab_size
+    return [torch.randint(0, V, (n,), generator=g).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+def test_generation_crosses_pages_and_reaches_the_context_end_inside_the_decode_session(
+        model_dirs, name, dtype):
+    """Unequal prompts (3, 61, 64 and 70 tokens) generate until the longest allowed: every
+    sequence crosses a page end (64 tokens) *inside* the session, the prompt of 64 needs its
+    new page for the session's very first token, and the prompts of 61 and 70 run into the end
+    of the context, where their budget is clipped.  Guards `DecodeSession.step`'s
+    `cache.reserve(grow)` between replays (a page that was not reserved, or a block table that
+    was not brought up to date before the replay, would make the step read or write a wrong
+    page, and the ids would part from the plain implementation's at that token) and the
+    session's layout (`max_kv_len` pinned to the context, positions advanced on the device).
+    A second call with other lengths and the same batch size finds the buffers and the recorded
+    step that `close()` kept (`engine.decode_states`) and must be as right as the first."""
+    W = P.PlainWeights(model_dirs[name])
+    e = Engine.load(model_dirs[name], dtype=dtype, cache_tokens=4096)
+    m = e.spec.max_seq_len
+    n_new = min(m - 61, 75)
+    for call, lengths in enumerate(((3, 61, 64, 70), (66, 2, 63, 17))):
+        prompts = _session_prompts(e, lengths, seed=31 + call)
+        out = e.generate(prompts, SamplingParams(max_new_tokens=n_new, temperature=0.0))
+        crossed = 0
+        for p, o in zip(prompts, out):
+            assert len(o) == min(n_new, m - len(p))                  # clipped at the context end
+            crossed += (len(p) + len(o) - 2) // 64 > (len(p) - 1) // 64   # cached tokens: a new page
+            assert_greedy_matches(o, W, p, dtype)
+        assert crossed >= 3                     # (a prompt of 70 in a context of 128 cannot)
+        if call == 0:
+            assert len(e.decode_states) == 1                          # kept for the next batch
+            kept = next(iter(e.decode_states.values()))["graph"]
+        else:
+            assert next(iter(e.decode_states.values()))["graph"] is kept   # and used again
+    assert e.cache.slots.n_free == e.cache.n_slots
+    assert all(g.pool.n_free == g.pool.n_pages for g in e.cache.groups)
+    e.ops.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_row_that_stops_becomes_padding_while_the_others_cross_a_page(model_dirs, dtype):
+    """One sequence samples a stop token early; `DecodeSession.retire` turns its row into
+    padding (slot -1) and its slot and pages go back at once, while the other rows go on past
+    a page end.  A row that was not retired (or whose freed pages the step still wrote) would
+    change the others' ids, and the plain implementation's stop rule would not be met."""
+    W = P.PlainWeights(model_dirs["A"])
+    e = Engine.load(model_dirs["A"], dtype=dtype, cache_tokens=4096)
+    prompts = _session_prompts(e, (50, 60, 7), seed=77)
+    free_run = P.greedy_generate(W, prompts[2], 30)
+    stop = free_run[5]                                  # request 2 ends after at most 6 tokens
+    out = e.generate(prompts, SamplingParams(max_new_tokens=30, temperature=0.0, stop_tokens=[stop]))
+    for p, o in zip(prompts, out):
+        assert_greedy_matches(o, W, p, dtype, stop_tokens=(stop,))
+    assert out[2][-1] == stop and len(out[2]) <= 6
+    assert any(len(o) == 30 for o in out[:2]) or all(o[-1] == stop for o in out[:2])
+    assert e.cache.slots.n_free == e.cache.n_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_the_sessions_logits_equal_the_plain_implementations(model_dirs, name, dtype):
+    """Not only ids: after N replayed steps of a session (N chosen so that a page end lies
+    behind every row) the logits the session holds are the plain implementation's last-row
+    logits of each sequence, at the tolerance of every other logits test."""
+    from gpu_helpers import assert_close
+    from nimbus_infer_rs_b200.engine.decode import DecodeSession
+    W = P.PlainWeights(model_dirs[name])
+    e = Engine.load(model_dirs[name], dtype=dtype, cache_tokens=4096)
+    seqs = _session_prompts(e, (40, 62, 64), seed=5)
+    extra = _session_prompts(e, (30, 30, 30), seed=6)
+    slots = [e.alloc_slot() for _ in seqs]
+    e.step([(s, p[:-1], []) for s, p in zip(slots, seqs)])
+    session = DecodeSession(e, slots, [p[-1] for p in seqs])
+    n_steps = 27
+    for t in range(n_steps):
+        session.step([(seqs[i] + extra[i])[len(seqs[i]) - 1 + t] for i in range(3)])
+        session.read_tokens()
+        if t in (0, 1, 2, 5, n_steps - 1):
+            got = session.logits.clone()
+            want = torch.stack([P.forward_logits(W, (seqs[i] + extra[i])[:len(seqs[i]) + t])[-1]
+                                for i in range(3)])
+            assert_close(got, want, dtype, f"{name} session step {t}")
+    assert session._graph is not None                   # the steps after the first were replays
+    session.close()
+    for s in slots:
+        e.free_slot(s)
+
+
+def test_tiny_b_samples_at_temperature_as_the_host_sampler_does_on_plain_logits(model_dirs):
+    """Tiny B's own workload: prompts of 1 and 17 tokens, 12 steps at temperature 0.7 from a
+    fixed seed.  In 32-bit the ids must be the ones `sampling.host.sample` draws, with the same
+    per-sequence xoshiro256++ stream, from the plain implementation's logits; the comparison of
+    a sequence ends where a draw falls so close to an edge of the cumulative distribution that
+    rounding may decide it (as `assert_greedy_matches` ends at a near tie)."""
+    import copy
+
+    import numpy as np
+    from nimbus_infer_rs_b200.sampling import SequenceSampler
+    from nimbus_infer_rs_b200.sampling import host as host_sampler
+    W = P.PlainWeights(model_dirs["B"])
+    e = Engine.load(model_dirs["B"], dtype="float32", cache_tokens=1024)
+    prompts = prompts_for("B", e.spec.vocab_size)
+    assert [len(p) for p in prompts] == [1, 17]
+    params = SamplingParams(max_new_tokens=12, temperature=0.7, seed=1234)
+    out = e.generate(prompts, params)
+    assert [len(o) for o in out] == [12, 12]
+    compared = 0
+    for i, (p, o) in enumerate(zip(prompts, out)):
+        seq = SequenceSampler(params, i)
+        ctx = list(p)
+        for step, tok in enumerate(o):
+            row = P.forward_logits(W, ctx)[-1].numpy()
+            # where the draw lands in the cumulative distribution, and how near an edge
+            z = (row - row.max()) / 0.7
+            pr = np.exp(z) / np.exp(z).sum()
+            cdf = np.cumsum(pr)
+            u = copy.deepcopy(seq.rng).next_f64()          # the number this step will draw
+            want = host_sampler.sample(row.astype(np.float32), params, [], seq.rng)
+            near_edge = np.abs(cdf - u).min() < 1e-4
+            if tok != want:
+                assert near_edge, f"request {i} step {step}: got {tok}, host sampler says {want}"
+                break
+            compared += 1
+            ctx.append(tok)
+    assert compared >= 12

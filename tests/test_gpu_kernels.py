@@ -113,15 +113,20 @@ def test_linear_against_float64(ops, M, N, K, xdt, wdt):
     assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
 
 
-def _paged_cache(n_seqs, lens, Hk, hd, dtype, seed, extra_pages=3):
-    """A cache with shuffled pages, filled with random keys/values for the given lengths."""
+def _paged_cache(n_seqs, lens, Hk, hd, dtype, seed, extra_pages=3, page=PAGE, stale_nan=False):
+    """A cache with shuffled pages, filled with random keys/values for the given lengths; what
+    lies in the unused part of every page is random too, or (``stale_nan``) not a number."""
     g = torch.Generator().manual_seed(seed)
-    max_pages = max(-(-l // PAGE) for l in lens) + 1
-    n_pages = sum(-(-l // PAGE) for l in lens) + extra_pages
+    max_pages = max(-(-l // page) for l in lens) + 1
+    n_pages = sum(-(-l // page) for l in lens) + extra_pages
     perm = torch.randperm(n_pages, generator=g).tolist()
     table = torch.zeros(n_seqs + 2, max_pages, dtype=torch.int32)
-    k = torch.randn(n_pages, Hk, PAGE, hd, generator=g).to(dtype)     # stale data everywhere
-    v = torch.randn(n_pages, Hk, PAGE, hd, generator=g).to(dtype)
+    k = torch.randn(n_pages, Hk, page, hd, generator=g).to(dtype)     # stale data everywhere
+    v = torch.randn(n_pages, Hk, page, hd, generator=g).to(dtype)
+    if stale_nan:
+        k.fill_(float("nan"))
+        v.fill_(float("nan"))
+        v[::2] = float("inf")
     dense_k, dense_v = [], []
     it = iter(perm)
     for s, l in enumerate(lens):
@@ -129,13 +134,13 @@ def _paged_cache(n_seqs, lens, Hk, hd, dtype, seed, extra_pages=3):
         vs = torch.randn(l, Hk, hd, generator=g).to(dtype)
         dense_k.append(ks)
         dense_v.append(vs)
-        for p in range(-(-l // PAGE)):
-            page = next(it)
-            table[s + 1, p] = page                                      # slot = s + 1
-            n = min(PAGE, l - p * PAGE)
-            k[page, :, :n] = ks[p * PAGE:p * PAGE + n].transpose(0, 1)
-            v[page, :, :n] = vs[p * PAGE:p * PAGE + n].transpose(0, 1)
-    kv = LayerKV(k.to(DEV), v.to(DEV), table.to(DEV), PAGE, Hk, hd)
+        for p in range(-(-l // page)):
+            pg = next(it)
+            table[s + 1, p] = pg                                        # slot = s + 1
+            n = min(page, l - p * page)
+            k[pg, :, :n] = ks[p * page:p * page + n].transpose(0, 1)
+            v[pg, :, :n] = vs[p * page:p * page + n].transpose(0, 1)
+    kv = LayerKV(k.to(DEV), v.to(DEV), table.to(DEV), page, Hk, hd)
     return kv, dense_k, dense_v
 
 
@@ -181,6 +186,62 @@ def test_attention_over_paged_cache(ops, dtype, H, Hk, hd, window):
             assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (s, i)
             r += 1
     assert (out[r:] == 0).all()                  # padding rows give zeros
+
+
+def _check_attention(ops, kv, dk, dv, lens, new, H, Hk, hd, dtype, window=0, seed=5):
+    entries = [(s + 1, [0] * n, []) for s, n in enumerate(new)]
+    pos0 = [l - n for l, n in zip(lens, new)]
+    lay = build_layout(entries, pos0, DEV, pad_rows_to=8)
+    torch.manual_seed(seed)
+    qkv = torch.randn(lay.n_rows, (H + 2 * Hk) * hd, device=DEV).to(dtype)
+    out = torch.full((lay.n_rows, H * hd), 7.0, device=DEV, dtype=dtype)
+    scale = 0.37 / math.sqrt(hd)
+    ops.attention(qkv, 0, lay, kv, H, out, scale, window)
+    assert torch.isfinite(out.float()).all()
+    r = 0
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    for s, n in enumerate(new):
+        for i in range(n):
+            q = qkv[r, :H * hd].view(H, hd).cpu()
+            ref = _attention_ref(q, dk[s], dv[s], pos0[s] + i, scale, H // Hk, window)
+            got = out[r].view(H, hd).double().cpu()
+            assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (s, i)
+            r += 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, Hk, hd", [(4, 4, 32), (6, 2, 48), (12, 12, 64), (2, 1, 128)])
+def test_what_an_earlier_owner_left_in_a_page_never_reaches_a_result(ops, dtype, H, Hk, hd):
+    """Every row of every page that holds no key of its sequence is NaN (keys) and NaN or
+    infinity (values), as if an earlier owner of the page had overflowed.  A masked score is
+    replaced, but a probability of zero times such a value is NaN unless the kernel keeps the
+    value out: the results must be finite and equal to the reference's, in single decode rows
+    (the split decode kernel), in chunks (the mma.sync and the tensor-core prefill kernels,
+    by head size) and in 32-bit."""
+    lens = [200, 1, 64, 65, 333, 130]
+    kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H + hd, stale_nan=True)
+    _check_attention(ops, kv, dk, dv, lens, [1] * len(lens), H, Hk, hd, dtype)          # decode
+    _check_attention(ops, kv, dk, dv, lens, [200, 1, 3, 65, 40, 130], H, Hk, hd, dtype)   # chunks
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_cache_with_another_page_size_takes_the_generic_kernel(ops, dtype):
+    """The fast attention kernels are written for pages of 64 tokens and say so
+    (`nb_attention_*_supported` return 0 for another page size); the dispatcher then takes the
+    generic kernel, which reads any page size: same results, decode rows and chunks."""
+    H, Hk, hd, page = 4, 2, 64, 32
+    code = 0 if dtype == torch.float32 else 1
+    assert not ops.lib.nb_attention_decode_supported(code, hd, H, Hk, page)
+    assert ops.lib.nb_attention_decode_supported(code, hd, H, Hk, PAGE)
+    assert not ops.lib.nb_attention_prefill_supported(1, hd, H, Hk, page, (H + 2 * Hk) * hd, 0)
+    assert not ops.lib.nb_attention_prefill_tc_supported(1, hd, H, Hk, page, (H + 2 * Hk) * hd, 0, 1, H * hd)
+    lens = [100, 1, 32, 33, 70]
+    kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=9, page=page)
+    before = ops.launches
+    _check_attention(ops, kv, dk, dv, lens, [1] * len(lens), H, Hk, hd, dtype)
+    _check_attention(ops, kv, dk, dv, lens, [100, 1, 2, 33, 8], H, Hk, hd, dtype)
+    assert ops.launches - before == 2          # one generic launch each, no append pass
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -627,3 +688,45 @@ def test_decode_attention_appends_its_own_key_and_value(ops, dtype, H, Hk, hd, m
     ops.attention(qkv, 0, lay, kv_b, H, got, 0.2, 0, (kc, vc))
     assert torch.equal(kv_a.k, kv_b.k) and torch.equal(kv_a.v, kv_b.v)
     assert torch.equal(got, want)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_product_is_right(ops):
+    """Every wait on a barrier in the tensor-core kernels has a clock budget; a wait that runs
+    out makes the kernel give up, free what it holds, return, and raise a word in pinned host
+    memory that the host reads where it waits for results anyway.  The probe runs that same
+    bounded wait on a barrier that nothing ever completes.  Then a real product runs with a
+    budget of zero cycles: each of its waits either finds its barrier complete already or
+    gives up at once, so the kernel either finishes with the right result or returns early and
+    says so; never a wrong result without the word.  With the budget restored the same
+    product is right and nothing is reported."""
+    from nimbus_infer_rs_b200.csrc.ops import KernelError
+    ops.check_device_errors()                               # nothing pending from earlier tests
+    torch.manual_seed(3)
+    M, N, K = 128, 192, 2048
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    tol = 1e-2 * float(ref.abs().max())
+    try:
+        ops.set_wait_budget(20_000)                         # about ten microseconds
+        assert ops.wait_probe() == 2                        # gave up after the budget
+        with pytest.raises(KernelError, match="wait_probe"):
+            ops.raise_device_errors()
+        ops.raise_device_errors()                           # reading lowered the word
+        ops.set_wait_budget(0)
+        out = torch.zeros(M, N, device=DEV)
+        ops.linear(x, w, None, out)
+        try:
+            ops.check_device_errors()
+            gave_up = False
+        except KernelError as e:
+            gave_up = True
+            assert "gemm_tcgen05" in str(e)
+        if not gave_up:
+            assert (out.double() - ref).abs().max() <= tol
+    finally:
+        ops.set_wait_budget(None)
+    out = torch.zeros(M, N, device=DEV)
+    ops.linear(x, w, None, out)
+    ops.check_device_errors()
+    assert (out.double() - ref).abs().max() <= tol

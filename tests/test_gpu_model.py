@@ -13,7 +13,7 @@ from nimbus_infer_rs_b200 import Engine
 from nimbus_infer_rs_b200.cache import PAGE
 
 pytestmark = pytest.mark.gpu
-CONFIGS = ["A", "B", "C"]
+CONFIGS = ["A", "B", "C", "D"]
 
 
 def _engine(model_dirs, name, dtype, cache_tokens=2048, **kw):
@@ -134,7 +134,8 @@ def _spiky_model(tmp_path, dtype_store):
     """Tiny C with weights made so that, in layer 0, a query of token `b` scores one key of
     token `a` far above all others: the answer then hangs on that single far key."""
     from nimbus_infer_rs_b200.config import GPT2Config
-    from nimbus_infer_rs_b200.weights import gpt2_tensors, write_safetensors
+    from nimbus_infer_rs_b200.models.gpt2 import random_tensors as gpt2_tensors
+    from nimbus_infer_rs_b200.weights import write_safetensors
     from tiny_configs import TINY_C
     cfg = GPT2Config.from_json(TINY_C)
     t = gpt2_tensors(cfg, 99, std=0.05, bias_std=0.01, dtype=torch.float32)
@@ -213,8 +214,9 @@ def test_padding_changes_no_result(model_dirs, dtype):
 
 
 def test_stored_32bit_weights_stay_32bit_in_a_bfloat16_run(model_dirs):
-    e = _engine(model_dirs, "C", "bfloat16")          # tiny C is stored in fp32
+    e = _engine(model_dirs, "C", "bfloat16")          # tiny C: bf16 tables, matrices kept in fp32
     assert e.model.params["layers.0.ffn.fc.weight"].dtype == torch.float32
+    assert e.model.params["embedding.table"].dtype == torch.bfloat16
     assert e.cache.groups[0].storage.dtype == torch.bfloat16
     e = _engine(model_dirs, "A", "bfloat16")
     assert e.model.params["layers.0.ffn.fc.weight"].dtype == torch.bfloat16
@@ -312,3 +314,35 @@ def test_kernels_that_start_before_their_predecessor_ends_change_nothing(model_d
     assert torch.equal(runs[True], runs[False])
     ref = plain_logits(model_dirs[name], toks[:37])
     assert_close(runs[True][:37], ref[:37], "bfloat16", f"{name} prompt")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+def test_a_poisoned_cache_page_does_not_reach_another_request(model_dirs, name, dtype):
+    """Pages go back to the pool and are handed out again uncleared.  Here every row of every
+    page is NaN (keys) or infinite (values) before each batch, as if earlier requests had
+    overflowed: prompts of unequal lengths in one step, then single tokens across a page end,
+    must give the plain implementation's logits, because no kernel may let a row that holds
+    no key of the sequence into a sum (a zero probability times infinity is not zero)."""
+    e = _engine(model_dirs, name, dtype, cache_tokens=8 * PAGE, n_slots=3)
+    V = e.spec.vocab_size
+    for batch in range(2):
+        for g in e.cache.groups:
+            g.storage[:, 0] = float("nan")
+            g.storage[:, 1] = float("inf")
+        seqs = [random_tokens(V, n, seed=300 + 10 * batch + i) for i, n in enumerate((70, 9, 61))]
+        slots = [e.alloc_slot() for _ in seqs]
+        outs = [e.step([(s, t[:-6], list(range(len(t) - 6))) for s, t in zip(slots, seqs)])]
+        for i in range(6):
+            outs.append(e.step([(s, [t[len(t) - 6 + i]], [0]) for s, t in zip(slots, seqs)]))
+        for s in slots:
+            e.free_slot(s)
+        o = 0
+        for j, t in enumerate(seqs):
+            n = len(t) - 6
+            ref = plain_logits(model_dirs[name], t)
+            assert_close(outs[0][o:o + n], ref[:n], dtype, f"{name} batch {batch} prompt {j}")
+            assert_close(torch.cat([st[j:j + 1] for st in outs[1:]]), ref[n:], dtype,
+                         f"{name} batch {batch} decode {j}")
+            o += n
+    e.ops.check_device_errors()

@@ -1,52 +1,75 @@
-"""Real layer sizes (GPT-2 small and XL widths, full vocabulary, a few layers): the bfloat16
-engine against the float32 engine on the same seeded weights, whole prompts against token by
-token.  The plain implementation is too slow at these sizes; the float32 path, itself checked
-against it on the tiny models, is the yardstick here."""
+"""Real layer sizes (GPT-2 small, medium and XL widths and head counts, the full vocabulary,
+two layers) against the plain implementation, in 32-bit and in bfloat16, cut three ways: each
+request alone and whole; two unequal prompts in one step and then eight single-token steps of
+the batch; and the bfloat16 engine beside the float32 engine.  These are the kernels the
+benchmark runs: the tensor-core products at K = 768 ... 6400, the tensor-core prefill
+attention with heads of 64, the weight-streaming products with the folded norm, the head over
+50,257 columns."""
 import pytest
 import torch
 
-from gpu_helpers import TOL, random_tokens
+import plain_gpt2 as P
+from gpu_helpers import DTYPES, TOL, assert_close, random_tokens
 from nimbus_infer_rs_b200 import Engine
-from nimbus_infer_rs_b200.config import GPT2Config
+from nimbus_infer_rs_b200.config import GPT2Config, preset_json
+from nimbus_infer_rs_b200.weights import write_random_model
 
 pytestmark = pytest.mark.gpu
 
-SIZES = {
-    "small": {"vocab_size": 50257, "n_positions": 320, "n_embd": 768, "n_layer": 3, "n_head": 12,
-              "activation_function": "gelu_new", "model_type": "gpt2"},
-    "xl": {"vocab_size": 50257, "n_positions": 200, "n_embd": 1600, "n_layer": 2, "n_head": 25,
-           "activation_function": "gelu_new", "model_type": "gpt2"},
-}
+LAYERS, CONTEXT = 2, 192
+LENGTHS = (138, 45)          # the last 8 tokens of each are decoded one by one
+_made = {}
 
 
-def _rel(a, b):
-    return float((a.double() - b.double()).abs().max() / b.double().abs().max())
+def _model(tmp_path_factory, preset):
+    """The preset's widths with two layers and a short context, as a model folder; with what
+    the plain implementation says about the two test sequences."""
+    if preset not in _made:
+        obj = dict(preset_json(preset), n_layer=LAYERS, n_positions=CONTEXT)
+        cfg = GPT2Config.from_json(obj)
+        d = write_random_model(tmp_path_factory.mktemp(preset), cfg, 4, std=0.02, bias_std=0.01,
+                               gamma_jitter=0.02)
+        W = P.PlainWeights(d)
+        seqs = [random_tokens(cfg.vocab_size, n, seed=i + 1) for i, n in enumerate(LENGTHS)]
+        _made[preset] = (d, seqs, [P.forward_logits(W, t) for t in seqs])
+    return _made[preset]
 
 
-@pytest.mark.parametrize("name", list(SIZES))
-def test_bfloat16_follows_float32_at_real_sizes(name):
-    cfg = GPT2Config.from_json(SIZES[name])
-    opts = dict(seed=4, cache_tokens=1024, std=0.02, bias_std=0.01, gamma_jitter=0.02)
-    e32 = Engine.random(cfg, dtype="float32", **opts)
-    e16 = Engine.random(cfg, dtype="bfloat16", **opts)
-    n = cfg.max_seq_len - 8
-    seqs = [random_tokens(cfg.vocab_size, n, seed=1), random_tokens(cfg.vocab_size, 37, seed=2)]
-    out = {}
-    for tag, e in (("f32", e32), ("b16", e16)):
-        slots = [e.alloc_slot() for _ in seqs]
-        whole = e.step([(s, t[:-8], list(range(len(t) - 8))) for s, t in zip(slots, seqs)])
-        steps = [e.step([(s, [t[len(t) - 8 + i]], [0]) for s, t in zip(slots, seqs)])
-                 for i in range(8)]
-        out[tag] = (whole, torch.cat(steps))
-        # the same positions again, each sequence alone and whole: cutting changes nothing
-        for s in slots:
-            e.free_slot(s)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("preset", ["gpt2", "gpt2-medium", "gpt2-xl"])
+def test_real_widths_against_the_plain_implementation(tmp_path_factory, preset, dtype):
+    d, seqs, refs = _model(tmp_path_factory, preset)
+    e = Engine.load(d, dtype=dtype, cache_tokens=1024)
+    # each request alone and whole
+    for t, ref in zip(seqs, refs):
         s = e.alloc_slot()
-        alone = e.step([(s, seqs[1], list(range(len(seqs[1]))))])
+        out = e.step([(s, t, list(range(len(t))))])
         e.free_slot(s)
-        first = len(seqs[0]) - 8
-        cut = torch.cat([whole[first:], torch.cat(steps)[1::2]])
-        assert _rel(cut, alone) <= (2 * TOL["float32"] if tag == "f32" else TOL["bfloat16"]), tag
+        assert_close(out, ref, dtype, f"{preset} alone, {len(t)} tokens")
+    # both prompts in one step (all but the last 8 tokens), then one token each, 8 times
+    slots = [e.alloc_slot() for _ in seqs]
+    whole = e.step([(s, t[:-8], list(range(len(t) - 8))) for s, t in zip(slots, seqs)])
+    steps = [e.step([(s, [t[len(t) - 8 + i]], [0]) for s, t in zip(slots, seqs)]) for i in range(8)]
+    for s in slots:
+        e.free_slot(s)
+    o = 0
+    for j, (t, ref) in enumerate(zip(seqs, refs)):
+        n = len(t) - 8
+        assert_close(whole[o:o + n], ref[:n], dtype, f"{preset} batch prompt {j}")
+        assert_close(torch.cat([st[j:j + 1] for st in steps]), ref[n:], dtype,
+                     f"{preset} batch decode {j}")
+        o += n
+    e.ops.check_device_errors()
+
+
+@pytest.mark.parametrize("preset", ["gpt2", "gpt2-xl"])
+def test_bfloat16_follows_float32_at_real_sizes(tmp_path_factory, preset):
+    d, seqs, _ = _model(tmp_path_factory, preset)
+    outs = {}
+    for dtype in DTYPES:
+        e = Engine.load(d, dtype=dtype, cache_tokens=1024)
+        slots = [e.alloc_slot() for _ in seqs]
+        outs[dtype] = e.step([(s, t, [len(t) - 2, len(t) - 1]) for s, t in zip(slots, seqs)])
         e.ops.check_device_errors()
-    assert _rel(out["b16"][0], out["f32"][0]) <= TOL["bfloat16"]
-    assert _rel(out["b16"][1], out["f32"][1]) <= TOL["bfloat16"]
+    a, b = outs["bfloat16"].double(), outs["float32"].double()
+    assert float((a - b).abs().max() / b.abs().max()) <= TOL["bfloat16"]

@@ -60,13 +60,15 @@ def test_replay_whole_decoded_and_batched(model_dirs, tmp_path, name, dtype):
     got = torch.cat([_read(tmp_path / "dec", 1 + j, vocab) for j in range(32)])
     assert_close(got, refs[k][head:], dtype, "last 32 one by one")
 
-    # (3) one batch of unequal lengths: prompts (all but the last 4 tokens, at least 1) in one
-    # step, then one token each; shorter requests end earlier; then a second batch reuses slots
-    for rnd, ids in enumerate((["r0", "r1", "r2"], ["r3", "r1"])):
+    # (3) batches of unequal lengths: prompts (all but the last 4 tokens, at least 1) in one
+    # step, then one token each; shorter requests end earlier.  Each batch in a process of its
+    # own, then both one after the other in one process, on a cache that holds just one of them
+    # at a time: the second batch gets the slots and pages the first gave back.
+    def batch_steps(ids, first_step):
         plen = {k: max(1, len(reqs[k]) - 4) for k in ids}
-        steps = [{"step": 0, "entries": [{"id": k, "tokens": reqs[k][:plen[k]],
-                                          "want": [plen[k] - 1]} for k in ids], "end": []}]
-        pos, live, got = dict(plen), list(ids), {k: [] for k in ids}
+        steps = [{"step": first_step, "entries": [{"id": k, "tokens": reqs[k][:plen[k]],
+                                                   "want": [plen[k] - 1]} for k in ids], "end": []}]
+        pos, live = dict(plen), list(ids)
         order = [list(ids)]
         while True:
             ending = [k for k in live if pos[k] >= len(reqs[k])]
@@ -75,18 +77,34 @@ def test_replay_whole_decoded_and_batched(model_dirs, tmp_path, name, dtype):
                 live = [k for k in live if k not in ending]
             if not live:
                 break
-            steps.append({"step": len(steps), "entries": [
+            steps.append({"step": first_step + len(steps), "entries": [
                 {"id": k, "tokens": [reqs[k][pos[k]]], "want": [0]} for k in live], "end": []})
             order.append(list(live))
             for k in live:
                 pos[k] += 1
-        out = tmp_path / f"batch{rnd}"
-        held = sum(-(-len(reqs[k]) // 64) * 64 for k in ids)
-        _replay(model_dirs[name], dtype, out, steps, max_tokens=held)
+        return steps, order, plen
+
+    def check(out, first_step, order, plen, ids, what):
+        got = {k: [] for k in ids}
         for si, members in enumerate(order):
-            rows = _read(out, si, vocab)
+            rows = _read(out, first_step + si, vocab)
             assert rows.shape[0] == len(members)
             for ri, k in enumerate(members):
                 got[k].append(rows[ri:ri + 1])
         for k in ids:
-            assert_close(torch.cat(got[k]), refs[k][plen[k] - 1:], dtype, f"batch {rnd} {k}")
+            assert_close(torch.cat(got[k]), refs[k][plen[k] - 1:], dtype, f"{what} {k}")
+
+    rounds = (["r0", "r1", "r2"], ["r3", "r1"])
+    held = [sum(-(-len(reqs[k]) // 64) * 64 for k in ids) for ids in rounds]
+    for rnd, ids in enumerate(rounds):
+        steps, order, plen = batch_steps(ids, 0)
+        _replay(model_dirs[name], dtype, tmp_path / f"batch{rnd}", steps, max_tokens=held[rnd])
+        check(tmp_path / f"batch{rnd}", 0, order, plen, ids, f"batch {rnd}")
+    all_steps, parts = [], []
+    for ids in rounds:
+        steps, order, plen = batch_steps(ids, len(all_steps))
+        parts.append((len(all_steps), order, plen, ids))
+        all_steps += steps
+    _replay(model_dirs[name], dtype, tmp_path / "both", all_steps, max_tokens=max(held))
+    for rnd, (first, order, plen, ids) in enumerate(parts):
+        check(tmp_path / "both", first, order, plen, ids, f"one process, batch {rnd}")

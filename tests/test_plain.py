@@ -38,7 +38,8 @@ def test_causality_and_float32_agreement(model_dirs):
 
 def test_both_naming_schemes_read_the_same(model_dirs, tmp_path):
     from nimbus_infer_rs_b200.config import GPT2Config
-    from nimbus_infer_rs_b200.weights import gpt2_tensors, write_safetensors
+    from nimbus_infer_rs_b200.models.gpt2 import random_tensors as gpt2_tensors
+    from nimbus_infer_rs_b200.weights import write_safetensors
     from tiny_configs import TINY_A
     cfg = GPT2Config.from_json(TINY_A)
     for scheme in ("nimbus", "checkpoint"):

@@ -13,7 +13,8 @@ def _letters(arg: str) -> str:
     arg = arg.strip()
     if "*" in arg or "cudaStream_t" in arg:
         return "p"
-    for prefix, letter in (("float", "f"), ("double", "d"), ("int", "i"), ("const int", "i")):
+    for prefix, letter in (("float", "f"), ("double", "d"), ("long long", "l"), ("int", "i"),
+                           ("const int", "i")):
         if arg.startswith(prefix + " "):
             return letter
     raise AssertionError(f"argument type not understood: {arg!r}")

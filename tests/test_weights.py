@@ -6,13 +6,13 @@ import torch
 import nimbus_infer_rs_b200  # noqa: F401
 from nimbus_infer_rs_b200.config import GPT2Config, get_architecture
 from nimbus_infer_rs_b200.engine.model import Model, Runtime
+from nimbus_infer_rs_b200.models.gpt2 import random_tensors as gpt2_tensors
 from nimbus_infer_rs_b200.weights import (SafeTensorsError, SafeTensorsFile, WeightError,
-                                          find_weight_file, gpt2_tensors, load_params,
-                                          write_safetensors)
+                                          find_weight_file, load_params, write_safetensors)
 from tiny_configs import TINY_A, TINY_B, TINY_C
 
 
-def _load(cfg_json, tensors, tmp_path, precision="bfloat16", cast=False):
+def _load(cfg_json, tensors, tmp_path, precision="bfloat16", cast=None):
     cfg = GPT2Config.from_json(cfg_json)
     arch = get_architecture("gpt2")
     spec = arch.build_spec(cfg)
@@ -82,10 +82,21 @@ def test_loads_by_name_in_both_schemes(cfg_json, scheme, tmp_path):
 def test_element_types_follow_the_rule(tmp_path):
     cfg = GPT2Config.from_json(TINY_B)
     t32 = gpt2_tensors(cfg, 5, dtype=torch.float32)
-    p, _ = _load(TINY_B, t32, tmp_path, "bfloat16")
-    assert p["embedding.table"].dtype == torch.float32          # stored in 32-bit: stays so
+    p, _ = _load(TINY_B, t32, tmp_path, "bfloat16", cast=False)
+    assert p["embedding.table"].dtype == torch.float32          # kept as stored on request
     p, _ = _load(TINY_B, t32, tmp_path, "bfloat16", cast=True)
     assert p["embedding.table"].dtype == torch.bfloat16
+    # no bf16 matrix in the whole file = a full-precision checkpoint: a bfloat16 run rounds it
+    p, _ = _load(TINY_B, t32, tmp_path, "bfloat16", cast=None)
+    assert p["embedding.table"].dtype == torch.bfloat16
+    assert p["layers.1.mixer.qkv.weight"].dtype == torch.bfloat16
+    assert p["layers.1.norm_ffn.weight"].dtype == torch.float32  # vectors are always 32-bit
+    # a file of bf16 matrices in which one tensor was kept in 32-bit: that one stays 32-bit
+    mixed = dict(gpt2_tensors(cfg, 5, dtype=torch.bfloat16))
+    mixed["h.1.mlp.fc.weight"] = t32["h.1.mlp.fc.weight"]
+    p, _ = _load(TINY_B, mixed, tmp_path, "bfloat16", cast=None)
+    assert p["layers.1.ffn.fc.weight"].dtype == torch.float32
+    assert p["layers.0.ffn.fc.weight"].dtype == torch.bfloat16
     t16 = gpt2_tensors(cfg, 5, dtype=torch.bfloat16)
     p, _ = _load(TINY_B, t16, tmp_path, "bfloat16")
     assert p["layers.0.ffn.fc.weight"].dtype == torch.bfloat16  # kept in bfloat16

@@ -83,17 +83,44 @@ def test_static_scratch_variant_matches_the_usual_entry_point(dtype, H, Hk, hd, 
     torch.cuda.synchronize()
     assert torch.isfinite(want.float()).all() and (want[1] == 0).all()
 
-    # the variant that allocates nothing, twice in a row on the same built-in array
+    # a plain float64 restatement of the operation, so that this file stands on its own
+    page_of = table.cpu()
+    for r in (0, 2, n_rows - 1):
+        n_keys = int(pos[r]) + 1
+        ks = torch.cat([k[int(page_of[r, p])] for p in range(-(-n_keys // PAGE))], dim=1)[:, :n_keys]
+        vs = torch.cat([v[int(page_of[r, p])] for p in range(-(-n_keys // PAGE))], dim=1)[:, :n_keys]
+        for h in (0, H - 1):
+            qh = q[r, h * hd:(h + 1) * hd].double()
+            sc = (ks[h // (H // Hk)].double() @ qh) * scale
+            ref = torch.softmax(sc, 0) @ vs[h // (H // Hk)].double()
+            err = (want[r, h * hd:(h + 1) * hd].double() - ref).abs().max()
+            assert err <= (2e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, float(ref.abs().max()))
+
+    # the variant that allocates nothing, twice in a row on the same built-in array; between
+    # the two calls another call with other sizes and another number of splits leaves partial
+    # sums and non-zero bytes where the second call's counters and sums go
     tol = 2e-5 if dtype == torch.float32 else 1.5e-2
     for call in range(2):
         got = torch.full((n_rows, H * hd), -5.0, dtype=dtype, device=DEV)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]           # the driver's count, not torch's
         before = torch.cuda.memory_allocated()
         rc = lib.nb_attention_decode_static(*common(got), stream)
         assert rc == 0, lib.nb_last_error()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] >= free_before   # no device memory was taken
         err = (got.double() - want.double()).abs().max()
         assert err <= tol * max(1.0, float(want.double().abs().max())), (call, float(err))
+        if call == 0:
+            other = torch.empty(3, H * hd, dtype=dtype, device=DEV)
+            args = list(common(other))
+            args[19], args[20] = c_int(3), c_int(n_splits + 2)        # rows, splits
+            rc = lib.nb_attention_decode_static(*args, stream)
+            assert rc == 0, lib.nb_last_error()
+            torch.cuda.synchronize()
+            assert (other.double() - want[:3].double()).abs().max() <= \
+                tol * max(1.0, float(want.double().abs().max()))
 
 
 def test_sizes_beyond_the_built_in_array_are_refused():
