@@ -27,6 +27,7 @@ PREFILL_TARGET_CTAS = 148
 FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to this many rows
 FUSED_NORM_MAX_COLS = 16384    # ... and output columns (a long weight stream wants the leaner kernel)
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
+STREAM_MAX_ROWS = 16   # ... and with at most this many the kernel that stages weights in shared memory
 
 
 class KernelError(RuntimeError):
@@ -79,6 +80,9 @@ class CudaBackend:
         self._prefill_scr = {}
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
+        # NIMBUS_B200_STREAM=0 keeps a decode step's products on the kernel that streams weights
+        # through registers (comparison runs)
+        self.use_stream = os.environ.get("NIMBUS_B200_STREAM", "1") != "0"
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and first weight fetch overlap the tail
         # of the kernel before it (programmatic dependent launch; on by default)
         self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "1") != "0")
@@ -164,6 +168,21 @@ class CudaBackend:
         # weights faster (TMA ring), where it applies
         skinny = (M <= FUSED_NORM_MAX_ROWS or (M <= SKINNY_MAX_ROWS and not tensor_core)) \
             and (K * 32 <= 220 * 1024 if w.dtype == torch.float32 else K % 8 == 0)
+        # a decode step's products (at most 16 rows, bf16 weights): weights into shared memory
+        # before the kernel waits for its predecessor, so that they stream across kernel ends
+        if self.use_stream and M <= STREAM_MAX_ROWS and w.dtype == torch.bfloat16 and K % 8 == 0 \
+                and (norm is None or norm[3] == torch.bfloat16):
+            fused = norm is not None and self.lib.nb_gemm_stream_supported(M, N, K, 1)
+            if fused or self.lib.nb_gemm_stream_supported(M, N, K, 0):
+                if norm is not None and not fused:
+                    h = torch.empty((M, K), device=x.device, dtype=norm[3])
+                    self.layernorm(x, norm[0], norm[1], norm[2], h)
+                    x, norm = h, None
+                gamma, beta, eps = (norm[0], norm[1], norm[2]) if norm is not None else (None, None, 0.0)
+                self._call("nb_gemm_stream", _ptr(x), dtype_code(x.dtype), _ptr(gamma), _ptr(beta), eps,
+                           _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype), M, N,
+                           K, act, self._stream())
+                return
         if skinny:
             if norm is not None and (M > FUSED_NORM_MAX_ROWS or N > FUSED_NORM_MAX_COLS
                                      or w.dtype != torch.bfloat16
@@ -194,7 +213,7 @@ class CudaBackend:
 
     # A kernel whose bounded wait on a barrier ran out says so in a word of pinned host memory
     # (one per kernel family); its results are not valid.
-    _ERROR_WORDS = {0: "gemm_tcgen05", 1: "attention_prefill_tc", 2: "wait_probe"}
+    _ERROR_WORDS = {0: "gemm_tcgen05", 1: "attention_prefill_tc", 2: "wait_probe", 3: "gemm_stream"}
 
     def raise_device_errors(self) -> None:
         """Raise if a kernel that has finished reported a timed-out wait.  Reads host memory
@@ -215,7 +234,8 @@ class CudaBackend:
         """Clock cycles a wait on a barrier may take in the tensor-core kernels before the
         kernel gives up and reports it (``None``: the default, about two seconds)."""
         cycles = 4_000_000_000 if cycles is None else int(cycles)
-        for fn in ("nb_gemm_tcgen05_set_wait_budget", "nb_attention_prefill_tc_set_wait_budget"):
+        for fn in ("nb_gemm_tcgen05_set_wait_budget", "nb_attention_prefill_tc_set_wait_budget",
+                   "nb_gemm_stream_set_wait_budget"):
             rc = getattr(self.lib, fn)(cycles)
             if rc != 0:
                 raise KernelError(f"{fn} failed ({rc}): "

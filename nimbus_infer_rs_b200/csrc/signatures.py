@@ -22,6 +22,11 @@ SIGNATURES = {
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",
+    "nb_gemm_stream": "pippfppppiiiiip",
+    "nb_gemm_stream_supported": "iiii",
+    "nb_gemm_stream_plan": "iiiip",
+    "nb_gemm_stream_tune": "ii",
+    "nb_gemm_stream_set_wait_budget": "l",
     "nb_gemm_skinny_norm_supported": "iii",
     "nb_gemm_tcgen05_supported": "iiiii",
     "nb_gemm_tcgen05_error": "",

@@ -730,3 +730,64 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_product_is_right(ops):
     ops.linear(x, w, None, out)
     ops.check_device_errors()
     assert (out.double() - ref).abs().max() <= tol
+
+
+STREAM_SHAPES = [  # M, N, K, norm first?
+    (8, 2304, 768, True), (8, 768, 768, False), (8, 3072, 768, True), (8, 768, 3072, False),
+    (8, 50257, 768, True), (1, 50257, 768, True), (1, 768, 3072, False), (16, 4800, 1600, True),
+    (9, 1600, 6400, False), (16, 1600, 6400, False), (5, 777, 80, True), (7, 80, 136, False),
+    (3, 1000, 96, True), (2, 72, 8192, True), (13, 264, 1600, True), (4, 50257, 1600, True),
+    (12, 4104, 1024, True), (6, 8, 8, False)]
+
+
+@pytest.mark.parametrize("M, N, K, ln", STREAM_SHAPES)
+def test_products_of_a_decode_step(ops, M, N, K, ln):
+    """At most 16 rows, bf16 weights: the kernel that brings its weight rows into shared memory
+    before it waits for its predecessor.  One batch of columns per CTA (a layer's products), a
+    long walk through the ring (the head's 50,257 columns), K cut into chunks when a stage
+    cannot hold whole rows, rows 9..16, widths that are no multiple of 32 and outputs that are
+    no multiple of 8; with the norm of the rows folded in, bias, GELU, the residual added in
+    place, bf16 and fp32 results: all against float64."""
+    taken = bool(ops.lib.nb_gemm_stream_supported(M, N, K, 0))
+    assert ops.use_stream and (taken or K >= 6400)         # very long rows go to the other kernel
+    torch.manual_seed(M + N + K)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    if ln:
+        x = torch.randn(M, K, device=DEV) * 2 + 0.3
+        gamma, beta = torch.randn(K, device=DEV), torch.randn(K, device=DEV)
+        xd = x.double()
+        mean = xd.mean(-1, keepdim=True)
+        h = (xd - mean) / torch.sqrt(((xd - mean) ** 2).mean(-1, keepdim=True) + 1e-5) \
+            * gamma.double() + beta.double()
+        norm = (gamma, beta, 1e-5, torch.bfloat16)
+        xin = x
+    else:
+        xin = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        h, norm = xin.double(), None
+    pre = h @ w.double().t() + bias.double()
+    before = ops.launches
+    # GELU, bf16 result
+    ref = _gelu(pre, 1)
+    out = torch.full((M, N), 9.0, device=DEV, dtype=torch.bfloat16)
+    ops.linear(xin, w, bias, out, 1, None, norm)
+    tol = 1.5e-2 * float(ref.abs().max())
+    assert (out.double() - ref).abs().max() <= tol
+    # residual added in place on the fp32 stream, no bias
+    res = torch.randn(M, N, device=DEV)
+    ref = (h @ w.double().t()) + res.double()
+    stream = res.clone()
+    ops.linear(xin, w, None, stream, 0, stream, norm)
+    assert (stream.double() - ref).abs().max() <= 1.5e-2 * float(ref.abs().max())
+    fused = (not ln) or ops.lib.nb_gemm_stream_supported(M, N, K, 1)
+    if taken:
+        assert ops.launches - before == (2 if fused else 4)     # a norm that cannot be folded in runs first
+    # the other kernel for few rows gives the same within rounding
+    ops.use_stream = False
+    try:
+        other = res.clone()
+        ops.linear(xin, w, None, other, 0, other, norm)
+    finally:
+        ops.use_stream = True
+    assert (other.double() - stream.double()).abs().max() <= 1.5e-2 * float(ref.abs().max())
+    ops.check_device_errors()
