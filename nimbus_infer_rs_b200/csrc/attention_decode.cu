@@ -288,7 +288,10 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int HD, typename TOut>
+// MMA_STAGES: pages (keys and values) in flight per CTA: three when the CTAs of a launch fit
+// on the GPU with them (a short chain per CTA wants its pages early), two when more CTAs per
+// SM matter more (a large batch).
+template <int HD, typename TOut, int MMA_STAGES>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, int q_col,
                             const int* __restrict__ row_slot, const int* __restrict__ row_pos,
@@ -305,22 +308,28 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size not supported");
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                   // [2 stages][K | V][64][ROW]
+  bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                   // [stages][K | V][64][ROW]
   // the warps' partial results, after the last page has been read: over the page tiles
   // (more CTAs fit on an SM that way)
   float* w_acc = reinterpret_cast<float*>(smem_raw);                 // [WARPS][GH][HD]
   float* w_ml = w_acc + WARPS * GH * HD;                             // [WARPS][GH][2]
   static_assert((size_t)(WARPS * GH * HD + WARPS * GH * 2) * sizeof(float) <=
-                    (size_t)4 * STILE * sizeof(bf16), "partial results must fit in the page tiles");
+                    (size_t)2 * MMA_STAGES * STILE * sizeof(bf16), "partial results must fit in the page tiles");
   __shared__ int s_last;
 
-  nb_grid_dependency_wait();
+  // Before the wait: where the row's pages lie, and its first pages on their way.  The batch
+  // layout, the block table and the pages were written at least two kernels ago (earlier
+  // steps, host copies); the only thing the kernel in front of this one writes is the step's
+  // own rows (queries, and the new key and value, which are patched into the staged page
+  // after the wait).
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_heads = kv.n_kv_heads * group;
   const int slot = row_slot[r];
   if (slot < 0) {   // padding row: zeros, written by split 0
+    nb_grid_dependency_wait();
+    nb_launch_dependents();
     if (split == 0)
       for (int i = tid; i < group * HD; i += THREADS)
         out[(size_t)r * out_stride + (size_t)kvh * group * HD + i] = nb_from_f32<TOut>(0.0f);
@@ -349,9 +358,16 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
       cp_async16(kdst + row * ROW + c * 8, ksrc + row * HD + c * 8);
       cp_async16(vdst + row * ROW + c * 8, vsrc + row * HD + c * 8);
     }
-    cp_async_commit();
   };
-  if (p_begin < p_end) issue(p_begin, 0);
+  // one commit group per stage of the ring, also an empty one: the count of groups in flight
+  // then says which page has landed
+#pragma unroll
+  for (int i = 0; i < MMA_STAGES; ++i) {
+    if (p_begin + i < p_end) issue(p_begin + i, i);
+    cp_async_commit();
+  }
+
+  nb_grid_dependency_wait();
 
   // Q^T as the B operand of the score product: column g of the block is query head g of the
   // group (zero beyond the group); this thread holds rows 2t, 2t+1 and 2t+8, 2t+9 of each k-step
@@ -376,14 +392,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = scale * 1.4426950408889634f;
 
+  int stage = 0;
   for (int p = p_begin; p < p_end; ++p) {
-    const int stage = (p - p_begin) & 1;
-    if (p + 1 < p_end) {
-      issue(p + 1, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    cp_async_wait<MMA_STAGES - 1>();   // all but the newest groups: page p is in
     __syncthreads();
     bf16* kt = tiles + (size_t)stage * 2 * STILE;
     bf16* vt = kt + STILE;
@@ -419,12 +430,26 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     }
     const int key0 = p * PAGE_TOKENS + warp * 16;     // first key of this warp's 16
     if (key0 < kv_len && key0 + 16 > j_begin) {       // warp-uniform: something to attend to
-      float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // the k-steps of the score product in accumulators of their own, added up afterwards:
+      // a tensor-core instruction takes long to hand its result to the next one
+      float sck[KS < 4 ? KS : 4][4];
+#pragma unroll
+      for (int i = 0; i < (KS < 4 ? KS : 4); ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sck[i][j] = 0.0f;
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         uint32_t ka[4];
         ldsm_x4(ka, kt + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
-        mma_16816(sc, ka, qb[ks][0], qb[ks][1]);
+        mma_16816(sck[ks & 3], ka, qb[ks][0], qb[ks][1]);
+      }
+      float sc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a = sck[0][j];
+#pragma unroll
+        for (int i = 1; i < (KS < 4 ? KS : 4); ++i) a += sck[i][j];
+        sc[j] = a;
       }
       const int ja = key0 + g, jb = ja + 8;
       const bool va = ja >= j_begin && ja < kv_len, vb = jb >= j_begin && jb < kv_len;
@@ -467,8 +492,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
         mma_16816(o[i], va4, pb0, pb1);
       }
     }
-    __syncthreads();   // the stage is free for the copy after next
+    __syncthreads();   // the stage is free: the page after the ones in flight goes there
+    if (p + MMA_STAGES < p_end) issue(p + MMA_STAGES, stage);
+    cp_async_commit();
+    if (++stage == MMA_STAGES) stage = 0;
   }
+  cp_async_wait<0>();
 
   nb_launch_dependents();   // the pages are read: the next kernel may be set up
   // row sums over the lanes that share a head (different keys), then the warps
@@ -546,20 +575,48 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   }
 }
 
-template <int HD, typename TOut>
-int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
-               int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
-               int k_col, int v_col, cudaStream_t stream) {
-  const size_t smem = (size_t)4 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
-  auto kern = attention_decode_mma_kernel<HD, TOut>;
-  if (smem > 48 * 1024)
+template <int HD, typename TOut, int MMA_STAGES>
+int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
+                 const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+                 int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
+                 int k_col, int v_col, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * MMA_STAGES * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
+  auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES>;
+  static bool configured = false;   // per instantiation
+  if (smem > 48 * 1024 && !configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
   NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride, q_col,
                     row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits,
                     part_acc, part_ml, counters, append, k_col, v_col));
   return 0;
+}
+
+template <int HD, typename TOut>
+int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
+               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+               int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
+               int k_col, int v_col, cudaStream_t stream) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  // CTAs of three stages that fit on an SM (of 220 KB), and whether the launch fits with them
+  const size_t smem3 = (size_t)6 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
+  const long long ctas = (long long)n_splits * kv.n_kv_heads * n_rows;
+  const long long room3 = (long long)((220 * 1024) / smem3) * sms;
+  if (ctas <= room3)
+    return launch_mma_s<HD, TOut, 3>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
+                                     scale, window, n_rows, n_splits, part_acc, part_ml, counters,
+                                     append, k_col, v_col, stream);
+  return launch_mma_s<HD, TOut, 2>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
+                                   scale, window, n_rows, n_splits, part_acc, part_ml, counters, append,
+                                   k_col, v_col, stream);
 }
 
 template <typename TOut>

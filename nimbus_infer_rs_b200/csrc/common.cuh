@@ -73,14 +73,18 @@ __device__ __forceinline__ void nb_report_timeout(int* err_word) {
 // ---------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched through nb_launch with overlap enabled
 // may start while the kernel before it in the stream is still running; it must execute
-// nb_grid_dependency_wait() before it reads anything an earlier kernel wrote or writes
-// anything at all (before that point it may only fetch constants: weights, biases), and it
-// must do so in every CTA, also in one that has nothing to do: a grid that ended without
-// waiting would let its own successor run ahead of the kernel before it.  A kernel calls
-// nb_launch_dependents() once its own loads are in (the products and the decode attention: at
-// the start of the kernel the successor's loads compete with its own and the chain gets
-// slower) so that its successor is set up while it finishes.  Without the launch attribute
-// both instructions do nothing.
+// nb_grid_dependency_wait() before it reads anything that kernel wrote or writes anything at
+// all, and it must do so in every CTA, also in one that has nothing to do: a grid that ended
+// without waiting would let its own successor run ahead of the kernel before it.
+//
+// Every kernel of this library calls nb_launch_dependents() only AFTER its own wait.  A kernel
+// therefore starts at the earliest when its predecessor's wait is over, i.e. when everything
+// before the predecessor is complete: before its own wait a kernel may read constants
+// (weights, biases) and anything written by kernels two or more places ahead of it in the
+// stream (the cache of earlier steps, the batch layout), but nothing its direct predecessor
+// writes.  Where the trigger sits after the wait is a matter of speed: the products and the
+// decode attention give it once their own loads are on their way.  Without the launch
+// attribute both instructions do nothing.
 // ---------------------------------------------------------------------------------
 bool nb_overlap_enabled();
 

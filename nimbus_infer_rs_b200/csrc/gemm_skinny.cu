@@ -337,8 +337,8 @@ gemm_skinny_f32_kernel(const TX* __restrict__ X, const float* __restrict__ gamma
                        int N, int K, int act) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);  // [F32_ROWS][K]
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.x * F32_WARPS + warp;
   const float* wrow = W + (size_t)(n < N ? n : 0) * K;

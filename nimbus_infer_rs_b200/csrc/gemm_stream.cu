@@ -20,9 +20,8 @@
 // ring: a product with few columns has one item per CTA, all of it requested before the wait;
 // the output head (50,257 columns) is a long walk with the ring refilled as stages drain.
 //
-// Before the wait a kernel may touch constants only (weights, biases, norm vectors): the
-// kernel in front of it may itself have started before *its* predecessor ended, so nothing
-// that any kernel of the step writes is safe to read there.
+// Before the wait a kernel touches constants only (weights, biases, norm vectors); it lets its
+// successor start right after its own wait, as every kernel of the library does (common.cuh).
 //
 // Every wait on an mbarrier is bounded by a clock budget; a wait that runs out raises an error
 // word, the CTA skips its stores, gives its copies time to land and returns.
@@ -94,7 +93,6 @@ struct StreamShape {
   int tpr;        // threads that share a row while it is normalised
   int n16;        // groups of 16 columns of the whole product
   unsigned vpr_magic;   // ceil(2^32 / vectors per staged row): index / vectors = umulhi(index, magic)
-  int trigger_late;     // let the next kernel start only once this one's wait is over
 };
 
 // The tensor-core instruction takes 16 x 16 of one operand and 16 x 8 of the other.  The weights
@@ -118,6 +116,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
   constexpr int NT = NW * 32;
   constexpr int NH = HI ? 2 : 1;
   constexpr int MP = HI ? 16 : 8;          // rows of the step as the instruction sees them
+  // 32-column steps per turn of the product loop (four, with eight accumulators, measured
+  // slower: 0.392 against 0.354 ms a decode step at batch 8)
+  constexpr int SPI = 2;
+  constexpr int NCH = 2 * SPI;             // accumulators per column group and half
   constexpr int EPT = 4;                   // outputs a thread finishes per batch when warps split K
   constexpr int ROUND = sizeof(TX) == 2 ? 12 : 6;   // vectors a thread copies per trip to L2
   extern __shared__ unsigned char smem_dyn[];
@@ -177,8 +179,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
       if (++fill_c == sh.n_kc) { fill_c = 0; ++fill_b; }
     }
   }
-  // the weights are asked for: the kernel behind this one may start and ask for its own
-  if (!sh.trigger_late) nb_launch_dependents();
 
   // ---- constants, indices and addresses, while the kernel in front finishes: after the wait
   // every instruction is on the step's critical path
@@ -210,15 +210,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
   // byte offsets of this lane's two pieces in a row of a box (even and odd 32-column step)
   const int piece0 = ((t ^ g) & 7) << 4, piece1 = (((4 + t) ^ g) & 7) << 4;
   const int w_row0 = (gw * 16 + g) * 128;                  // row g of the warp's first group
-  // four accumulator chains per column group (two 32-column steps in flight, two instructions
-  // each): a warp's instructions then do not wait for one another
-  float acc[GPW][NH][4][4];
+  // accumulators: one per instruction of a turn (see the loop)
+  float acc[GPW][NH][NCH][4];
 #pragma unroll
   for (int i = 0; i < GPW; ++i)
 #pragma unroll
     for (int h = 0; h < NH; ++h)
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
+      for (int q = 0; q < NCH; ++q)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][h][q][j] = 0.0f;
   // staging: which vectors this thread brings in
@@ -240,7 +239,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
   const float inv_k = 1.0f / (float)K;
 
   nb_grid_dependency_wait();
-  if (sh.trigger_late) nb_launch_dependents();
+  // this kernel's weights were asked for long ago: the kernel behind it may start and ask for
+  // its own (only now: see common.cuh on what a kernel may read before its wait)
+  nb_launch_dependents();
 
   // what the first batch's epilogue adds, asked for before anything else
   float e_res[EPT];
@@ -354,38 +355,37 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
     if (ok) {
       const int k0 = c * sh.n_kbox * 64;
       const int steps = min(sh.n_kbox * 2, (k_pad - k0) >> 5);       // 32-column steps of the item
-      for (int ks = kpart; ks < steps; ks += 2 * wk) {
-        const int ks1 = ks + wk;
-        const bool two = ks1 < steps;
-        uint4 xl0 = zero4, xl1 = zero4, xh0 = zero4, xh1 = zero4;
-        if (row_lo) xl0 = *reinterpret_cast<const uint4*>(x_lo + k0 + ks * 32);
-        if (row_lo && two) xl1 = *reinterpret_cast<const uint4*>(x_lo + k0 + ks1 * 32);
-        if (row_hi) xh0 = *reinterpret_cast<const uint4*>(x_hi + k0 + ks * 32);
-        if (row_hi && two) xh1 = *reinterpret_cast<const uint4*>(x_hi + k0 + ks1 * 32);
-        const int o0 = (ks >> 1) * box_bytes + ((ks & 1) ? piece1 : piece0);
-        const int o1 = (ks1 >> 1) * box_bytes + ((ks1 & 1) ? piece1 : piece0);
-        uint4 wa0[GPW], wb0[GPW], wa1[GPW], wb1[GPW];
+      for (int ks = kpart; ks < steps; ks += SPI * wk) {
+        // SPI 32-column steps per turn, two instructions each, every one with an accumulator
+        // of its own: a tensor-core instruction of this kind takes a few hundred clocks to hand
+        // its result on, so none of a turn's instructions waits for another
+        uint4 xl[SPI], xh[SPI], wa[GPW][SPI], wb[GPW][SPI];
 #pragma unroll
-        for (int i = 0; i < GPW; ++i) {
-          const unsigned char* wr = st + i * sh.wn * (16 * 128);
-          wa0[i] = *reinterpret_cast<const uint4*>(wr + o0);
-          wb0[i] = *reinterpret_cast<const uint4*>(wr + 8 * 128 + o0);
-          wa1[i] = two ? *reinterpret_cast<const uint4*>(wr + o1) : zero4;
-          wb1[i] = two ? *reinterpret_cast<const uint4*>(wr + 8 * 128 + o1) : zero4;
+        for (int u = 0; u < SPI; ++u) {
+          const int k1 = ks + u * wk;
+          const bool in = k1 < steps;
+          xl[u] = (row_lo && in) ? *reinterpret_cast<const uint4*>(x_lo + k0 + k1 * 32) : zero4;
+          xh[u] = (row_hi && in) ? *reinterpret_cast<const uint4*>(x_hi + k0 + k1 * 32) : zero4;
+          const int off = (k1 >> 1) * box_bytes + ((k1 & 1) ? piece1 : piece0);
+#pragma unroll
+          for (int i = 0; i < GPW; ++i) {
+            const unsigned char* wr = st + i * sh.wn * (16 * 128);
+            wa[i][u] = in ? *reinterpret_cast<const uint4*>(wr + off) : zero4;
+            wb[i][u] = in ? *reinterpret_cast<const uint4*>(wr + 8 * 128 + off) : zero4;
+          }
         }
 #pragma unroll
-        for (int i = 0; i < GPW; ++i) {
-          // K is permuted inside a 32-column step: lane group t owns columns 8t..8t+7 of both
-          // operands, which a dot product does not mind
-          mma_16816(acc[i][0][0], wa0[i].x, wb0[i].x, wa0[i].y, wb0[i].y, xl0.x, xl0.y);
-          mma_16816(acc[i][0][1], wa0[i].z, wb0[i].z, wa0[i].w, wb0[i].w, xl0.z, xl0.w);
-          mma_16816(acc[i][0][2], wa1[i].x, wb1[i].x, wa1[i].y, wb1[i].y, xl1.x, xl1.y);
-          mma_16816(acc[i][0][3], wa1[i].z, wb1[i].z, wa1[i].w, wb1[i].w, xl1.z, xl1.w);
-          if constexpr (HI) {
-            mma_16816(acc[i][1][0], wa0[i].x, wb0[i].x, wa0[i].y, wb0[i].y, xh0.x, xh0.y);
-            mma_16816(acc[i][1][1], wa0[i].z, wb0[i].z, wa0[i].w, wb0[i].w, xh0.z, xh0.w);
-            mma_16816(acc[i][1][2], wa1[i].x, wb1[i].x, wa1[i].y, wb1[i].y, xh1.x, xh1.y);
-            mma_16816(acc[i][1][3], wa1[i].z, wb1[i].z, wa1[i].w, wb1[i].w, xh1.z, xh1.w);
+        for (int u = 0; u < SPI; ++u) {
+#pragma unroll
+          for (int i = 0; i < GPW; ++i) {
+            // K is permuted inside a 32-column step: lane group t owns columns 8t..8t+7 of both
+            // operands, which a dot product does not mind
+            mma_16816(acc[i][0][2 * u], wa[i][u].x, wb[i][u].x, wa[i][u].y, wb[i][u].y, xl[u].x, xl[u].y);
+            mma_16816(acc[i][0][2 * u + 1], wa[i][u].z, wb[i][u].z, wa[i][u].w, wb[i][u].w, xl[u].z, xl[u].w);
+            if constexpr (HI) {
+              mma_16816(acc[i][1][2 * u], wa[i][u].x, wb[i][u].x, wa[i][u].y, wb[i][u].y, xh[u].x, xh[u].y);
+              mma_16816(acc[i][1][2 * u + 1], wa[i][u].z, wb[i][u].z, wa[i][u].w, wb[i][u].w, xh[u].z, xh[u].w);
+            }
           }
         }
       }
@@ -399,8 +399,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
 #pragma unroll
         for (int h = 0; h < NH; ++h)
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            acc[i][h][0][j] = (acc[i][h][0][j] + acc[i][h][1][j]) + (acc[i][h][2][j] + acc[i][h][3][j]);
+          for (int j = 0; j < 4; ++j) {
+            float a = (acc[i][h][0][j] + acc[i][h][1][j]) + (acc[i][h][2][j] + acc[i][h][3][j]);
+            if constexpr (NCH == 8)
+              a += (acc[i][h][4][j] + acc[i][h][5][j]) + (acc[i][h][6][j] + acc[i][h][7][j]);
+            acc[i][h][0][j] = a;
+          }
     }
     // a thread holds, per column group and half: columns g and g + 8 of the group (j = 0,1 and
     // j = 2,3), rows 2t and 2t + 1 of the step (+ 8 in the upper half)
@@ -487,7 +491,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restri
 #pragma unroll
         for (int h = 0; h < NH; ++h)
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+          for (int q = 0; q < NCH; ++q)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][h][q][j] = 0.0f;
     }
@@ -527,7 +531,6 @@ struct StreamPlan {
 };
 
 int g_target_ctas = 0;    // 0: about two CTAs per SM at most; see plan_stream
-int g_trigger_late = 1;
 int g_sms = 0;
 int sm_count() {
   if (g_sms == 0) {
@@ -556,7 +559,6 @@ StreamPlan plan_stream(int M, int N, int K, bool ln) {
   const int nt = p.nw * 32;
   StreamShape& sh = p.sh;
   sh.n16 = n16;
-  sh.trigger_late = g_trigger_late;
   sh.vpr_magic = (unsigned)((0x100000000ull + (unsigned)(k_pad / 8) - 1) / (unsigned)(k_pad / 8));
   if ((long long)(M + 16) * (k_pad / 8) >= (1 << 20)) return p;   // the division by multiplication is exact below
   if ((long long)M * N >= (1ll << 31) || (long long)M * K >= (1ll << 31)) return p;   // 32-bit offsets
@@ -578,54 +580,69 @@ StreamPlan plan_stream(int M, int N, int K, bool ln) {
   const size_t x_bytes = (((size_t)M * sh.x_stride * 2) + 15) & ~(size_t)15;
   const size_t tail = (ln ? (size_t)2 * k_pad * 4 : 0) + (size_t)p.nw * 4 + 8 * 8 + 16 + 1024 /* alignment */;
   const int mp_rows = M > 8 ? 16 : 8;
-  // CTAs: one per SM for a walk; else as many as there are column groups, up to two per SM
-  // (every CTA stages all the rows, which costs a trip to L2 whatever their number; the
-  // tensor-core instructions of this path are slow, so they are spread over all SMs)
-  int ctas = walk ? sms : (n16 < 2 * sms ? n16 : 2 * sms);
-  if (!walk && g_target_ctas > 0 && ctas > g_target_ctas) ctas = g_target_ctas;
-  for (; ctas >= 1; ctas = ctas > 1 ? (ctas + 1) / 2 : 0) {
-    const int per_cta = (n16 + ctas - 1) / ctas;          // most column groups of a CTA
-    // groups per batch: all of a CTA's if it has few (one batch, everything asked for before
-    // the wait); a walk takes a warp's worth at a time
-    int GB = 1;
-    while (GB < per_cta && GB < p.nw) GB <<= 1;
-    if (!walk && GB < per_cta) continue;                  // too many groups for one batch
-    for (; GB >= 1; GB >>= 1) {
-      if (!walk && GB < per_cta) break;
-      sh.GB = GB;
-      sh.wn = GB < p.nw ? GB : p.nw;
-      const int wk = p.nw / sh.wn;
-      if (wk > 1 && (GB * 16 * mp_rows + nt - 1) / nt > 4) continue;   // the epilogue's four outputs a thread
-      const size_t red_bytes = wk > 1 ? (size_t)wk * mp_rows * GB * 16 * 4 : 0;
-      if (x_bytes + red_bytes + tail >= (size_t)SMEM_LIMIT) continue;
-      const size_t room = SMEM_LIMIT - x_bytes - red_bytes - tail;
-      const size_t box = (size_t)GB * 16 * 128;
-      sh.S = 0;
-      if (!walk) {   // whole rows, one item
-        if ((size_t)n_box_k * box <= room) {
-          sh.n_kbox = n_box_k;
-          sh.n_kc = 1;
-          sh.S = 1;
-        }
-      } else {       // a ring of at least three stages of at most 48 KB
-        for (int nkb = n_box_k; nkb >= 1; --nkb) {
-          const size_t stage = (size_t)nkb * box;
-          const int fit = (int)(room / stage);
-          if (fit >= 3 && (stage <= 48 * 1024 || nkb == 1)) {
-            sh.n_kbox = nkb;
-            sh.n_kc = (n_box_k + nkb - 1) / nkb;
-            sh.S = fit < 6 ? fit : 6;
-            break;
+  // CTAs: one per SM for a walk.  Else every CTA gets the same number of column groups (the
+  // slowest CTA sets the time), as few as keep the CTAs within one per SM; every CTA stages
+  // all the rows, which costs a trip to L2 whatever their number, and the tensor-core
+  // instructions of this path are slow, so the work is spread over the SMs.  First choice:
+  // whole rows of a CTA's groups in shared memory, everything asked for before the wait; if
+  // that does not fit, fewer groups per CTA (more CTAs than SMs then, up to two per SM); if
+  // nothing fits whole, K in chunks through a ring of two stages.
+  const int cap = (!walk && g_target_ctas > 0) ? g_target_ctas : sms;
+  const int per0 = walk ? 0 : (n16 + cap - 1) / cap;
+  // (pass 0: whole rows, all CTAs on the GPU at once; pass 1: a ring; pass 2: whole rows, a few
+  // CTAs in a second wave)
+  for (int pass = 0; pass < (walk ? 1 : 3); ++pass) {
+    for (int per = per0; per >= (walk ? 0 : 1); --per) {
+      const int ctas = walk ? sms : (n16 + per - 1) / per;
+      if (!walk && ctas > 2 * sms) break;
+      int GB = 1;
+      if (walk) {
+        GB = p.nw;
+      } else {
+        while (GB < per) GB <<= 1;
+        if (GB > 2 * p.nw) break;
+      }
+      for (; GB >= 1; GB >>= 1) {
+        if (!walk && GB < per) break;
+        sh.GB = GB;
+        sh.wn = GB < p.nw ? GB : p.nw;
+        const int wk = p.nw / sh.wn;
+        if (wk > 1 && (GB * 16 * mp_rows + nt - 1) / nt > 4) continue;   // the epilogue's four outputs a thread
+        const size_t red_bytes = wk > 1 ? (size_t)wk * mp_rows * GB * 16 * 4 : 0;
+        if (x_bytes + red_bytes + tail >= (size_t)SMEM_LIMIT) continue;
+        const size_t room = SMEM_LIMIT - x_bytes - red_bytes - tail;
+        const size_t box = (size_t)GB * 16 * 128;
+        sh.S = 0;
+        if (!walk && pass != 1) {   // whole rows, one item
+          if ((size_t)n_box_k * box <= room) {
+            sh.n_kbox = n_box_k;
+            sh.n_kc = 1;
+            sh.S = 1;
+          }
+        } else {       // a ring: three stages of at most 48 KB for a walk, two large ones else
+          const int want = walk ? 3 : 2;
+          for (int nkb = n_box_k; nkb >= 1; --nkb) {
+            const size_t stage = (size_t)nkb * box;
+            const int fit = (int)(room / stage);
+            if (!walk && stage < 16 * 1024) break;   // a ring of crumbs: leave it to the other kernel
+            if (fit >= want && (!walk || stage <= 48 * 1024 || nkb == 1)) {
+              sh.n_kbox = nkb;
+              sh.n_kc = (n_box_k + nkb - 1) / nkb;
+              sh.S = walk ? (fit < 6 ? fit : 6) : 2;
+              if (sh.S > sh.n_kc) sh.S = sh.n_kc;
+              break;
+            }
           }
         }
+        if (sh.S == 0) continue;
+        p.smem = (size_t)sh.S * sh.n_kbox * box + x_bytes + red_bytes + tail;
+        if (pass == 0 && !walk && ctas > sms && p.smem > (size_t)SMEM_LIMIT / 2) continue;
+        p.grid = ctas;
+        p.ok = true;
+        return p;
       }
-      if (sh.S == 0) continue;
-      p.smem = (size_t)sh.S * sh.n_kbox * box + x_bytes + red_bytes + tail;
-      p.grid = ctas;
-      p.ok = true;
-      return p;
+      if (walk || pass == 1) break;   // the ring is tried for the widest cut only
     }
-    if (walk) break;
   }
   return p;
 }
@@ -719,11 +736,10 @@ NB_EXPORT int nb_gemm_stream_plan(int M, int N, int K, int ln, int* out) {
   return 1;
 }
 
-// Tuning: the most CTAs a product is cut into (0: up to two per SM), and whether
-// a kernel lets its successor start only after its own wait is over (1) or at once (0).
-NB_EXPORT int nb_gemm_stream_tune(int target_ctas, int trigger_late) {
+// Tuning: the most CTAs a product is cut into (0: one per SM at most, every CTA as many column
+// groups as the others).
+NB_EXPORT int nb_gemm_stream_tune(int target_ctas) {
   g_target_ctas = target_ctas > 0 ? target_ctas : 0;
-  g_trigger_late = trigger_late != 0;
   return 0;
 }
 

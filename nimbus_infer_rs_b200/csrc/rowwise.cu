@@ -68,8 +68,8 @@ template <typename T>
 __global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
                                  float* __restrict__ out, int d) {
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x;
   const int tok = tokens[r];
   float* o = out + (size_t)r * d;
@@ -115,8 +115,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  TOut* __restrict__ out, int d, float eps) {
   extern __shared__ float row[];
   __shared__ float red[32];
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   TOut* o = out + (size_t)r * d;
@@ -153,8 +153,8 @@ __global__ void __launch_bounds__(128)
 layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                       const float* __restrict__ gamma, const float* __restrict__ beta,
                       TOut* __restrict__ out, int n_rows, int d, float eps) {
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= n_rows) return;
   const int src = rows ? rows[r] : r;
@@ -363,8 +363,8 @@ NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col
 __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ next,
                                       int* __restrict__ row_pos, const int* __restrict__ row_slot,
                                       int n) {
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (row_slot[i] >= 0) {

@@ -38,8 +38,8 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
 __global__ void history_append_kernel(int* __restrict__ history, int history_stride,
                                       int* __restrict__ history_len, const int* __restrict__ tokens,
                                       const int* __restrict__ row_slot, int n) {
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n || row_slot[i] < 0) return;
   const int len = history_len[i];
@@ -55,8 +55,8 @@ __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
   __shared__ float s_val[THREADS];
   __shared__ int s_idx[THREADS];
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   // every thread starts from element 0, as the reference's scan does
@@ -102,8 +102,8 @@ argmax_split_kernel(const float* __restrict__ logits, int vocab, int* __restrict
                     unsigned long long* __restrict__ keys, int* __restrict__ counters) {
   __shared__ unsigned long long s_key[THREADS / 32];
   __shared__ int s_last;
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.y, tid = threadIdx.x;
   const int per = (vocab + gridDim.x - 1) / gridDim.x;
   const int i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
@@ -149,8 +149,8 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, float tem
                           const double* __restrict__ u, int* __restrict__ out) {
   __shared__ double s_red[THREADS];
   __shared__ int s_choice;
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const double temp = fmax((double)temperature, 1e-6);
@@ -326,8 +326,8 @@ sample_top_k_kernel(const float* __restrict__ logits, int vocab, int k, float te
   __shared__ float s_maxf[CAND_THREADS / 32];
   __shared__ double s_red[CAND_THREADS];
   __shared__ int s_choice;
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   if (tid == 0) { s_prefix = 0u; s_mask = 0u; s_remaining = (unsigned)k; s_nan = 0u; s_choice = -1; }
@@ -469,8 +469,8 @@ sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float to
   __shared__ double s_red[CAND_THREADS];
   __shared__ unsigned long long s_last_kept;
   __shared__ int s_choice;
-  nb_launch_dependents();
   nb_grid_dependency_wait();
+  nb_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const int n_keep = min(TOPP_KEEP, vocab);

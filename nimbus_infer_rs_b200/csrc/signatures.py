@@ -25,7 +25,7 @@ SIGNATURES = {
     "nb_gemm_stream": "pippfppppiiiiip",
     "nb_gemm_stream_supported": "iiii",
     "nb_gemm_stream_plan": "iiiip",
-    "nb_gemm_stream_tune": "ii",
+    "nb_gemm_stream_tune": "i",
     "nb_gemm_stream_set_wait_budget": "l",
     "nb_gemm_skinny_norm_supported": "iii",
     "nb_gemm_tcgen05_supported": "iiiii",
