@@ -370,6 +370,17 @@ class CudaBackend:
                        (dtype_code(out.dtype)), (out.shape[1]), (scale),
                        (window), (layout.n_seqs), (layout.max_q_len), self._stream())
             return
+        if (not layout.is_decode) and q_src.dtype == torch.float32 and \
+                self.lib.nb_attention_prefill_f32_supported(kv.head_dim, n_heads, kv.n_kv_heads, kv.page):
+            # the 32-bit path's prompts: tiles of 64 rows, fp32 multiply-adds
+            if layout.n_rows > layout.n_tokens:
+                out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
+            self._call("nb_attention_prefill_f32", _ptr(q_src), dtype_code(q_src.dtype), q_src.shape[1],
+                       q_col, _ptr(layout.cu_rows), _ptr(layout.seq_slot), _ptr(layout.seq_pos0),
+                       _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1], kv.page,
+                       n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out), dtype_code(out.dtype),
+                       out.shape[1], scale, window, layout.n_seqs, layout.max_q_len, self._stream())
+            return
         self._call("nb_attention_generic", _ptr(q_src), (dtype_code(q_src.dtype)),
                    (q_src.shape[1]), (q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
                    _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), (kv.block_table.shape[1]),

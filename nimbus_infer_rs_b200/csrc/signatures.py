@@ -14,6 +14,8 @@ SIGNATURES = {
     "nb_attention_decode_static": "piiipppppiiiiipiifiiip",
     "nb_attention_generic": "piiipppppiiiiipiifiip",
     "nb_attention_prefill_supported": "iiiiiii",
+    "nb_attention_prefill_f32_supported": "iiii",
+    "nb_attention_prefill_f32": "piiippppppiiiiipiifiiip",
     "nb_attention_prefill": "piiippppppiiiiipiifiiip",
     "nb_attention_prefill_tc_supported": "iiiiiiiii",
     "nb_attention_prefill_tc_error": "",

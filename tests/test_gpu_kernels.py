@@ -80,7 +80,7 @@ def _gelu(y, act):
 
 
 LINEAR_SHAPES = [(1, 64, 64), (5, 1001, 96), (33, 130, 100), (130, 257, 72), (64, 768, 3072),
-                 (300, 2304, 768), (7, 50257, 64), (2048, 96, 320)]
+                 (300, 2304, 768), (7, 50257, 64), (2048, 96, 320), (260, 333, 70), (513, 1000, 100)]
 
 
 @pytest.mark.parametrize("M, N, K", LINEAR_SHAPES)
