@@ -1,5 +1,12 @@
 """The reference's sampler restated on the host in float64 (src/sampler.rs:163-217): the
-path taken when top-k or top-p filtering is on, and the yardstick of the device kernels."""
+path taken when top-k or top-p filtering is on, and the yardstick of the device kernels.
+
+Where it parts from the reference, all in degenerate rows: a row with a NaN gives the first
+index of the maximum as numpy sees it (the reference's ``fold(f64::max)`` ignores the NaN and
+returns token 0 once the total is not finite); with ``top_p <= 0`` the first of tied maxima is
+kept (Rust's ``max_by`` keeps the last); and the callers draw a number for every row and
+step, while the reference draws none when it falls back to the argmax of a row without a
+finite maximum, so after such a row the two random streams differ."""
 from __future__ import annotations
 
 import numpy as np
