@@ -149,7 +149,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   // Barriers and tensor memory are set up; what the kernel before this one wrote (the rows of
   // X, the residual) is touched from here on.  Under a programmatic launch the set-up above
-  // ran while that kernel was finishing.
+  // ran while that kernel was finishing -- and so do the loads of the first tile's weights
+  // (constants): a product of a decode step is a few microseconds long, and the trip to HBM
+  // for its first weights would be a good part of that.
+  int pre_kb = 0;   // K blocks whose weights are already on their way (the producer's)
+  if constexpr (!PAIR) {
+    if (tid == 0 && walker < num_tiles) {
+      pre_kb = num_kb < L::STAGES ? num_kb : L::STAGES;
+      const int n0 = (walker % tiles_n) * BN;
+      for (int kb = 0; kb < pre_kb; ++kb) {
+        mbar_expect_tx(full_bar(kb), (uint32_t)a_box_bytes + L::B_BYTES);
+        tma_load_2d(base + kb * L::STAGE_BYTES + L::A_BYTES, &map_w, kb * BK, n0, full_bar(kb));
+      }
+    }
+  }
   nb_grid_dependency_wait();
 
   // The CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the shared-memory
@@ -165,7 +178,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t phase = (it / L::STAGES) & 1u;
-          ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
+          if (!(tile == walker && kb < pre_kb)) ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
           if (!ok) break;
           const uint32_t a_dst = base + s * L::STAGE_BYTES;
           if constexpr (PAIR) {
@@ -174,6 +187,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const uint32_t lead_bar = cluster_addr(full_bar(s), 0);
             tma_load_2d_pair(a_dst, &map_x, kb * BK, m0, lead_bar);
             tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, kb * BK, n0, lead_bar);
+          } else if (tile == walker && kb < pre_kb) {
+            // the stage was armed and its weights asked for before the wait: the rows follow
+            tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
           } else {
             // the X box has fewer than 128 rows when the whole product has (see the launcher)
             mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + L::B_BYTES);
