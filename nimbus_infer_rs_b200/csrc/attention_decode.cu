@@ -17,6 +17,8 @@
 #include <mutex>
 
 #include "common.cuh"
+#include <atomic>
+
 #include "attention_common.cuh"
 
 namespace {
@@ -24,6 +26,7 @@ namespace {
 constexpr int THREADS = 128;
 constexpr int WARPS = 4;
 constexpr int PAGE_TOKENS = 64;
+constexpr int MAX_CLUSTER = 8;   // most splits that one thread-block cluster merges (portable size)
 
 // G: query heads per key/value head served by one CTA (group <= G).
 template <typename T, int HD, int G, typename TOut>
@@ -291,7 +294,7 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
 // MMA_STAGES: pages (keys and values) in flight per CTA: three when the CTAs of a launch fit
 // on the GPU with them (a short chain per CTA wants its pages early), two when more CTAs per
 // SM matter more (a large batch).
-template <int HD, typename TOut, int MMA_STAGES>
+template <int HD, typename TOut, int MMA_STAGES, bool CLUSTERED>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, int q_col,
                             const int* __restrict__ row_slot, const int* __restrict__ row_pos,
@@ -300,6 +303,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
                             float* __restrict__ part_ml, int* __restrict__ counters, int append,
                             int k_col, int v_col) {
   typedef __nv_bfloat16 bf16;
+  constexpr bool clustered = CLUSTERED;
   constexpr int ROW = HD + 8;          // padded row of a staged page (elements)
   constexpr int KS = HD / 16;          // k-steps of the score product = row tiles of the value product
   constexpr int GH = 8;                // query heads an MMA column block holds
@@ -316,6 +320,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   static_assert((size_t)(WARPS * GH * HD + WARPS * GH * 2) * sizeof(float) <=
                     (size_t)2 * MMA_STAGES * STILE * sizeof(bf16), "partial results must fit in the page tiles");
   __shared__ int s_last;
+  // clustered: the splits of a row and key-value head are one thread-block cluster (split =
+  // rank); they hand their partial results to split 0 through its shared memory, in a region
+  // of its own behind the page tiles, instead of through global memory and a counter
+  float* c_part = reinterpret_cast<float*>(smem_raw + (size_t)2 * MMA_STAGES * STILE * sizeof(bf16));
 
   // Before the wait: where the row's pages lie, and its first pages on their way.  The batch
   // layout, the block table and the pages were written at least two kernels ago (earlier
@@ -368,6 +376,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   }
 
   nb_grid_dependency_wait();
+  // Every CTA of a cluster says that it runs (a padding row's CTAs have all left above); the
+  // matching wait stands in front of the first store into another CTA's shared memory.  The
+  // arrive stands behind the wait on the predecessor on purpose: in front of it, steps that
+  // were replayed from a recorded graph came out wrong on a B200 (the same launches issued
+  // one by one did not).  Why is not known; the later place costs nothing.
+  if constexpr (clustered) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
 
   // Q^T as the B operand of the score product: column g of the block is query head g of the
   // group (zero beyond the group); this thread holds rows 2t, 2t+1 and 2t+8, 2t+9 of each k-step
@@ -522,6 +536,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
   }
   __syncthreads();
   // merge the warps -> partial result of this split (maxima in units of log2 e)
+  unsigned c_remote = 0;    // this split's place in split 0's shared memory
+  if constexpr (clustered) {
+    asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+    const unsigned local = (unsigned)__cvta_generic_to_shared(c_part + (size_t)split * group * (HD + 2));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(c_remote) : "r"(local), "r"(0));
+  }
   for (int i = tid; i < group * HD; i += THREADS) {
     const int gh = i / HD, c = i - gh * HD;
     float M = -INFINITY;
@@ -540,6 +560,15 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
       out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
       continue;
     }
+    if constexpr (clustered) {
+      const unsigned at = c_remote + (unsigned)(gh * (HD + 2)) * 4u;
+      asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (unsigned)c * 4u), "f"(a) : "memory");
+      if (c == 0) {
+        asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (unsigned)HD * 4u), "f"(M) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (unsigned)(HD + 1) * 4u), "f"(l) : "memory");
+      }
+      continue;
+    }
     const size_t pi = ((size_t)r * n_heads + head) * n_splits + split;
     part_acc[pi * HD + c] = a;
     if (c == 0) {
@@ -548,6 +577,30 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     }
   }
   if (n_splits == 1) return;
+  if constexpr (clustered) {
+    // the stores above are visible to split 0 once every CTA has arrived (release) and split 0
+    // has waited (acquire); the other splits wait too, so that none leaves the cluster early
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    if (split != 0) return;
+    for (int i = tid; i < group * HD; i += THREADS) {
+      const int gh = i / HD, c = i - gh * HD;
+      const float* row = c_part + (size_t)gh * (HD + 2);
+      const int step = group * (HD + 2);
+      float M = -INFINITY;
+      for (int s = 0; s < n_splits; ++s) M = fmaxf(M, row[s * step + HD]);
+      float a = 0.0f, l = 0.0f;
+      for (int s = 0; s < n_splits; ++s) {
+        const float ms = row[s * step + HD];
+        const float f = (ms == -INFINITY) ? 0.0f : nb_exp2(ms - M);
+        a += f * row[s * step + c];
+        l += f * row[s * step + HD + 1];
+      }
+      out[(size_t)r * out_stride + (size_t)(kvh * group + gh) * HD + c] =
+          nb_from_f32<TOut>(l > 0.0f ? a / l : a);
+    }
+    return;
+  }
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -579,16 +632,32 @@ template <int HD, typename TOut, int MMA_STAGES>
 int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
                  const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
                  int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
-                 int k_col, int v_col, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * MMA_STAGES * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
-  auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES>;
+                 int k_col, int v_col, bool clustered, cudaStream_t stream) {
+  const size_t tiles = (size_t)2 * MMA_STAGES * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
+  // room for the splits' partial results in split 0's shared memory (see the kernel)
+  const size_t most = tiles + (size_t)MAX_CLUSTER * 8 * (HD + 2) * sizeof(float);
+  dim3 grid(n_splits, kv.n_kv_heads, n_rows);
+  if (clustered) {
+    auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, true>;
+    static bool configured = false;   // per instantiation
+    if (most > 48 * 1024 && !configured) {
+      NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+      configured = true;
+    }
+    const size_t smem = tiles + (size_t)n_splits * group * (HD + 2) * sizeof(float);
+    NB_CUDA(nb_launch_clusters(kern, grid, dim3(THREADS), smem, stream, n_splits,
+                               (const __nv_bfloat16*)q, q_stride, q_col, row_slot, row_pos, kv, group,
+                               (TOut*)out, out_stride, scale, window, n_splits, part_acc, part_ml,
+                               counters, append, k_col, v_col));
+    return 0;
+  }
+  auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, false>;
   static bool configured = false;   // per instantiation
-  if (smem > 48 * 1024 && !configured) {
-    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (tiles > 48 * 1024 && !configured) {
+    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
     configured = true;
   }
-  dim3 grid(n_splits, kv.n_kv_heads, n_rows);
-  NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride, q_col,
+  NB_CUDA(nb_launch(kern, grid, dim3(THREADS), tiles, stream, (const __nv_bfloat16*)q, q_stride, q_col,
                     row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits,
                     part_acc, part_ml, counters, append, k_col, v_col));
   return 0;
@@ -598,7 +667,7 @@ template <int HD, typename TOut>
 int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
                const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
                int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
-               int k_col, int v_col, cudaStream_t stream) {
+               int k_col, int v_col, bool clustered, cudaStream_t stream) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -613,19 +682,19 @@ int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, cons
   if (ctas <= room3)
     return launch_mma_s<HD, TOut, 3>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
                                      scale, window, n_rows, n_splits, part_acc, part_ml, counters,
-                                     append, k_col, v_col, stream);
+                                     append, k_col, v_col, clustered, stream);
   return launch_mma_s<HD, TOut, 2>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
                                    scale, window, n_rows, n_splits, part_acc, part_ml, counters, append,
-                                   k_col, v_col, stream);
+                                   k_col, v_col, clustered, stream);
 }
 
 template <typename TOut>
 int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* row_slot,
                     const int* row_pos, const NbPagedKV& kv, int group, void* out, int out_stride,
                     float scale, int window, int n_rows, int n_splits, float* pa, float* pm,
-                    int* cn, int ap, int kc, int vc, cudaStream_t st) {
+                    int* cn, int ap, int kc, int vc, bool clustered, cudaStream_t st) {
 #define NB_HD(HD_) \
-  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, clustered, st)
   switch (hd) {
     NB_HD(16); NB_HD(32); NB_HD(48); NB_HD(64); NB_HD(80); NB_HD(96); NB_HD(112); NB_HD(128);
   }
@@ -705,14 +774,15 @@ NB_EXPORT void nb_attention_decode_scratch(int n_rows, int n_heads, int n_kv_hea
 // append != 0: row r of `q` also holds this step's key and value at columns k_col / v_col;
 // the kernel writes them to the cache at token row_pos[r] and attends to them as well, so no
 // separate append pass is needed.
-NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_col,
-                                  const int* row_slot, const int* row_pos, const void* k_cache,
-                                  const void* v_cache, const int* block_table, int max_pages,
-                                  int page, int n_heads, int n_kv_heads, int head_dim, void* out,
-                                  int out_dtype, int out_stride, float scale, int window,
-                                  int n_rows, int n_splits, float* part_acc, float* part_ml,
-                                  int* counters, int append, int k_col, int v_col,
-                                  cudaStream_t stream) {
+namespace {
+std::atomic<int> g_cluster_merge{1};
+
+int attention_decode(const void* q, int dtype, int q_stride, int q_col, const int* row_slot,
+                     const int* row_pos, const void* k_cache, const void* v_cache,
+                     const int* block_table, int max_pages, int page, int n_heads, int n_kv_heads,
+                     int head_dim, void* out, int out_dtype, int out_stride, float scale, int window,
+                     int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters,
+                     int append, int k_col, int v_col, int clusters_allowed, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(nb_attention_decode_supported(dtype, head_dim, n_heads, n_kv_heads, page),
              NB_ERR_UNSUPPORTED,
@@ -737,15 +807,56 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
     // bf16 cache: tensor cores (needs 16-byte aligned rows and 4-byte aligned query columns)
     NB_REQUIRE(q_stride % 8 == 0 && q_col % 2 == 0 && (uintptr_t)q % 16 == 0, NB_ERR_UNSUPPORTED,
                "attention_decode: query rows must be 16-byte aligned");
+    // up to MAX_CLUSTER splits merge through the shared memory of a thread-block cluster, more
+    // through the scratch arrays and a counter
+    bool clustered = clusters_allowed > 0 && n_splits >= 2 && n_splits <= MAX_CLUSTER;
+    if (clustered && clusters_allowed == 1) {
+      // launching in clusters has a price of its own; measured on a B200 it is repaid while
+      // the launch is small (up to about two CTAs per SM), where the merge is a large part
+      static int sms = 0;
+      if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+          sms = 148;
+      }
+      clustered = (long long)n_splits * n_kv_heads * n_rows <= 2LL * sms;
+    }
     rc = out_dtype == NB_F32
-             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream)
-             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream);
+             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
+             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
   }
 #undef NB_ARGS
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_decode");
   return 0;
 }
+}  // namespace
+
+NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_col,
+                                  const int* row_slot, const int* row_pos, const void* k_cache,
+                                  const void* v_cache, const int* block_table, int max_pages,
+                                  int page, int n_heads, int n_kv_heads, int head_dim, void* out,
+                                  int out_dtype, int out_stride, float scale, int window,
+                                  int n_rows, int n_splits, float* part_acc, float* part_ml,
+                                  int* counters, int append, int k_col, int v_col,
+                                  cudaStream_t stream) {
+  return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache, block_table,
+                          max_pages, page, n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
+                          scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col,
+                          v_col, g_cluster_merge.load(), stream);
+}
+
+// How the splits of the bfloat16 kernel merge: 0 always through the scratch arrays; 1 (the
+// default) through a cluster's shared memory where there are at most 8 of them and the launch
+// has at most two CTAs per SM; 2 through a cluster wherever there are 2 to 8.  Returns the
+// earlier setting.
+NB_EXPORT int nb_attention_decode_cluster_merge(int mode) {
+  return g_cluster_merge.exchange(mode < 0 ? 0 : mode > 2 ? 2 : mode);
+}
+
+// Most splits that merge inside a cluster.
+NB_EXPORT int nb_attention_decode_cluster_limit() { return MAX_CLUSTER; }
 
 // ---------------------------------------------------------------------------------------
 // The same kernel for callers that cannot allocate device memory (see no_alloc.h).
@@ -819,10 +930,12 @@ NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride,
   // the array keeps what the last call left; the counters are the only part that must start
   // at zero (a launch that ran to its end leaves them so, an interrupted one may not)
   NB_CUDA(cudaMemsetAsync(base, 0, (size_t)cnt_b, stream));
-  return nb_attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache,
-                             block_table, max_pages, page, n_heads, n_kv_heads, head_dim, out,
-                             out_dtype, out_stride, scale, window, n_rows, n_splits,
-                             reinterpret_cast<float*>(base + cnt_b + ml_b),
-                             reinterpret_cast<float*>(base + cnt_b),
-                             reinterpret_cast<int*>(base), /*append=*/0, 0, 0, stream);
+  // always through the scratch arrays: this entry point exists for them
+  return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache,
+                          block_table, max_pages, page, n_heads, n_kv_heads, head_dim, out,
+                          out_dtype, out_stride, scale, window, n_rows, n_splits,
+                          reinterpret_cast<float*>(base + cnt_b + ml_b),
+                          reinterpret_cast<float*>(base + cnt_b),
+                          reinterpret_cast<int*>(base), /*append=*/0, 0, 0,
+                          /*clusters_allowed=*/0, stream);
 }

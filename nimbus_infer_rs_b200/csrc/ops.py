@@ -19,7 +19,7 @@ ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
-DECODE_TARGET_CTAS = 4 * 148   # CTAs the split decode attention aims to put on the GPU
+DECODE_TARGET_CTAS = 4 * 148   # CTAs the split 32-bit decode attention aims to put on the GPU
 # CTAs the tensor-core prefill attention aims to put on the GPU by cutting the keys of a tile
 # into runs: one per SM.  (Two of its CTAs on an SM are bound by instruction issue, so cutting
 # further only adds the merge; measured on GPT-2 124M, 2 x 1024 tokens.)
@@ -83,6 +83,12 @@ class CudaBackend:
         # NIMBUS_B200_STREAM=0 keeps a decode step's products on the kernel that streams weights
         # through registers (comparison runs)
         self.use_stream = os.environ.get("NIMBUS_B200_STREAM", "1") != "0"
+        # NIMBUS_B200_DECODE_CLUSTERS=0/1/2: the splits of the bfloat16 decode attention merge
+        # through scratch memory and a counter / inside a thread-block cluster's shared memory
+        # where the launch is small / inside a cluster wherever there are 2 to 8 of them
+        self._cluster_limit = int(self.lib.nb_attention_decode_cluster_limit())
+        self._sms = torch.cuda.get_device_properties(self._device_index).multi_processor_count
+        self.set_decode_clusters(int(os.environ.get("NIMBUS_B200_DECODE_CLUSTERS", "1") or 1))
         # NIMBUS_B200_OVERLAP=0/1: let a kernel's set-up and first weight fetch overlap the tail
         # of the kernel before it (programmatic dependent launch; on by default)
         self.set_overlap(os.environ.get("NIMBUS_B200_OVERLAP", "1") != "0")
@@ -95,6 +101,13 @@ class CudaBackend:
         1/True where the cost model prefers them, 2 wherever a paired kernel exists."""
         self.pairs = int(mode)
         self.lib.nb_gemm_tcgen05_use_pairs(self.pairs)
+
+    def set_decode_clusters(self, mode) -> None:
+        """How the splits of the bfloat16 decode attention merge: 0/False through scratch
+        memory, 1/True inside thread-block clusters where the launch is small, 2 inside
+        clusters wherever there are 2 to 8 splits."""
+        self.decode_clusters = int(mode)
+        self.lib.nb_attention_decode_cluster_merge(self.decode_clusters)
 
     def set_overlap(self, on: bool) -> None:
         self.lib.nb_set_overlap((1 if on else 0))
@@ -249,6 +262,30 @@ class CudaBackend:
         return int(status.item())
 
     # -- cache and attention ----------------------------------------------------------
+    def _decode_splits(self, base_ctas: int, pages: int, kv, dtype) -> int:
+        """Into how many splits a decode launch cuts each sequence's pages; `base_ctas` is
+        rows x key-value heads.  The tensor-core kernel: as many as keep every CTA of the
+        launch on the GPU at once with three pages in flight each (measured on a B200 at
+        contexts of 256 and 1,024 and batches of 1 to 32: a CTA that has to wait for a place
+        costs more than a longer walk), and none that would get no page.  A small launch (at
+        most two CTAs per SM) merges its splits inside thread-block clusters and has at most
+        as many as a cluster holds; the library applies the same rule."""
+        if dtype != torch.bfloat16:
+            return max(1, min(pages, DECODE_TARGET_CTAS // base_ctas))
+        three_pages = 6 * kv.page * (kv.head_dim + 8) * 2
+        room = max(1, (220 * 1024) // three_pages) * self._sms
+
+        def cut(most):
+            most = max(1, min(pages, most, room // base_ctas))
+            per_split = -(-pages // most)
+            return -(-pages // per_split)
+
+        if self.decode_clusters:
+            n = cut(self._cluster_limit)
+            if self.decode_clusters == 2 or n * base_ctas <= 2 * self._sms:
+                return n
+        return cut(16)
+
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
         """Scratch of the split decode attention: partial sums per (row, head, split) and one
         counter per (row, key/value head).  Kept and grown as needed; the counters start at
@@ -304,7 +341,7 @@ class CudaBackend:
                 (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
                 (kv.n_kv_heads), (kv.page)):
             pages = max(1, -(-layout.max_kv_len // kv.page))
-            n_splits = max(1, min(pages, DECODE_TARGET_CTAS // (n_rows * kv.n_kv_heads)))
+            n_splits = self._decode_splits(n_rows * kv.n_kv_heads, pages, kv, q_src.dtype)
             acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
                                                      kv.head_dim, n_splits)
             self._call("nb_attention_decode", _ptr(q_src), (dtype_code(q_src.dtype)),

@@ -12,6 +12,8 @@ SIGNATURES = {
     "nb_attention_decode_scratch": "iiiiippp",
     "nb_attention_decode": "piiipppppiiiiipiifiiipppiiip",
     "nb_attention_decode_static": "piiipppppiiiiipiifiiip",
+    "nb_attention_decode_cluster_merge": "i",
+    "nb_attention_decode_cluster_limit": "",
     "nb_attention_generic": "piiipppppiiiiipiifiip",
     "nb_attention_prefill_supported": "iiiiiii",
     "nb_attention_prefill_f32_supported": "iiii",

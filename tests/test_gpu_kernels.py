@@ -592,11 +592,25 @@ def test_linear_with_norm_of_the_rows_first(ops, M, N, K, wdt):
                                                (8, 1, 128, 0), (6, 2, 64, 100), (3, 3, 48, 0),
                                                (25, 25, 64, 0), (16, 1, 64, 0)])
 @pytest.mark.parametrize("max_kv", [64, 1024, 4096])
-def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
+@pytest.mark.parametrize("clusters", [True, False])
+def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv, clusters):
     """One query row per sequence (a decode step): sequences of very unequal lengths, pages
     shuffled, a padding row in the middle; run twice on the same scratch (the counters must be
     left at zero).  `max_kv` (the longest context the launch is sized for) changes the number
-    of splits a sequence's pages are spread over."""
+    of splits a sequence's pages are spread over.  The splits of the bfloat16 kernel merge in
+    the shared memory of a thread-block cluster (at most 8 of them) or, with `clusters` off,
+    through scratch memory and a counter like the 32-bit kernel's."""
+    if dtype == torch.float32 and not clusters:
+        pytest.skip("the 32-bit kernel has one way to merge")
+    was = ops.decode_clusters
+    ops.set_decode_clusters(2 if clusters else 0)
+    try:
+        _decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv)
+    finally:
+        ops.set_decode_clusters(was)
+
+
+def _decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv):
     lens = [1, 64, 65, 700, 333, 1000, 129]
     kv, dk, dv = _paged_cache(len(lens), lens, Hk, hd, dtype, seed=H + hd)
     entries = [(s + 1, [0], []) for s in range(len(lens))]
