@@ -60,7 +60,7 @@ void nb_set_error(const char* fmt, ...);
 // device memory) and returns nullptr if that fails; kernels given nullptr still give up their
 // waits and return, they only cannot say so.
 // ---------------------------------------------------------------------------------
-enum NbErrorWord : int { NB_ERRW_GEMM_TCGEN05 = 0, NB_ERRW_ATTENTION_PREFILL_TC = 1, NB_ERRW_PROBE = 2, NB_ERRW_GEMM_STREAM = 3, NB_ERRW_COUNT = 16 };
+enum NbErrorWord : int { NB_ERRW_GEMM_TCGEN05 = 0, NB_ERRW_ATTENTION_PREFILL_TC = 1, NB_ERRW_PROBE = 2, NB_ERRW_GEMM_STREAM = 3, NB_ERRW_GEMM_TC_ROWS = 4, NB_ERRW_COUNT = 16 };
 int* nb_error_words();
 
 __device__ __forceinline__ void nb_report_timeout(int* err_word) {

@@ -28,6 +28,7 @@ FUSED_NORM_MAX_ROWS = 16       # a LayerNorm is folded into the product up to th
 FUSED_NORM_MAX_COLS = 16384    # ... and output columns (a long weight stream wants the leaner kernel)
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 STREAM_MAX_ROWS = 16   # ... and with at most this many the kernel that stages weights in shared memory
+ROWS_MAX_ROWS = 128    # up to this many rows a product's weights are the tensor cores' 128-row operand
 
 
 class KernelError(RuntimeError):
@@ -83,6 +84,10 @@ class CudaBackend:
         # NIMBUS_B200_STREAM=0 keeps a decode step's products on the kernel that streams weights
         # through registers (comparison runs)
         self.use_stream = os.environ.get("NIMBUS_B200_STREAM", "1") != "0"
+        # NIMBUS_B200_ROWS=0/1/2: products of up to 128 rows on the kernel that cuts K among the
+        # CTAs of a cluster: never / where it is the faster one (a long K over few columns) /
+        # wherever it applies
+        self.use_rows = int(os.environ.get("NIMBUS_B200_ROWS", "1") or 1)
         # NIMBUS_B200_DECODE_CLUSTERS=0/1/2: the splits of the bfloat16 decode attention merge
         # through scratch memory and a counter / inside a thread-block cluster's shared memory
         # where the launch is small / inside a cluster wherever there are 2 to 8 of them
@@ -213,6 +218,16 @@ class CudaBackend:
             h = torch.empty((M, K), device=x.device, dtype=norm[3])
             self.layernorm(x, norm[0], norm[1], norm[2], h)
             x = h
+        # up to 128 rows with a long K over few columns (the MLP's second product of a decode
+        # step of a larger batch or of a short prompt): weights as the 128-row operand, K cut
+        # among the CTAs of a cluster
+        if self.use_tcgen05 and self.use_rows and M <= ROWS_MAX_ROWS and x.dtype == torch.bfloat16 \
+                and w.dtype == torch.bfloat16 and (
+                    self.lib.nb_gemm_tc_rows_preferred(M, N, K) if self.use_rows == 1
+                    else self.lib.nb_gemm_tc_rows_supported(M, N, K)):
+            self._call("nb_gemm_tc_rows", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                       dtype_code(out.dtype), M, N, K, act, self._stream())
+            return
         if self.use_tcgen05 and self.lib.nb_gemm_tcgen05_supported(
                 (dtype_code(x.dtype)), (dtype_code(w.dtype)), (M), (N), (K)):
             self._call("nb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
@@ -226,7 +241,8 @@ class CudaBackend:
 
     # A kernel whose bounded wait on a barrier ran out says so in a word of pinned host memory
     # (one per kernel family); its results are not valid.
-    _ERROR_WORDS = {0: "gemm_tcgen05", 1: "attention_prefill_tc", 2: "wait_probe", 3: "gemm_stream"}
+    _ERROR_WORDS = {0: "gemm_tcgen05", 1: "attention_prefill_tc", 2: "wait_probe", 3: "gemm_stream",
+                    4: "gemm_tc_rows"}
 
     def raise_device_errors(self) -> None:
         """Raise if a kernel that has finished reported a timed-out wait.  Reads host memory
@@ -248,7 +264,7 @@ class CudaBackend:
         kernel gives up and reports it (``None``: the default, about two seconds)."""
         cycles = 4_000_000_000 if cycles is None else int(cycles)
         for fn in ("nb_gemm_tcgen05_set_wait_budget", "nb_attention_prefill_tc_set_wait_budget",
-                   "nb_gemm_stream_set_wait_budget"):
+                   "nb_gemm_stream_set_wait_budget", "nb_gemm_tc_rows_set_wait_budget"):
             rc = getattr(self.lib, fn)(cycles)
             if rc != 0:
                 raise KernelError(f"{fn} failed ({rc}): "

@@ -32,6 +32,12 @@ SIGNATURES = {
     "nb_gemm_stream_tune": "i",
     "nb_gemm_stream_set_wait_budget": "l",
     "nb_gemm_skinny_norm_supported": "iii",
+    "nb_gemm_tc_rows_supported": "iii",
+    "nb_gemm_tc_rows_preferred": "iii",
+    "nb_gemm_tc_rows_plan": "iiip",
+    "nb_gemm_tc_rows_force_split": "i",
+    "nb_gemm_tc_rows_set_wait_budget": "l",
+    "nb_gemm_tc_rows": "pppppiiiiip",
     "nb_gemm_tcgen05_supported": "iiiii",
     "nb_gemm_tcgen05_error": "",
     "nb_gemm_tcgen05_set_wait_budget": "l",

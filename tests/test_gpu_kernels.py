@@ -1,5 +1,6 @@
 """Each kernel alone against a plain torch fp32 restatement of the same operation, at sizes
 other than the engine's tiny models (odd widths, tails, several pages, grouped heads)."""
+import ctypes
 import math
 
 import numpy as np
@@ -111,6 +112,56 @@ def test_linear_against_float64(ops, M, N, K, xdt, wdt):
     stream = res.clone()
     ops.linear(x, w, bias, stream, 0, stream)
     assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
+
+
+ROWS_SHAPES = [(64, 2304, 768), (64, 768, 3072), (17, 130, 72), (33, 1000, 100 * 8), (48, 768, 768),
+               (100, 1600, 1600), (128, 4800, 1600), (80, 257 * 8, 6400), (20, 333, 64), (128, 128, 8)]
+
+
+@pytest.mark.parametrize("M, N, K", ROWS_SHAPES)
+@pytest.mark.parametrize("split", [0, 1, 2, 3, 5, 8])
+def test_products_of_17_to_128_rows(ops, M, N, K, split):
+    """The tensor-core kernel whose 128-row operand is the weights: K cut among the CTAs of a
+    cluster (the size it chooses, and sizes forced here: one CTA, a size that does not divide
+    the rows or the K blocks evenly, the largest), the sums dealt back through distributed
+    shared memory.  Rows that are no multiple of 16, columns that are no multiple of 128, a K
+    of one block and of a hundred; bias, GELU, the residual added in place, bf16 and fp32
+    results; all against float64, and twice, so that what one launch leaves in shared or tensor
+    memory cannot help the next."""
+    assert ops.use_rows and ops.lib.nb_gemm_tc_rows_supported(M, N, K)
+    assert ops.lib.nb_gemm_tc_rows_preferred(64, 768, 3072) and not ops.lib.nb_gemm_tc_rows_preferred(64, 2304, 768)
+    plan = (ctypes.c_int * 6)()
+    was, was_rows = ops.lib.nb_gemm_tc_rows_force_split(split), ops.use_rows
+    ops.use_rows = 2                      # wherever it applies, not only where it is the faster one
+    try:
+        if not ops.lib.nb_gemm_tc_rows_plan(M, N, K, plan):
+            pytest.skip("this cluster size leaves a CTA without a block of K, or the launch does not fit")
+        assert split == 0 or plan[1] == split
+        torch.manual_seed(M + N + K)
+        x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+        bias = torch.randn(N, device=DEV)
+        ref0 = x.double() @ w.double().t()
+        tol = 3e-6 * float(ref0.abs().max()) * math.sqrt(max(K, 64) / 64)
+        for attempt in range(2):
+            before = ops.launches
+            out = torch.full((M, N), 9.0, device=DEV)
+            ops.linear(x, w, None, out)
+            assert ops.launches == before + 1
+            assert (out.double() - ref0).abs().max() <= tol
+            ref = _gelu(ref0 + bias.double(), 1)
+            o = torch.full((M, N), 9.0, device=DEV, dtype=torch.bfloat16)
+            ops.linear(x, w, bias, o, 1)
+            assert (o.double() - ref).abs().max() <= tol + 8e-3 * float(ref.abs().max())
+            res = torch.randn(M, N, device=DEV)
+            stream = res.clone()
+            ops.linear(x, w, bias, stream, 0, stream)
+            ref = ref0 + bias.double() + res.double()
+            assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
+        ops.check_device_errors()
+    finally:
+        ops.lib.nb_gemm_tc_rows_force_split(was)
+        ops.use_rows = was_rows
 
 
 def _paged_cache(n_seqs, lens, Hk, hd, dtype, seed, extra_pages=3, page=PAGE, stale_nan=False):
