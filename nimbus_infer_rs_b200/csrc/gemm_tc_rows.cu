@@ -213,6 +213,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const int n_local = quarter * 32 + lane;      // weight row of the tile = column of the output
   const int n = n0 + n_local;
   const int m_end = min(M, sh.nb);
+  // the bias of this thread's column (a constant), fetched while the products run
+  const float b = (warp >= 2 && bias && n < N) ? __ldg(bias + n) : 0.0f;
   bool ready = true;
   if (warp >= 2)
     ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full, 0u, abort_flag), 0) != 0;
@@ -223,7 +225,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp >= 2 && ready) {
     tc05_fence_after();
-    const float b = (bias && n < N) ? __ldg(bias + n) : 0.0f;
     // columns of the accumulator = rows of X, in fours; four that belong to CTA d go to
     // [this rank][n_local][their place in d's rows] of d's buffer, the own ones stay here
     const uint32_t slot = recv + (uint32_t)(((int)rank * BW + n_local) * sh.cpad) * 4u;
@@ -275,7 +276,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncwarp();
   asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
   if (warp >= 2 && ready) {
-    const float b = (bias && n < N) ? __ldg(bias + n) : 0.0f;
     if (sh.split > 1) {
       // the residual of this CTA's first rows is fetched while the others' sums are on their way
       constexpr int PRE = 4;

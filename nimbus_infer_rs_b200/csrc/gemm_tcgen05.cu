@@ -270,6 +270,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
       }
       __syncwarp();
+      // the bias of this warp's columns (a constant) is fetched while the products still run:
+      // behind the accumulator it would be a trip to memory at the very end of the kernel
+      float bias_pre[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        if (bias && c < nch && col0 + c * 32 + lane < N) bias_pre[c] = __ldg(bias + col0 + c * 32 + lane);
       const bool ready =
           __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
       if (!ready) break;
@@ -293,8 +299,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
         const int nb = col0 + c * 32;
-        float bias_l = 0.0f;
-        if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
+        const float bias_l = c == 0 ? bias_pre[0] : bias_pre[1];
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -369,6 +374,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       const int m = m0 + quarter * 32 + lane;
       const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
+      // the bias of this warp's columns, fetched while the products still run
+      float bias_pre[CHUNKS];
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int nbc = n0 + (half * CHUNKS + c) * 32;
+        bias_pre[c] = (bias && nbc + lane < N) ? __ldg(bias + nbc + lane) : 0.0f;
+      }
       // lane 0 decides for the warp: the tensor-memory loads below need all 32 lanes
       const bool ready =
           __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
@@ -387,9 +399,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
         }
         const int nb = n0 + c * 32;
-        // bias of the chunk's 32 columns: one load per lane, passed on by shuffles
-        float bias_l = 0.0f;
-        if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
+        // bias of the chunk's 32 columns: one value per lane, passed on by shuffles
+        float bias_l = bias_pre[0];
+#pragma unroll
+        for (int q = 1; q < CHUNKS; ++q)
+          if (c - half * CHUNKS == q) bias_l = bias_pre[q];
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
