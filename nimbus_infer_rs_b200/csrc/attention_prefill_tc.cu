@@ -167,6 +167,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int* table = block_table + (size_t)slot * max_pages;
 
   if (tid == 0) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    if (append) prefetch_tensormap(&map_new);
     mbar_init(q_full, 1);
     for (int i = 0; i < L::STAGES; ++i) {
       mbar_init(kv_full(i), 1);

@@ -122,6 +122,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const int n_kb = max(0, kb_hi - kb_lo);
 
   if (tid == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
     for (int s = 0; s < sh.stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);

@@ -108,6 +108,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   constexpr int TILE_M = PAIR ? 2 * BM : BM;
 
   if (tid == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+    if constexpr (EPI == 1) prefetch_tensormap(&map_out);
     for (int s = 0; s < L::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);

@@ -61,6 +61,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first use:
+// the first copy through a map otherwise waits for that fetch.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar) {
   asm volatile(
