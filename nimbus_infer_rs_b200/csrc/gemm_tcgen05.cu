@@ -500,229 +500,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
-// ------------------------------------------------------------------------------ one row tile, K cut
-// A product of at most 128 rows is a walk over K: with 64-column tiles each K block costs the
-// MMA thread about 500 clocks whatever its size, and few columns mean few CTAs.  Here a cluster
-// of SPLIT CTAs takes one 128 x 64 tile: CTA r walks over the r-th run of K blocks into its own
-// accumulator, the CTAs other than the first write their sums into the first CTA's shared
-// memory (distributed shared memory), and after a cluster barrier the first adds them up in
-// rank order and finishes the tile (bias, activation, residual, store).
-template <typename TOut>
-__device__ __forceinline__ void finish_chunk_direct(float (&f)[32], int m, int nb, int M, int N,
-                                                    const float* __restrict__ bias,
-                                                    const float* residual, TOut* out, int act,
-                                                    int lane) {
-  float bias_l = 0.0f;
-  if (bias && nb + lane < N) bias_l = __ldg(bias + nb + lane);
-#pragma unroll
-  for (int j = 0; j < 32; ++j)
-    f[j] = nb_apply_act_fast(f[j] + __shfl_sync(0xffffffffu, bias_l, j), act);
-  if (m >= M || nb >= N) return;
-  const size_t row = (size_t)m * N;
-  const float* r = residual ? residual + row + nb : nullptr;
-  float rs[32];   // `residual` may be `out` itself: all of it before the first store
-#pragma unroll
-  for (int j = 0; j < 32; ++j) rs[j] = (r && nb + j < N) ? r[j] : 0.0f;
-  if constexpr (sizeof(TOut) == 4) {
-    float* o = reinterpret_cast<float*>(out) + row + nb;
-    if (nb + 32 <= N && N % 4 == 0) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<float4*>(o + 4 * j) =
-            make_float4(f[4 * j] + rs[4 * j], f[4 * j + 1] + rs[4 * j + 1], f[4 * j + 2] + rs[4 * j + 2],
-                        f[4 * j + 3] + rs[4 * j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (nb + j < N) o[j] = f[j] + rs[j];
-    }
-  } else {
-    bf16* o = reinterpret_cast<bf16*>(out) + row + nb;
-    if (nb + 32 <= N && N % 8 == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint4 pk;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          h[e] = __floats2bfloat162_rn(f[j + 2 * e] + rs[j + 2 * e], f[j + 2 * e + 1] + rs[j + 2 * e + 1]);
-        *reinterpret_cast<uint4*>(o + j) = pk;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (nb + j < N) o[j] = __float2bfloat16_rn(f[j] + rs[j]);
-    }
-  }
-}
-
-constexpr int SK_BN = 64;
-constexpr int SK_STAGES = 4;
-constexpr int SK_STAGE_BYTES = BM * BK * 2 + SK_BN * BK * 2;     // 24 KB
-constexpr int SK_THREADS = 64 + 8 * 32;
-template <int SPLIT>
-struct SplitSmem {
-  static constexpr int TILES_BYTES = SK_STAGES * SK_STAGE_BYTES;
-  static constexpr int RB_BYTES = (SPLIT - 1) * BM * SK_BN * 4;   // the other CTAs' sums, in the first CTA
-  static constexpr int N_BARRIERS = 2 * SK_STAGES + 1;
-  static constexpr int TOTAL = TILES_BYTES + RB_BYTES + N_BARRIERS * 8 + 16 + 1024;
-};
-
-template <int SPLIT, typename TOut>
-__global__ void __launch_bounds__(SK_THREADS)
-gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                           const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
-                           int K, int act, int kb_per, int a_box_bytes, int* err_word) {
-  using L = SplitSmem<SPLIT>;
-  extern __shared__ unsigned char smem_dyn[];
-  const uint32_t raw = smem_u32(smem_dyn);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  unsigned char* gen = smem_dyn + (base - raw);
-  const uint32_t rb_base = base + L::TILES_BYTES;
-  const uint32_t bars = rb_base + L::RB_BYTES;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (SK_STAGES + s); };
-  const uint32_t acc_full = bars + 8u * (2 * SK_STAGES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + L::TILES_BYTES + L::RB_BYTES + L::N_BARRIERS * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint32_t rank;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
-  const int n0 = (int)(blockIdx.x / SPLIT) * SK_BN;
-  const int num_kb = (K + BK - 1) / BK;
-  const int kb_lo = (int)rank * kb_per, kb_hi = min(num_kb, kb_lo + kb_per);
-  const int n_kb = max(0, kb_hi - kb_lo);
-
-  if (tid == 0) {
-    for (int s = 0; s < SK_STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    mbar_init(acc_full, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"((uint32_t)SK_BN)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  tc05_fence_before();
-  __syncthreads();
-  tc05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  // every CTA of the cluster runs before any of them writes into another's shared memory
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-
-  if (warp == 0) {
-    if (lane == 0) {   // TMA producer
-      for (int i = 0; i < n_kb; ++i) {
-        const int s = i % SK_STAGES;
-        if (!mbar_wait(empty_bar(s), ((i / SK_STAGES) & 1u) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + SK_BN * BK * 2);
-        const uint32_t a_dst = base + s * SK_STAGE_BYTES;
-        tma_load_2d(a_dst, &map_x, (kb_lo + i) * BK, 0, full_bar(s));
-        tma_load_2d(a_dst + BM * BK * 2, &map_w, (kb_lo + i) * BK, n0, full_bar(s));
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {   // MMA issuer
-      constexpr uint32_t idesc = instr_desc_bf16(BM, SK_BN);
-      bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % SK_STAGES;
-        ok = mbar_wait(full_bar(s), (i / SK_STAGES) & 1u, abort_flag);
-        if (!ok) break;
-        tc05_fence_after();
-        const uint32_t a_addr = base + s * SK_STAGE_BYTES;
-        const uint64_t da = smem_desc_sw128(a_addr);
-        const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          tc05_mma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                        (i > 0 || k > 0) ? 1u : 0u);
-        tc05_commit(empty_bar(s));
-      }
-      if (ok) {
-        if (n_kb > 0) tc05_commit(acc_full);
-        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_full) : "memory");
-      }
-    }
-  }
-  // epilogue warps: quarter = rows, half = which 32 of the 64 columns
-  const int quarter = warp & 3, half = (warp - 2) >> 2;
-  const int m = quarter * 32 + lane;
-  float f[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) f[j] = 0.0f;
-  bool ready = true;
-  if (warp >= 2) {
-    ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full, 0u, abort_flag), 0) != 0;
-    if (ready && n_kb > 0) {
-      tc05_fence_after();
-      uint32_t v[32];
-      tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 32), v);
-      tc05_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-    }
-    if (rank > 0 && m < M) {   // into the first CTA's buffer: [rank - 1][row][64 columns]
-      const uint32_t local = rb_base + (uint32_t)((((rank - 1) * BM + m) * SK_BN + half * 32) * 4);
-      const uint32_t remote = cluster_addr(local, 0);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(remote + 16u * j), "f"(f[4 * j]),
-                     "f"(f[4 * j + 1]), "f"(f[4 * j + 2]), "f"(f[4 * j + 3])
-                     : "memory");
-    }
-  }
-  // the sums of the other CTAs have arrived in the first one (the lanes of the producer's and
-  // the issuer's warps come together again first: the barrier wants whole warps)
-  __syncwarp();
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-  if (warp >= 2 && rank == 0 && ready) {
-    if (m < M) {
-#pragma unroll 1
-      for (int s = 0; s < SPLIT - 1; ++s) {   // in rank order: the result does not depend on timing
-        const uint32_t src = rb_base + (uint32_t)(((s * BM + m) * SK_BN + half * 32) * 4);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float4 x;
-          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
-                       : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                       : "r"(src + 16u * j));
-          f[4 * j] += x.x; f[4 * j + 1] += x.y; f[4 * j + 2] += x.z; f[4 * j + 3] += x.w;
-        }
-      }
-    }
-    finish_chunk_direct<TOut>(f, m, n0 + half * 32, M, N, bias, residual, out, act, lane);
-  }
-
-  tc05_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    if (tid == 0) {
-      nb_report_timeout(err_word);
-      const long long t0 = clock64();
-      while (clock64() - t0 < 4000000LL) {
-      }
-    }
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base),
-                 "r"((uint32_t)SK_BN)
-                 : "memory");
-  }
-}
-
 // The word of pinned host memory in which these kernels report a wait that ran out.
 int* error_word() {
   int* w = nb_error_words();
@@ -745,44 +522,6 @@ __global__ void wait_probe_kernel(int* err_word, int* status) {
     *status = ok ? 1 : 2;
   }
 }
-
-template <int SPLIT, typename TOut>
-int launch_splitk(const void* X, const void* W, const float* bias, const float* residual, void* out,
-                  int M, int N, int K, int act, cudaStream_t stream) {
-  using L = SplitSmem<SPLIT>;
-  CUtensorMap mx, mw;
-  const int a_rows = M >= BM ? BM : ((M + 15) / 16) * 16;
-  int rc = make_map(&mx, X, M, K, a_rows, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
-  if (rc) return rc;
-  rc = make_map(&mw, W, N, K, SK_BN, BK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
-  if (rc) return rc;
-  auto kern = gemm_tcgen05_splitk_kernel<SPLIT, TOut>;
-  static bool configured = false;
-  if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    configured = true;
-  }
-  const int num_kb = (K + BK - 1) / BK;
-  const int kb_per = (num_kb + SPLIT - 1) / SPLIT;
-  const int tiles_n = (N + SK_BN - 1) / SK_BN;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles_n * SPLIT);
-  cfg.blockDim = dim3(SK_THREADS);
-  cfg.dynamicSmemBytes = L::TOTAL;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = SPLIT;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, bias, residual, (TOut*)out, M, N, K, act, kb_per,
-                             a_rows * BK * 2, error_word()));
-  return 0;
-}
-
-int g_use_splitk = 1;
 
 // ---------------------------------------------------------------------------------- host
 template <int BN, int EPI, typename TOut, int PAIR = 0>
@@ -933,14 +672,8 @@ NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, 
          (M + BM - 1) / BM <= 65535;
 }
 
-// 1 (the default): pairs of CTAs (`cta_group::2`, 256-row tiles) where the cost model prefers
-// them; 2: for every product of more than 128 rows that has a paired kernel; 0: single CTAs.
-// 1 (the default): products of at most 128 rows with few columns cut K among a cluster of CTAs.
-NB_EXPORT int nb_gemm_tcgen05_use_splitk(int on) {
-  g_use_splitk = on != 0;
-  return 0;
-}
-
+// Pairs of CTAs on 256-row tiles: 0 never, 1 where the cost model prefers them, 2 wherever a
+// paired kernel exists.
 NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
   g_use_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return 0;
@@ -991,26 +724,6 @@ NB_EXPORT int nb_gemm_tcgen05(const void* X, const void* W, const float* bias, c
   const bool tma_epi = ((long long)N * esize) % 16 == 0 && (residual == nullptr || residual == out);
   const int bn = pick_tile_width(M, N, out_dtype == NB_F32, tma_epi);
   int rc;
-  // One row tile, few columns: a cluster of CTAs cuts K among them (see the split kernel).
-  {
-    const int num_kb = (K + BK - 1) / BK, tiles_n = (N + 63) / 64;
-    // measured: it pays from about 24 K blocks on (K >= 1536) and up to about 96 rows
-    if (g_use_splitk && M <= 96 && num_kb >= 24 && tiles_n <= 74) {
-      const bool four = true;
-      if (out_dtype == NB_F32)
-        rc = four ? launch_splitk<4, float>(X, W, bias, residual, out, M, N, K, act, stream)
-                  : launch_splitk<2, float>(X, W, bias, residual, out, M, N, K, act, stream);
-      else if (out_dtype == NB_BF16)
-        rc = four ? launch_splitk<4, bf16>(X, W, bias, residual, out, M, N, K, act, stream)
-                  : launch_splitk<2, bf16>(X, W, bias, residual, out, M, N, K, act, stream);
-      else
-        rc = NB_ERR_BAD_ARG;
-      NB_REQUIRE(rc != NB_ERR_BAD_ARG, NB_ERR_BAD_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
-      if (rc) return rc;
-      NB_CHECK_LAUNCH("gemm_tcgen05");
-      return 0;
-    }
-  }
   // Pairs of CTAs on 256-row tiles bring less into each SM per flop (half of the weight tile
   // each); they are taken when that outweighs the coarser tiles (see pick_pair_width).
   const int pair_bn = (tma_epi && g_use_pairs) ? pick_pair_width(M, N, out_dtype == NB_F32, bn) : 0;
