@@ -298,19 +298,19 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
               if (off0 + 4 * g4 < my_rows) load_residual4(res[g4], residual, m_lo + off0 + 4 * g4, m_end, n, N);
           }
 #pragma unroll
-        for (int g4 = 0; g4 < PRE; ++g4) {
-          const int off = off0 + 4 * g4;
-          if (off >= my_rows || m_lo + off >= m_end) break;
-          float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-          for (int s = 0; s < sh.split; ++s) {   // in rank order
-            float4 x;
-            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
-                         : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                         : "r"(recv + (uint32_t)((s * BW + n_local) * sh.cpad + off) * 4u));
-            a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+          for (int g4 = 0; g4 < PRE; ++g4) {
+            const int off = off0 + 4 * g4;
+            if (off >= my_rows || m_lo + off >= m_end) break;
+            float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int s = 0; s < sh.split; ++s) {   // in rank order
+              float4 x;
+              asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                           : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                           : "r"(recv + (uint32_t)((s * BW + n_local) * sh.cpad + off) * 4u));
+              a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+            }
+            finish_rows4<TOut>(a, res[g4], m_lo + off, m_end, n, N, b, act, out);
           }
-          finish_rows4<TOut>(a, res[g4], m_lo + off, m_end, n, N, b, act, out);
-        }
         }
       }
     }
