@@ -170,8 +170,15 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
 
   if (warp == 0) {
-    if (lane == 0) {   // ---------------------------------------------------- TMA producer
-      for (int i = 0; i < n_kb; ++i) {
+    // A TMA tile load costs its issuing thread about 190 clocks whatever the size of its box:
+    // up to four lanes, each with every n-th block of K, keep the TMA unit busy.  Their number
+    // divides the number of stages, so a lane owns its stages and fills one again only after
+    // its own earlier wait for it: it can never be two rounds of the ring ahead of the MMAs
+    // (where the parity of an older phase of the stage's barrier would pass for the awaited one).
+    pre_kb = __shfl_sync(0xffffffffu, pre_kb, 0);
+    const int producers = sh.stages % 4 == 0 ? 4 : (sh.stages % 3 == 0 ? 3 : (sh.stages % 2 == 0 ? 2 : 1));
+    if (lane < producers) {   // --------------------------------------------- TMA producers
+      for (int i = lane; i < n_kb; i += producers) {
         const int s = i % sh.stages;
         const uint32_t dst = base + s * sh.stage_bytes;
         if (i < pre_kb) {   // armed, and its weights on their way: the rows follow

@@ -25,6 +25,10 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
+// Tuning (nb_gemm_tcgen05_tune): bit 0: two MMA-issuing threads where a CTA has one tile and a
+// long K; bits 1 and up: the most producer lanes.
+int g_tune = 1 | (4 << 1);
+
 constexpr int BM = 128;
 constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
@@ -57,7 +61,9 @@ struct SmemLayout {
   static constexpr int STG_BYTES = EPI_WARPS * STG_PER_WARP;
   static constexpr int BUDGET = 222 * 1024;   // of the 227 KB a CTA may have
   static constexpr int STAGES_RAW = (BUDGET - STG_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  // 2, 3, 4, 6 or 8 stages: the producer lanes share the stages out among them (see the kernel)
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW == 7 ? 6 : (STAGES_RAW == 5 ? 4 : STAGES_RAW));
+  static constexpr int PRODUCERS = PAIR ? 1 : (STAGES % 4 == 0 ? 4 : (STAGES % 3 == 0 ? 3 : (STAGES % 2 == 0 ? 2 : 1)));
   static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
   // after tiles and staging: full[STAGES], empty[STAGES], accumulator full[2] / empty[2], two
   // residual barriers per epilogue warp, then the tensor-memory base address and the abort flag
@@ -70,7 +76,7 @@ __global__ void __launch_bounds__(cta_threads(BN, EPI))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
                     const float* residual, TOut* out, int M, int N, int K, int act, int tiles_n,
-                    int num_tiles, int a_box_bytes, int* err_word) {
+                    int num_tiles, int a_box_bytes, int* err_word, int tune) {
   using L = SmemLayout<BN, EPI, (int)sizeof(TOut), PAIR>;
   constexpr int EW = L::EPI_WARPS;
   constexpr int ACC = acc_stride(BN);
@@ -167,18 +173,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   }
   nb_grid_dependency_wait();
+  if (warp == 0) pre_kb = __shfl_sync(0xffffffffu, pre_kb, 0);   // the producer lanes all need it
+
+  // Two issuing threads.  A `tcgen05.mma` costs the thread that issues it about 80 clocks
+  // whatever its width, so a CTA with one tile and a long K (a decode step, a short prompt) is
+  // bound by that thread while the tensor cores idle; two threads with an accumulator each
+  // get rid of an instruction every 50 clocks between them.  The first takes the even blocks
+  // of K into the first accumulator, lane 0 of the first epilogue warp (idle until then) the
+  // odd ones into the second, and the epilogue adds the two.
+  const bool dual = !PAIR && (tune & 1) && num_tiles <= n_walkers && num_kb >= 8;
+  auto dual_walk = [&](int first) {
+    constexpr uint32_t idesc = instr_desc_bf16(TILE_M, BN);
+    const uint32_t d_tmem = tmem_base + (uint32_t)first * ACC;
+    bool ok = walker < num_tiles;
+    for (int kb = first; kb < num_kb && ok; kb += 2) {
+      const int s = kb % L::STAGES;
+      ok = mbar_wait(full_bar(s), (uint32_t)(kb / L::STAGES) & 1u, abort_flag);
+      if (!ok) break;
+      tc05_fence_after();
+      const uint32_t a_addr = base + s * L::STAGE_BYTES;
+      const uint64_t da = smem_desc_sw128(a_addr);
+      const uint64_t db = smem_desc_sw128(a_addr + L::A_BYTES);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        tc05_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                      (kb > first || k > 0) ? 1u : 0u);
+      tc05_commit(empty_bar(s));
+    }
+    if (ok) tc05_commit(acc_full(first));
+  };
 
   // The CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the shared-memory
   // ring runs on across tiles, and while the epilogue drains one accumulator the MMAs of the
   // next tile fill the other.
+  //
+  // A TMA tile load costs its issuing thread about 190 clocks whatever the size of the box
+  // (measured: 16 to 256 rows of 128 bytes), so one thread brings in at most 85 bytes a clock
+  // with the two boxes of a wide tile and 40 with those of a 64-row product; four lanes of the
+  // producer's warp, each with every fourth block of K, reach what the TMA unit takes (about
+  // 100 bytes a clock).
+  // The number of lanes divides the number of stages, so a lane owns its stages: it fills a
+  // stage again only after its own earlier wait for that stage, and can never be two rounds
+  // of the ring ahead of the MMAs that free it (where the parity of an older phase of the
+  // stage's barrier would pass for the one it waits for), in whatever order two issuing
+  // threads consume the stages.
+  const int PRODUCERS = (tune >> 1) >= L::PRODUCERS ? L::PRODUCERS : 1;
   if (warp == 0) {
-    if (lane == 0) {   // ---------------------------------------------------- TMA producer
-      uint32_t it = 0;
+    if (lane < PRODUCERS) {   // --------------------------------------------- TMA producers
+      uint32_t it_tile = 0;
       bool ok = true;
-      for (int tile = walker; tile < num_tiles && ok; tile += n_walkers) {
+      for (int tile = walker; tile < num_tiles && ok; tile += n_walkers, it_tile += (uint32_t)num_kb) {
         const int m0 = (tile / tiles_n) * TILE_M + m_off;
         const int n0 = (tile % tiles_n) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        // a lane takes every PRODUCERS-th block of the CTA's whole walk (across its tiles)
+        const int kb_first = (int)(((uint32_t)lane + PRODUCERS - it_tile % PRODUCERS) % PRODUCERS);
+        for (int kb = kb_first; kb < num_kb; kb += PRODUCERS) {
+          const uint32_t it = it_tile + (uint32_t)kb;
           const int s = it % L::STAGES;
           const uint32_t phase = (it / L::STAGES) & 1u;
           if (!(tile == walker && kb < pre_kb)) ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
@@ -206,7 +256,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       nb_launch_dependents();
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {   // ------------------------------------------ MMA issuer
+    if (lane == 0 && rank == 0 && dual) {
+      dual_walk(0);
+    } else if (lane == 0 && rank == 0) {   // ----------------------------------- MMA issuer
       constexpr uint32_t idesc = instr_desc_bf16(TILE_M, BN);
       uint32_t it = 0, t = 0;
       bool ok = true;
@@ -259,6 +311,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t swz = (uint32_t)(lane & 7);
     uint32_t t = 0;
     const uint32_t lead_empty0 = PAIR ? cluster_addr(acc_empty(0), 0) : 0u;
+    if (dual) {   // the second issuing thread, before its warp turns to the epilogue
+      if (e == 0 && lane == 0) dual_walk(1);
+      __syncwarp();
+    }
     for (int tile = walker; tile < num_tiles; tile += n_walkers, ++t) {
       const int m0 = (tile / tiles_n) * TILE_M + m_off, n0 = (tile % tiles_n) * BN;
       const int row0 = m0 + quarter * 32, col0 = n0 + unit * 64;
@@ -279,8 +335,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
       for (int c = 0; c < 2; ++c)
         if (bias && c < nch && col0 + c * 32 + lane < N) bias_pre[c] = __ldg(bias + col0 + c * 32 + lane);
-      const bool ready =
+      bool ready =
           __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
+      if (ready && dual)
+        ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(1), 0u, abort_flag), 0) != 0;
       if (!ready) break;
       tc05_fence_after();
 #pragma unroll 1
@@ -288,6 +346,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         uint32_t v[32];
         tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * ACC +
                                (uint32_t)(unit * 64 + c * 32), v);
+        if (dual) {   // the odd blocks of K
+          uint32_t w[32];
+          tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ACC +
+                                 (uint32_t)(unit * 64 + c * 32), w);
+          tc05_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+        }
         tc05_wait_ld();
         if (c == nch - 1) {   // this warp has read its share of the accumulator: hand it back
           tc05_fence_before();
@@ -373,6 +439,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const bool vec_f32 = (N % 4 == 0);
     const bool vec_b16 = (N % 8 == 0);
     uint32_t t = 0;
+    if (dual) {   // the second issuing thread, before its warp turns to the epilogue
+      if (warp == 2 && lane == 0) dual_walk(1);
+      __syncwarp();
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       const int m = m0 + quarter * 32 + lane;
@@ -385,8 +455,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         bias_pre[c] = (bias && nbc + lane < N) ? __ldg(bias + nbc + lane) : 0.0f;
       }
       // lane 0 decides for the warp: the tensor-memory loads below need all 32 lanes
-      const bool ready =
+      bool ready =
           __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(ab), aphase, abort_flag), 0) != 0;
+      if (ready && dual)
+        ready = __shfl_sync(0xffffffffu, (int)mbar_wait(acc_full(1), 0u, abort_flag), 0) != 0;
       if (!ready) break;
       tc05_fence_after();
 #pragma unroll 1
@@ -394,6 +466,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         uint32_t v[32];
         tc05_ld_32x32b_x32(
             tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * ACC + (uint32_t)(c * 32), v);
+        if (dual) {   // the odd blocks of K
+          uint32_t w[32];
+          tc05_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ACC + (uint32_t)(c * 32), w);
+          tc05_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+        }
         tc05_wait_ld();
         if (c == (half + 1) * CHUNKS - 1) {   // this warp has read its share: hand it back
           tc05_fence_before();
@@ -580,13 +659,18 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
-                               (int)num_tiles, a_rows * BK * 2, error_word()));
+                               (int)num_tiles, a_rows * BK * 2, error_word(), g_tune));
     return 0;
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
+  // Several producer lanes only for a single row tile (a decode step, a short prompt): its
+  // boxes are small and the producer's issue rate bounds the kernel.  With large tiles the
+  // MMAs bound it, and lanes that fill the ring out of order only delay the stage the MMAs
+  // wait for (a 2,048-token prefill: 1.16 -> 1.28 ms with four lanes).
+  const int tune = M <= BM ? g_tune : (g_tune & 1) | (1 << 1);
   NB_CUDA(nb_launch(kern, dim3(grid), dim3(cta_threads(BN, EPI)), (size_t)smem, stream, mx, mw, mo, bias,
                     residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2,
-                    error_word()));
+                    error_word(), tune));
   return 0;
 }
 
@@ -674,6 +758,12 @@ NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, 
 
 // Pairs of CTAs on 256-row tiles: 0 never, 1 where the cost model prefers them, 2 wherever a
 // paired kernel exists.
+// Comparison runs: two MMA-issuing threads on or off, and the most producer lanes (1: one).
+NB_EXPORT int nb_gemm_tcgen05_tune(int dual, int producers) {
+  g_tune = (dual ? 1 : 0) | ((producers < 1 ? 1 : producers) << 1);
+  return 0;
+}
+
 NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
   g_use_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return 0;

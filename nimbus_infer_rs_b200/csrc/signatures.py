@@ -44,6 +44,7 @@ SIGNATURES = {
     "nb_wait_probe": "pp",
     "nb_device_errors": "i",
     "nb_gemm_tcgen05_use_pairs": "i",
+    "nb_gemm_tcgen05_tune": "ii",
     "nb_gemm_tcgen05": "pppppiiiiip",
     "nb_abi_version": "",
     "nb_set_overlap": "i",

@@ -114,6 +114,39 @@ def test_linear_against_float64(ops, M, N, K, xdt, wdt):
     assert (stream.double() - ref).abs().max() <= tol + 1e-6 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("M, N, K, out_dtype", [
+    (45, 4800, 1600, torch.bfloat16), (192, 4800, 1600, torch.bfloat16), (192, 1600, 6400, torch.float32),
+    (64, 768, 768, torch.float32), (130, 20001, 1600, torch.float32), (700, 2304, 776, torch.bfloat16),
+    (128, 6400, 1600, torch.bfloat16)])
+def test_tensor_core_products_again_and_again(ops, M, N, K, out_dtype):
+    """The tiled tensor-core product with its two MMA-issuing threads (a CTA with one tile and
+    a long K) and its producer lanes that share the ring's stages: K of 25 and 100 blocks (no
+    multiple of the lanes or the stages), rings of 3, 4, 6 and 8 stages, one tile per CTA and
+    CTAs that walk over many tiles.  Forty launches back to back, each overlapping the end of
+    the one before: every result must be the first one bit for bit (a stage handed out too
+    early shows as a difference that depends on timing), and the first one right."""
+    torch.manual_seed(N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    ref = x.double() @ w.double().t() + bias.double()
+    was = ops.use_rows
+    ops.use_rows = 0                         # the tiled kernel, also where the few-rows kernel would be taken
+    try:
+        outs = [torch.full((M, N), 3.0, device=DEV, dtype=out_dtype) for _ in range(40)]
+        for o in outs:
+            ops.linear(x, w, bias, o)
+        ops.check_device_errors()
+    finally:
+        ops.use_rows = was
+    tol = 3e-6 * float(ref.abs().max()) * math.sqrt(K / 64)
+    if out_dtype == torch.bfloat16:
+        tol += 8e-3 * float(ref.abs().max())
+    assert (outs[0].double() - ref).abs().max() <= tol
+    for i, o in enumerate(outs[1:], 1):
+        assert torch.equal(o, outs[0]), f"launch {i} differs from the first"
+
+
 ROWS_SHAPES = [(64, 2304, 768), (64, 768, 3072), (17, 130, 72), (33, 1000, 100 * 8), (48, 768, 768),
                (100, 1600, 1600), (128, 4800, 1600), (80, 257 * 8, 6400), (20, 333, 64), (128, 128, 8)]
 
