@@ -218,7 +218,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   // stage's barrier would pass for the one it waits for), in whatever order two issuing
   // threads consume the stages.
   const int PRODUCERS = (tune >> 1) >= L::PRODUCERS ? L::PRODUCERS : 1;
-  if (warp == 0) {
+  // Large tiles (tune says two lanes, fewer than the stage-sharing lanes): one lane brings
+  // the rows of X, the other the rows of W, both block after block in order, so the ring
+  // fills in the order the MMAs read it at twice one thread's issue rate.  The lane of X arms
+  // the stage's barrier with the bytes of both boxes; bytes of W that land before that only
+  // take the count below zero for a while (the phase cannot end before the arming arrives).
+  const bool split_xw = !PAIR && (tune >> 1) == 2 && L::PRODUCERS != 2;
+  if (warp == 0 && split_xw) {
+    if (lane < 2) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = walker; tile < num_tiles && ok; tile += n_walkers) {
+        const int m0 = (tile / tiles_n) * TILE_M + m_off;
+        const int n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t phase = (it / L::STAGES) & 1u;
+          const bool early = tile == walker && kb < pre_kb;   // armed, W on its way since before the wait
+          if (!early) ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = base + s * L::STAGE_BYTES;
+          if (lane == 0) {
+            if (!early) mbar_expect_tx(full_bar(s), (uint32_t)a_box_bytes + L::B_BYTES);
+            tma_load_2d(a_dst, &map_x, kb * BK, m0, full_bar(s));
+          } else if (!early) {
+            tma_load_2d(a_dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+          }
+        }
+      }
+      nb_launch_dependents();
+    }
+  } else if (warp == 0) {
     if (lane < PRODUCERS) {   // --------------------------------------------- TMA producers
       uint32_t it_tile = 0;
       bool ok = true;
@@ -666,8 +696,9 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   // Several producer lanes only for a single row tile (a decode step, a short prompt): its
   // boxes are small and the producer's issue rate bounds the kernel.  With large tiles the
   // MMAs bound it, and lanes that fill the ring out of order only delay the stage the MMAs
-  // wait for (a 2,048-token prefill: 1.16 -> 1.28 ms with four lanes).
-  const int tune = M <= BM ? g_tune : (g_tune & 1) | (1 << 1);
+  // wait for (a 2,048-token prefill: 1.16 -> 1.28 ms with four lanes); there one lane brings X
+  // and one W, both in order (the kernel's `split_xw`).
+  const int tune = M <= BM ? g_tune : (g_tune & 1) | (((g_tune >> 1) >= 2 ? 2 : 1) << 1);
   NB_CUDA(nb_launch(kern, dim3(grid), dim3(cta_threads(BN, EPI)), (size_t)smem, stream, mx, mw, mo, bias,
                     residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2,
                     error_word(), tune));
