@@ -25,9 +25,11 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
-// Tuning (nb_gemm_tcgen05_tune): bit 0: two MMA-issuing threads where a CTA has one tile and a
-// long K; bits 1 and up: the most producer lanes.
-int g_tune = 1 | (4 << 1);
+// Tuning (nb_gemm_tcgen05_tune): whether a CTA with one tile and a long K has two MMA-issuing
+// threads, and whether the producer is more than one lane.  What a launch passes to the
+// kernel: bit 0: two issuing threads; bits 1-2: the producer is 0 one lane, 1 a lane for X and
+// a lane for W (large tiles), 2 lanes that share out the ring's stages (a single row tile).
+bool g_dual = true, g_lanes = true;
 
 constexpr int BM = 128;
 constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle atom row
@@ -217,13 +219,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   // of the ring ahead of the MMAs that free it (where the parity of an older phase of the
   // stage's barrier would pass for the one it waits for), in whatever order two issuing
   // threads consume the stages.
-  const int PRODUCERS = (tune >> 1) >= L::PRODUCERS ? L::PRODUCERS : 1;
-  // Large tiles (tune says two lanes, fewer than the stage-sharing lanes): one lane brings
+  const int PRODUCERS = (tune >> 1) == 2 ? L::PRODUCERS : 1;
+  // Large tiles: one lane brings
   // the rows of X, the other the rows of W, both block after block in order, so the ring
   // fills in the order the MMAs read it at twice one thread's issue rate.  The lane of X arms
   // the stage's barrier with the bytes of both boxes; bytes of W that land before that only
   // take the count below zero for a while (the phase cannot end before the arming arrives).
-  const bool split_xw = !PAIR && (tune >> 1) == 2 && L::PRODUCERS != 2;
+  const bool split_xw = !PAIR && (tune >> 1) == 1;
   if (warp == 0 && split_xw) {
     if (lane < 2) {
       uint32_t it = 0;
@@ -689,7 +691,7 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     NB_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, bias, residual, (TOut*)out, M, N, K, act, tiles_n,
-                               (int)num_tiles, a_rows * BK * 2, error_word(), g_tune));
+                               (int)num_tiles, a_rows * BK * 2, error_word(), 0));
     return 0;
   }
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);   // one CTA per SM walks the tiles
@@ -698,7 +700,7 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
   // MMAs bound it, and lanes that fill the ring out of order only delay the stage the MMAs
   // wait for (a 2,048-token prefill: 1.16 -> 1.28 ms with four lanes); there one lane brings X
   // and one W, both in order (the kernel's `split_xw`).
-  const int tune = M <= BM ? g_tune : (g_tune & 1) | (((g_tune >> 1) >= 2 ? 2 : 1) << 1);
+  const int tune = (g_dual ? 1 : 0) | ((g_lanes ? (M <= BM ? 2 : 1) : 0) << 1);
   NB_CUDA(nb_launch(kern, dim3(grid), dim3(cta_threads(BN, EPI)), (size_t)smem, stream, mx, mw, mo, bias,
                     residual, (TOut*)out, M, N, K, act, tiles_n, (int)num_tiles, a_rows * BK * 2,
                     error_word(), tune));
@@ -787,14 +789,15 @@ NB_EXPORT int nb_gemm_tcgen05_supported(int x_dtype, int w_dtype, int M, int N, 
          (M + BM - 1) / BM <= 65535;
 }
 
-// Pairs of CTAs on 256-row tiles: 0 never, 1 where the cost model prefers them, 2 wherever a
-// paired kernel exists.
-// Comparison runs: two MMA-issuing threads on or off, and the most producer lanes (1: one).
-NB_EXPORT int nb_gemm_tcgen05_tune(int dual, int producers) {
-  g_tune = (dual ? 1 : 0) | ((producers < 1 ? 1 : producers) << 1);
+// Comparison runs: two MMA-issuing threads on or off, several producer lanes on or off.
+NB_EXPORT int nb_gemm_tcgen05_tune(int dual, int lanes) {
+  g_dual = dual != 0;
+  g_lanes = lanes != 0;
   return 0;
 }
 
+// Pairs of CTAs on 256-row tiles: 0 never, 1 where the cost model prefers them, 2 wherever a
+// paired kernel exists.
 NB_EXPORT int nb_gemm_tcgen05_use_pairs(int mode) {
   g_use_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return 0;
