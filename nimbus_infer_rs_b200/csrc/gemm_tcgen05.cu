@@ -716,7 +716,6 @@ int launch(const void* X, const void* W, const float* bias, const float* residua
 // epilogue takes 64, 128 and 256.
 int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {
   const long long tiles_m = (M + BM - 1) / BM;
-  if (tiles_m == 1) return 64;
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -724,6 +723,11 @@ int pick_tile_width(int M, int N, bool f32_out, bool tma_epi) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
   }
+  // A single row tile: narrow tiles, so that many CTAs share the stream of weights -- unless
+  // there are more of them than SMs (the output head): an MMA costs its issuing thread the
+  // same up to 128 columns, so a CTA that walks over several tiles does so twice as fast with
+  // tiles of 128.
+  if (tiles_m == 1) return (N + 63) / 64 > sms ? 128 : 64;
   const int cand_f32_tma[] = {128, 96, 64}, cand_bf16_tma[] = {256, 192, 128, 64}, cand_direct[] = {256, 128, 64};
   const int* cand = !tma_epi ? cand_direct : (f32_out ? cand_f32_tma : cand_bf16_tma);
   const int n_cand = !tma_epi ? 3 : (f32_out ? 3 : 4);
