@@ -468,8 +468,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int quarter = warp & 3;   // the 32 tensor-memory lanes this warp may read
     const int half = (warp - 2) >> 2;   // which share of the tile's columns it takes
     constexpr int CHUNKS = BN / 32 / (EW / 4);   // 32-column chunks per warp
-    const bool vec_f32 = (N % 4 == 0);
-    const bool vec_b16 = (N % 8 == 0);
     uint32_t t = 0;
     if (dual) {   // the second issuing thread, before its warp turns to the epilogue
       if (warp == 2 && lane == 0) dual_walk(1);
@@ -477,7 +475,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-      const int m = m0 + quarter * 32 + lane;
       const uint32_t ab = t & 1u, aphase = (t >> 1) & 1u;
       // the bias of this warp's columns, fetched while the products still run
       float bias_pre[CHUNKS];
@@ -513,67 +510,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty(ab)) : "memory");
         }
         const int nb = n0 + c * 32;
-        // bias of the chunk's 32 columns: one value per lane, passed on by shuffles
+        // bias of the chunk's 32 columns: one value per lane
         float bias_l = bias_pre[0];
 #pragma unroll
         for (int q = 1; q < CHUNKS; ++q)
           if (c - half * CHUNKS == q) bias_l = bias_pre[q];
+        // The accumulator comes with a lane per row and a register per column; stored that way
+        // a warp's instruction would touch 32 rows, four bytes each.  The 32 x 32 block is
+        // transposed across the warp (five rounds of exchanges between lanes 16, 8, 4, 2, 1
+        // apart), after which lane l holds column l and register i row i: an instruction then
+        // writes 32 consecutive columns of one row, whatever the width of the output (the
+        // logits' 50,257 columns are no multiple of anything).
         float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float x = __uint_as_float(v[j]) + __shfl_sync(0xffffffffu, bias_l, j);
-          f[j] = nb_apply_act_fast(x, act);
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+#pragma unroll
+        for (int s2 = 16; s2 >= 1; s2 >>= 1) {
+          const bool upper = (lane & s2) != 0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j & s2) continue;
+            const float send = upper ? f[j] : f[j + s2];
+            const float got = __shfl_xor_sync(0xffffffffu, send, s2);
+            if (upper) f[j] = got; else f[j + s2] = got;
+          }
         }
-        if (m < M && nb < N) {
-          const size_t row = (size_t)m * N;
-          const bool full = nb + 32 <= N;
-          if constexpr (sizeof(TOut) == 4) {
-            float* o = reinterpret_cast<float*>(out) + row + nb;
-            const float* r = residual ? residual + row + nb : nullptr;
-            if (full && vec_f32) {
-              // `residual` may be `out` itself: fetch all of it before the first store, or
-              // every load would have to wait for the store before it
-              float4 rr[8];
-              if (r) {
+        const int col = nb + lane;
+        const int row0 = m0 + quarter * 32;
+        if (col < N) {
+          float rs[32];   // `residual` may be `out` itself: all of it before the first store
 #pragma unroll
-                for (int j = 0; j < 8; ++j) rr[j] = *reinterpret_cast<const float4*>(r + 4 * j);
-              }
+          for (int i = 0; i < 32; ++i)
+            rs[i] = (residual && row0 + i < M) ? residual[(size_t)(row0 + i) * N + col] : 0.0f;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 y = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-                if (r) { y.x += rr[j].x; y.y += rr[j].y; y.z += rr[j].z; y.w += rr[j].w; }
-                *reinterpret_cast<float4*>(o + 4 * j) = y;
-              }
-            } else {
-              float rs[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) rs[j] = (r && nb + j < N) ? r[j] : 0.0f;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < N) o[j] = f[j] + rs[j];
-            }
-          } else {
-            bf16* o = reinterpret_cast<bf16*>(out) + row + nb;
-            const float* r = residual ? residual + row + nb : nullptr;
-            if (r) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < N) f[j] += r[j];
-            }
-            if (full && vec_b16) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[j + 2 * e], f[j + 2 * e + 1]);
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < N) o[j] = __float2bfloat16_rn(f[j]);
-            }
+          for (int i = 0; i < 32; ++i) {
+            if (row0 + i >= M) break;
+            const float y = nb_apply_act_fast(f[i] + bias_l, act) + rs[i];
+            if constexpr (sizeof(TOut) == 4) reinterpret_cast<float*>(out)[(size_t)(row0 + i) * N + col] = y;
+            else reinterpret_cast<bf16*>(out)[(size_t)(row0 + i) * N + col] = __float2bfloat16_rn(y);
           }
         }
       }
