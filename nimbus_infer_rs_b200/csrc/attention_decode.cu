@@ -615,14 +615,32 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, i
     const int gh = i / HD, c = i - gh * HD;
     const int head = kvh * group + gh;
     const size_t base = ((size_t)r * n_heads + head) * n_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
-    float a = 0.0f, l = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = __ldcg(&part_ml[(base + s) * 2]);
-      const float f = (ms == -INFINITY) ? 0.0f : nb_exp2(ms - M);
-      a += f * __ldcg(&part_acc[(base + s) * HD + c]);
-      l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
+    // eight splits at a time, everything asked for before anything is used: one trip to L2
+    // for the maxima, the sums and the partial results together
+    float M = -INFINITY, a = 0.0f, l = 0.0f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float2 ml8[8];
+      float acc8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = s0 + j < n_splits;
+        ml8[j] = in ? __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s0 + j) * 2))
+                    : make_float2(-INFINITY, 0.0f);
+        acc8[j] = in ? __ldcg(&part_acc[(base + s0 + j) * HD + c]) : 0.0f;
+      }
+      float Mn = M;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, ml8[j].x);
+      const float keep = (M == -INFINITY) ? 0.0f : nb_exp2(M - Mn);
+      a *= keep;
+      l *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {   // in split order
+        const float f = (ml8[j].x == -INFINITY) ? 0.0f : nb_exp2(ml8[j].x - Mn);
+        a += f * acc8[j];
+        l += f * ml8[j].y;
+      }
+      M = Mn;
     }
     out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
   }
