@@ -31,11 +31,11 @@ constexpr int MAX_CLUSTER = 8;   // most splits that one thread-block cluster me
 // G: query heads per key/value head served by one CTA (group <= G).
 template <typename T, int HD, int G, typename TOut>
 __global__ void __launch_bounds__(THREADS)
-attention_decode_kernel(const T* __restrict__ q, int q_stride, int q_col,
-                        const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-                        NbPagedKV kv, int group, TOut* __restrict__ out, int out_stride,
-                        float scale, int window, int n_splits, float* __restrict__ part_acc,
-                        float* __restrict__ part_ml, int* __restrict__ counters, int append,
+attention_decode_kernel(const T* q, int q_stride, int q_col,
+                        const int* row_slot, const int* row_pos,
+                        NbPagedKV kv, int group, TOut* out, int out_stride,
+                        float scale, int window, int n_splits, float* part_acc,
+                        float* part_ml, int* counters, int append,
                         int k_col, int v_col) {
   constexpr int EPL = Lane16<T>::N;           // elements per lane
   constexpr int LPR = HD / EPL;               // lanes per key row
@@ -296,11 +296,11 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
 // SM matter more (a large batch).
 template <int HD, typename TOut, int MMA_STAGES, bool CLUSTERED>
 __global__ void __launch_bounds__(THREADS)
-attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, int q_col,
-                            const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-                            NbPagedKV kv, int group, TOut* __restrict__ out, int out_stride,
-                            float scale, int window, int n_splits, float* __restrict__ part_acc,
-                            float* __restrict__ part_ml, int* __restrict__ counters, int append,
+attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
+                            const int* row_slot, const int* row_pos,
+                            NbPagedKV kv, int group, TOut* out, int out_stride,
+                            float scale, int window, int n_splits, float* part_acc,
+                            float* part_ml, int* counters, int append,
                             int k_col, int v_col) {
   typedef __nv_bfloat16 bf16;
   constexpr bool clustered = CLUSTERED;

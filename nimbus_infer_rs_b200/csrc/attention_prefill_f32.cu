@@ -33,10 +33,10 @@ __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return
 
 template <typename T, int HD, typename TOut>
 __global__ void __launch_bounds__(THREADS)
-attention_prefill_f32_kernel(const T* __restrict__ q, int q_stride, int q_col,
-                             const int* __restrict__ cu_rows, const int* __restrict__ seq_slot,
-                             const int* __restrict__ seq_pos0, NbPagedKV kv, int group,
-                             TOut* __restrict__ out, int out_stride, float scale, int window) {
+attention_prefill_f32_kernel(const T* q, int q_stride, int q_col,
+                             const int* cu_rows, const int* seq_slot,
+                             const int* seq_pos0, NbPagedKV kv, int group,
+                             TOut* out, int out_stride, float scale, int window) {
   constexpr int CPT = HD / 16;          // output columns per thread
   constexpr int VLD = HD + 4;           // floats between rows of the value tile
   extern __shared__ __align__(16) float sm[];

@@ -100,11 +100,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_v,
                             const __grid_constant__ CUtensorMap map_new, int append, int k_col,
                             int v_col, int q_col,
-                            const int* __restrict__ cu_rows, const int* __restrict__ seq_slot,
-                            const int* __restrict__ seq_pos0, const int* __restrict__ block_table,
-                            int max_pages, int n_kv_heads, int group, TOut* __restrict__ out,
+                            const int* cu_rows, const int* seq_slot,
+                            const int* seq_pos0, const int* block_table,
+                            int max_pages, int n_kv_heads, int group, TOut* out,
                             int out_stride, float scale, int window, int max_splits,
-                            int chunk_pages, float* __restrict__ part, int* __restrict__ counters,
+                            int chunk_pages, float* part, int* counters,
                             int* err_word) {
   using L = AttnSmem<HD>;
   constexpr int HB = L::HB;

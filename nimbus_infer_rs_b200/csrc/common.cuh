@@ -82,7 +82,15 @@ __device__ __forceinline__ void nb_report_timeout(int* err_word) {
 // before the predecessor is complete: before its own wait a kernel may read constants
 // (weights, biases) and anything written by kernels two or more places ahead of it in the
 // stream (the cache of earlier steps, the batch layout), but nothing its direct predecessor
-// writes.  Where the trigger sits after the wait is a matter of speed: the products and the
+// writes.
+//
+// A pointer to anything that a kernel of the same step writes (activations, logits, the batch
+// layout, the cache) must not be `const __restrict__` in such a kernel: loads through one are
+// "invariant" to the compiler, which may then move them in front of the wait, whatever the
+// asm statement's memory clobber says -- the kernel reads the rows of the step before.  (It
+// happened to the decode attention's query loads, in some builds and not in others, and
+// showed only in replayed graphs, where kernels follow each other closely enough to overlap.)
+// Constants (weights, biases, a norm's scale and shift) keep the qualifier.  Where the trigger sits after the wait is a matter of speed: the products and the
 // decode attention give it once their own loads are on their way.  Without the launch
 // attribute both instructions do nothing.
 // ---------------------------------------------------------------------------------

@@ -77,7 +77,7 @@ __device__ __forceinline__ float row_group_sum(float v, float* part, int tid, in
 // bias together), mean and variance are reduced over the row's threads (two passes over the
 // registers, src/ops.rs:32-40).  Needs K <= 8 * tpr * VPT; only the M real rows are written.
 template <int NT, int VPT>
-__device__ __forceinline__ void stage_rows_norm(const float* __restrict__ X, bf16* xs, int stride,
+__device__ __forceinline__ void stage_rows_norm(const float* X, bf16* xs, int stride,
                                                 int M, int K, int width,
                                                 const float* __restrict__ gamma,
                                                 const float* __restrict__ beta, float eps,
@@ -149,7 +149,7 @@ __device__ __forceinline__ void stage_rows_norm(const float* __restrict__ X, bf1
 // Columns [k_lo, k_lo + width) of the M rows of X into shared memory as bf16 (no norm); columns
 // at or beyond K are zero.  The vectors are spread over all threads of the block.
 template <typename TX>
-__device__ __forceinline__ void stage_rows_copy(const TX* __restrict__ X, bf16* xs, int stride,
+__device__ __forceinline__ void stage_rows_copy(const TX* X, bf16* xs, int stride,
                                                 int M, int K, int k_lo, int width, int tid,
                                                 int n_threads) {
   const int vpr = width >> 3;   // vectors per row
@@ -173,7 +173,7 @@ __device__ __forceinline__ void stage_rows_copy(const TX* __restrict__ X, bf16* 
 // registers.  A fused norm needs a single segment (the launcher sees to it).
 template <int MT, int WARPS, typename TX, int VPT, int CH, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32, (CH <= 4 && VPT <= 3 && MT == 1) ? 2 : 1)
-gemm_skinny_bf16_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
+gemm_skinny_bf16_kernel(const TX* X, const float* __restrict__ gamma,
                         const float* __restrict__ beta, float eps, const bf16* __restrict__ W,
                         const float* __restrict__ bias, const float* residual, TOut* out, int M,
                         int N, int K, int act, int kseg, int tpr) {
@@ -331,7 +331,7 @@ constexpr int F32_ROWS = 8;
 
 template <typename TX, bool LN, typename TOut>
 __global__ void __launch_bounds__(F32_WARPS * 32)
-gemm_skinny_f32_kernel(const TX* __restrict__ X, const float* __restrict__ gamma,
+gemm_skinny_f32_kernel(const TX* X, const float* __restrict__ gamma,
                        const float* __restrict__ beta, float eps, const float* __restrict__ W,
                        const float* __restrict__ bias, const float* residual, TOut* out, int M,
                        int N, int K, int act) {

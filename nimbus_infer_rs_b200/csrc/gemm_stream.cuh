@@ -84,7 +84,7 @@ struct StreamShape {
 // of a row a thread holds while the row is normalised (0: no norm).
 template <int NW, int GPW, typename TX, int VPT, bool HI, typename TOut>
 __global__ void __launch_bounds__(NW * 32)
-gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* __restrict__ X,
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const TX* X,
                    const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                    const float* __restrict__ bias, const float* residual, TOut* out, int M, int N,
                    int K, int act, StreamShape sh, int* err_word) {

@@ -65,9 +65,9 @@ NB_EXPORT int nb_get_overlap() { return g_overlap; }
 // A negative token marks a padding row: it is written as zeros.
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
+__global__ void embed_pos_kernel(const int* tokens, const int* pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
-                                 float* __restrict__ out, int d) {
+                                 float* out, int d) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   const int r = blockIdx.x;
@@ -110,9 +110,9 @@ NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, c
 // The row is kept in shared memory between the passes.
 // ---------------------------------------------------------------------------------
 template <typename TOut>
-__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void layernorm_kernel(const float* x, const int* rows,
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
-                                 TOut* __restrict__ out, int d, float eps) {
+                                 TOut* out, int d, float eps) {
   extern __shared__ float row[];
   __shared__ float red[32];
   nb_grid_dependency_wait();
@@ -154,9 +154,9 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
 // is worth (a 2,048-token prefill: 1.15 -> 1.25 ms), so those fetch them where they are used.
 template <typename TOut, int VN, bool EARLY>
 __global__ void __launch_bounds__(128)
-layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+layernorm_warp_kernel(const float* x, const int* rows,
                       const float* __restrict__ gamma, const float* __restrict__ beta,
-                      TOut* __restrict__ out, int n_rows, int d, float eps) {
+                      TOut* out, int n_rows, int d, float eps) {
   const int lane = threadIdx.x & 31;
   float4 gm[EARLY ? VN : 1], bt[EARLY ? VN : 1];
   if constexpr (EARLY) {
@@ -293,7 +293,7 @@ NB_EXPORT int nb_layernorm(const float* x, const int* rows, const float* gamma, 
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ src, int src_stride, int k_col, int v_col,
-                                 const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                 const int* row_slot, const int* row_pos,
                                  NbPagedKV kv) {
   const int r = blockIdx.x;
   const int slot = row_slot[r];
@@ -319,7 +319,7 @@ __global__ void kv_append_kernel(const T* __restrict__ src, int src_stride, int 
 template <typename T>
 __global__ void __launch_bounds__(256)
 kv_append_vec_kernel(const T* __restrict__ src, int src_stride, int k_col, int v_col,
-                     const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                     const int* row_slot, const int* row_pos,
                      NbPagedKV kv, int n_rows) {
   constexpr int E = 16 / sizeof(T);              // elements per piece
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -383,8 +383,8 @@ NB_EXPORT int nb_kv_append(const void* src, int dtype, int src_stride, int k_col
 // Between two decode steps on the device: the sampled token becomes the next input and the
 // position of every live row moves on by one.  Rows with a negative slot are padding.
 // ---------------------------------------------------------------------------------
-__global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ next,
-                                      int* __restrict__ row_pos, const int* __restrict__ row_slot,
+__global__ void advance_decode_kernel(int* tokens, const int* next,
+                                      int* row_pos, const int* row_slot,
                                       int n) {
   nb_grid_dependency_wait();
   nb_launch_dependents();

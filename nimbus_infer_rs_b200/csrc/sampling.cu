@@ -14,9 +14,9 @@ constexpr int THREADS = 256;
 // For each distinct token of the sequence's history: logit > 0 ? logit / penalty
 // : logit * penalty  (src/sampler.rs:83-101).  A token that occurs several times is
 // penalised once: only its first occurrence acts.
-__global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
-                                          const int* __restrict__ history, int history_stride,
-                                          const int* __restrict__ history_len, float penalty) {
+__global__ void repetition_penalty_kernel(float* logits, int vocab,
+                                          const int* history, int history_stride,
+                                          const int* history_len, float penalty) {
   const int r = blockIdx.x;
   const int n = history_len[r];
   const int* hist = history + (size_t)r * history_stride;
@@ -35,9 +35,9 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
 
 // A decode session keeps each sequence's generated tokens on the device: the token a live row
 // runs in this step (the one selected in the step before) goes to the end of its history.
-__global__ void history_append_kernel(int* __restrict__ history, int history_stride,
-                                      int* __restrict__ history_len, const int* __restrict__ tokens,
-                                      const int* __restrict__ row_slot, int n) {
+__global__ void history_append_kernel(int* history, int history_stride,
+                                      int* history_len, const int* tokens,
+                                      const int* row_slot, int n) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -52,7 +52,7 @@ __global__ void history_append_kernel(int* __restrict__ history, int history_str
 // First index of the maximum: an element replaces the best only if it is strictly greater
 // (src/sampler.rs:173-179), so NaN never wins and ties go to the lower index.
 __global__ void __launch_bounds__(THREADS)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+argmax_kernel(const float* logits, int vocab, int* out) {
   __shared__ float s_val[THREADS];
   __shared__ int s_idx[THREADS];
   nb_grid_dependency_wait();
@@ -98,8 +98,8 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
 }
 
 __global__ void __launch_bounds__(THREADS)
-argmax_split_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out,
-                    unsigned long long* __restrict__ keys, int* __restrict__ counters) {
+argmax_split_kernel(const float* logits, int vocab, int* out,
+                    unsigned long long* keys, int* counters) {
   __shared__ unsigned long long s_key[THREADS / 32];
   __shared__ int s_last;
   nb_grid_dependency_wait();
@@ -145,8 +145,8 @@ argmax_split_kernel(const float* __restrict__ logits, int vocab, int* __restrict
 // generator on the host.  Each thread owns a contiguous segment of the vocabulary, so the
 // walk over the cumulative sum visits the tokens in index order as the reference does.
 __global__ void __launch_bounds__(THREADS)
-sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
-                          const double* __restrict__ u, int* __restrict__ out) {
+sample_temperature_kernel(const float* logits, int vocab, float temperature,
+                          const double* u, int* out) {
   __shared__ double s_red[THREADS];
   __shared__ int s_choice;
   nb_grid_dependency_wait();
@@ -226,9 +226,9 @@ __device__ __forceinline__ unsigned int order_key(float v) {
 }
 
 __global__ void __launch_bounds__(CAND_THREADS)
-top_candidates_kernel(const float* __restrict__ logits, int vocab, int n_keep, int cap, double temp,
-                      float* __restrict__ out_val, int* __restrict__ out_idx,
-                      int* __restrict__ out_count, double* __restrict__ out_stats) {
+top_candidates_kernel(const float* logits, int vocab, int n_keep, int cap, double temp,
+                      float* out_val, int* out_idx,
+                      int* out_count, double* out_stats) {
   __shared__ unsigned int hist[2048];
   __shared__ unsigned int s_prefix, s_mask, s_remaining, s_count, s_nan;
   __shared__ float s_maxf[CAND_THREADS / 32];
@@ -319,8 +319,8 @@ top_candidates_kernel(const float* __restrict__ logits, int vocab, int n_keep, i
 // u[r] that the sequence's own generator gave.  Each thread owns a contiguous piece of the
 // vocabulary.  A row with a NaN gives -1 (the caller decides on the host).
 __global__ void __launch_bounds__(CAND_THREADS)
-sample_top_k_kernel(const float* __restrict__ logits, int vocab, int k, float temperature,
-                    const double* __restrict__ u, int* __restrict__ out) {
+sample_top_k_kernel(const float* logits, int vocab, int k, float temperature,
+                    const double* u, int* out) {
   __shared__ unsigned int hist[2048];
   __shared__ unsigned int s_prefix, s_mask, s_remaining, s_nan;
   __shared__ float s_maxf[CAND_THREADS / 32];
@@ -459,8 +459,8 @@ __device__ __forceinline__ float key_value(unsigned long long c) {
 }
 
 __global__ void __launch_bounds__(CAND_THREADS)
-sample_top_p_kernel(const float* __restrict__ logits, int vocab, int k, float top_p, float temperature,
-                    const double* __restrict__ u, int* __restrict__ out) {
+sample_top_p_kernel(const float* logits, int vocab, int k, float top_p, float temperature,
+                    const double* u, int* out) {
   __shared__ double weight[TOPP_CAP];   // exp((x - max) / temp) of the sorted candidates ...
   unsigned int* hist = reinterpret_cast<unsigned int*>(weight);   // ... after the histograms
   __shared__ unsigned long long cand[TOPP_CAP];
