@@ -291,11 +291,13 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// MMA_STAGES: pages (keys and values) in flight per CTA: three when the CTAs of a launch fit
-// on the GPU with them (a short chain per CTA wants its pages early), two when more CTAs per
-// SM matter more (a large batch).
-template <int HD, typename TOut, int MMA_STAGES, bool CLUSTERED>
-__global__ void __launch_bounds__(THREADS)
+// MMA_STAGES: pages (keys and values) in flight per CTA; NW: warps.  Four warps share a page
+// (16 keys each).  A page costs a warp about 1,400 clocks of dependent steps (loads from
+// shared memory, two rounds of tensor-core instructions with the softmax between them), so
+// when the CTAs of a launch fit on the GPU with four pages each, eight warps take two pages
+// at a time; a large batch has four warps and two pages per CTA, for more CTAs per SM.
+template <int HD, typename TOut, int MMA_STAGES, bool CLUSTERED, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
                             const int* row_slot, const int* row_pos,
                             NbPagedKV kv, int group, TOut* out, int out_stride,
@@ -307,6 +309,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   constexpr int ROW = HD + 8;          // padded row of a staged page (elements)
   constexpr int KS = HD / 16;          // k-steps of the score product = row tiles of the value product
   constexpr int GH = 8;                // query heads an MMA column block holds
+  constexpr int NT = NW * 32;          // threads
+  constexpr int PPI = NW / 4;          // pages per turn of the loop
+  static_assert((NW == 4 || NW == 8) && MMA_STAGES % PPI == 0, "four or eight warps");
   constexpr int TILE = PAGE_TOKENS * HD;
   constexpr int STILE = PAGE_TOKENS * ROW;
   static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size not supported");
@@ -315,9 +320,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                   // [stages][K | V][64][ROW]
   // the warps' partial results, after the last page has been read: over the page tiles
   // (more CTAs fit on an SM that way)
-  float* w_acc = reinterpret_cast<float*>(smem_raw);                 // [WARPS][GH][HD]
-  float* w_ml = w_acc + WARPS * GH * HD;                             // [WARPS][GH][2]
-  static_assert((size_t)(WARPS * GH * HD + WARPS * GH * 2) * sizeof(float) <=
+  float* w_acc = reinterpret_cast<float*>(smem_raw);                 // [NW][GH][HD]
+  float* w_ml = w_acc + NW * GH * HD;                                // [NW][GH][2]
+  static_assert((size_t)(NW * GH * HD + NW * GH * 2) * sizeof(float) <=
                     (size_t)2 * MMA_STAGES * STILE * sizeof(bf16), "partial results must fit in the page tiles");
   __shared__ int s_last;
   // clustered: the splits of a row and key-value head are one thread-block cluster (split =
@@ -333,13 +338,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
+  const int wq = warp & 3, po = warp >> 2;   // quarter of a page, page of a turn
   const int n_heads = kv.n_kv_heads * group;
   const int slot = row_slot[r];
   if (slot < 0) {   // padding row: zeros, written by split 0
     nb_grid_dependency_wait();
     nb_launch_dependents();
     if (split == 0)
-      for (int i = tid; i < group * HD; i += THREADS)
+      for (int i = tid; i < group * HD; i += NT)
         out[(size_t)r * out_stride + (size_t)kvh * group * HD + i] = nb_from_f32<TOut>(0.0f);
     return;
   }
@@ -361,7 +367,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     bf16* kdst = tiles + (size_t)stage * 2 * STILE;
     bf16* vdst = kdst + STILE;
     constexpr int CPR = HD / 8;   // 16-byte pieces per row
-    for (int i = tid; i < PAGE_TOKENS * CPR; i += THREADS) {
+    for (int i = tid; i < PAGE_TOKENS * CPR; i += NT) {
       const int row = i / CPR, c = i - row * CPR;
       cp_async16(kdst + row * ROW + c * 8, ksrc + row * HD + c * 8);
       cp_async16(vdst + row * ROW + c * 8, vsrc + row * HD + c * 8);
@@ -407,10 +413,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   const float sl2 = scale * 1.4426950408889634f;
 
   int stage = 0;
-  for (int p = p_begin; p < p_end; ++p) {
-    cp_async_wait<MMA_STAGES - 1>();   // all but the newest groups: page p is in
+  for (int p0 = p_begin; p0 < p_end; p0 += PPI) {
+    cp_async_wait<MMA_STAGES - PPI>();   // all but the newest groups: the turn's pages are in
     __syncthreads();
-    bf16* kt = tiles + (size_t)stage * 2 * STILE;
+#pragma unroll
+    for (int q2 = 0; q2 < PPI; ++q2) {
+    const int p = p0 + q2;
+    if (p >= p_end) break;
+    bf16* kt = tiles + (size_t)(stage + q2) * 2 * STILE;
     bf16* vt = kt + STILE;
     const bool own_page = append && p == pos / PAGE_TOKENS;
     const int tail_row = kv_len - p * PAGE_TOKENS;   // first row of the page that holds no key yet
@@ -421,7 +431,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
         // tile and into the cache
         const int in_page = pos % PAGE_TOKENS;
         const int page_id = table[p];
-        for (int i = tid; i < 2 * CPR; i += THREADS) {
+        for (int i = tid; i < 2 * CPR; i += NT) {
           const bool is_v = i >= CPR;
           const int c = (is_v ? i - CPR : i) * 8;
           const uint4 val = *reinterpret_cast<const uint4*>(
@@ -436,14 +446,18 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
       // page left there.  Their probabilities are zero, but zero times a non-finite value is
       // not: the value rows are cleared in the staged copy (a masked score needs no such care,
       // it is replaced, not multiplied).
-      for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += THREADS) {
+      for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += NT) {
         const int row = tail_row + i / CPR, c = (i % CPR) * 8;
         *reinterpret_cast<uint4*>(vt + row * ROW + c) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncthreads();
     }
-    const int key0 = p * PAGE_TOKENS + warp * 16;     // first key of this warp's 16
-    if (key0 < kv_len && key0 + 16 > j_begin) {       // warp-uniform: something to attend to
+    }
+    const int p = p0 + po;                            // this warp's page
+    bf16* kt = tiles + (size_t)(stage + po) * 2 * STILE;
+    bf16* vt = kt + STILE;
+    const int key0 = p * PAGE_TOKENS + wq * 16;       // first key of this warp's 16
+    if (p < p_end && key0 < kv_len && key0 + 16 > j_begin) {   // warp-uniform: something to attend to
       // the k-steps of the score product in accumulators of their own, added up afterwards:
       // a tensor-core instruction takes long to hand its result to the next one
       float sck[KS < 4 ? KS : 4][4];
@@ -454,7 +468,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         uint32_t ka[4];
-        ldsm_x4(ka, kt + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
+        ldsm_x4(ka, kt + (wq * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
         mma_16816(sck[ks & 3], ka, qb[ks][0], qb[ks][1]);
       }
       float sc[4];
@@ -501,15 +515,19 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
 #pragma unroll
       for (int i = 0; i < KS; ++i) {
         uint32_t va4[4];
-        ldsm_x4_trans(va4, vt + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * ROW + i * 16 +
+        ldsm_x4_trans(va4, vt + (wq * 16 + (lane & 7) + (lane >> 4) * 8) * ROW + i * 16 +
                                ((lane >> 3) & 1) * 8);
         mma_16816(o[i], va4, pb0, pb1);
       }
     }
-    __syncthreads();   // the stage is free: the page after the ones in flight goes there
-    if (p + MMA_STAGES < p_end) issue(p + MMA_STAGES, stage);
-    cp_async_commit();
-    if (++stage == MMA_STAGES) stage = 0;
+    __syncthreads();   // the stages are free: the pages after the ones in flight go there
+#pragma unroll
+    for (int q2 = 0; q2 < PPI; ++q2) {
+      if (p0 + q2 + MMA_STAGES < p_end) issue(p0 + q2 + MMA_STAGES, stage + q2);
+      cp_async_commit();
+    }
+    stage += PPI;
+    if (stage == MMA_STAGES) stage = 0;
   }
   cp_async_wait<0>();
 
@@ -542,14 +560,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     const unsigned local = (unsigned)__cvta_generic_to_shared(c_part + (size_t)split * group * (HD + 2));
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(c_remote) : "r"(local), "r"(0));
   }
-  for (int i = tid; i < group * HD; i += THREADS) {
+  for (int i = tid; i < group * HD; i += NT) {
     const int gh = i / HD, c = i - gh * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, w_ml[(w * GH + gh) * 2]);
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, w_ml[(w * GH + gh) * 2]);
     float a = 0.0f, l = 0.0f;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float mw = w_ml[(w * GH + gh) * 2];
       const float f = (mw == -INFINITY) ? 0.0f : nb_exp2(mw - M);
       a += f * w_acc[(w * GH + gh) * HD + c];
@@ -583,7 +601,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     if (split != 0) return;
-    for (int i = tid; i < group * HD; i += THREADS) {
+    for (int i = tid; i < group * HD; i += NT) {
       const int gh = i / HD, c = i - gh * HD;
       const float* row = c_part + (size_t)gh * (HD + 2);
       const int step = group * (HD + 2);
@@ -611,7 +629,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int i = tid; i < group * HD; i += THREADS) {
+  for (int i = tid; i < group * HD; i += NT) {
     const int gh = i / HD, c = i - gh * HD;
     const int head = kvh * group + gh;
     const size_t base = ((size_t)r * n_heads + head) * n_splits;
@@ -646,7 +664,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   }
 }
 
-template <int HD, typename TOut, int MMA_STAGES>
+template <int HD, typename TOut, int MMA_STAGES, int NW>
 int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
                  const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
                  int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
@@ -656,26 +674,26 @@ int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, co
   const size_t most = tiles + (size_t)MAX_CLUSTER * 8 * (HD + 2) * sizeof(float);
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
   if (clustered) {
-    auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, true>;
+    auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, true, NW>;
     static bool configured = false;   // per instantiation
     if (most > 48 * 1024 && !configured) {
       NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
       configured = true;
     }
     const size_t smem = tiles + (size_t)n_splits * group * (HD + 2) * sizeof(float);
-    NB_CUDA(nb_launch_clusters(kern, grid, dim3(THREADS), smem, stream, n_splits,
+    NB_CUDA(nb_launch_clusters(kern, grid, dim3(NW * 32), smem, stream, n_splits,
                                (const __nv_bfloat16*)q, q_stride, q_col, row_slot, row_pos, kv, group,
                                (TOut*)out, out_stride, scale, window, n_splits, part_acc, part_ml,
                                counters, append, k_col, v_col));
     return 0;
   }
-  auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, false>;
+  auto kern = attention_decode_mma_kernel<HD, TOut, MMA_STAGES, false, NW>;
   static bool configured = false;   // per instantiation
   if (tiles > 48 * 1024 && !configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
     configured = true;
   }
-  NB_CUDA(nb_launch(kern, grid, dim3(THREADS), tiles, stream, (const __nv_bfloat16*)q, q_stride, q_col,
+  NB_CUDA(nb_launch(kern, grid, dim3(NW * 32), tiles, stream, (const __nv_bfloat16*)q, q_stride, q_col,
                     row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits,
                     part_acc, part_ml, counters, append, k_col, v_col));
   return 0;
@@ -693,17 +711,21 @@ int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, cons
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
   }
-  // CTAs of three stages that fit on an SM (of 220 KB), and whether the launch fits with them
-  const size_t smem3 = (size_t)6 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
+  // Eight warps and four pages in flight per CTA when the whole launch fits on the GPU that
+  // way (an SM has 228 KB of shared memory, a CTA costs its own and 1 KB), else four warps and
+  // two pages, for more CTAs per SM.
+  const size_t smem4 = (size_t)8 * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16) +
+                       (clustered ? (size_t)n_splits * group * (HD + 2) * sizeof(float) : 0);
   const long long ctas = (long long)n_splits * kv.n_kv_heads * n_rows;
-  const long long room3 = (long long)((220 * 1024) / smem3) * sms;
-  if (ctas <= room3)
-    return launch_mma_s<HD, TOut, 3>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                     scale, window, n_rows, n_splits, part_acc, part_ml, counters,
-                                     append, k_col, v_col, clustered, stream);
-  return launch_mma_s<HD, TOut, 2>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                   scale, window, n_rows, n_splits, part_acc, part_ml, counters, append,
-                                   k_col, v_col, clustered, stream);
+  long long per_sm = (long long)((228 * 1024) / (smem4 + 1024));
+  if (per_sm > 8) per_sm = 8;   // 2,048 threads an SM
+  if (ctas <= per_sm * sms)
+    return launch_mma_s<HD, TOut, 4, 8>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
+                                        scale, window, n_rows, n_splits, part_acc, part_ml, counters,
+                                        append, k_col, v_col, clustered, stream);
+  return launch_mma_s<HD, TOut, 2, 4>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
+                                      scale, window, n_rows, n_splits, part_acc, part_ml, counters, append,
+                                      k_col, v_col, clustered, stream);
 }
 
 template <typename TOut>

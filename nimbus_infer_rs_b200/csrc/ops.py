@@ -281,15 +281,15 @@ class CudaBackend:
     def _decode_splits(self, base_ctas: int, pages: int, kv, dtype) -> int:
         """Into how many splits a decode launch cuts each sequence's pages; `base_ctas` is
         rows x key-value heads.  The tensor-core kernel: as many as keep every CTA of the
-        launch on the GPU at once with three pages in flight each (measured on a B200 at
+        launch on the GPU at once with four pages in flight each and eight warps (measured on a B200 at
         contexts of 256 and 1,024 and batches of 1 to 32: a CTA that has to wait for a place
         costs more than a longer walk), and none that would get no page.  A small launch (at
         most two CTAs per SM) merges its splits inside thread-block clusters and has at most
         as many as a cluster holds; the library applies the same rule."""
         if dtype != torch.bfloat16:
             return max(1, min(pages, DECODE_TARGET_CTAS // base_ctas))
-        three_pages = 6 * kv.page * (kv.head_dim + 8) * 2
-        room = max(1, (220 * 1024) // three_pages) * self._sms
+        four_pages = 8 * kv.page * (kv.head_dim + 8) * 2
+        room = max(1, min(8, (228 * 1024) // (four_pages + 1024))) * self._sms
 
         def cut(most):
             most = max(1, min(pages, most, room // base_ctas))
