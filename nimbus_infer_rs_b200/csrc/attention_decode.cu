@@ -383,10 +383,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
 
   nb_grid_dependency_wait();
   // Every CTA of a cluster says that it runs (a padding row's CTAs have all left above); the
-  // matching wait stands in front of the first store into another CTA's shared memory.  The
-  // arrive stands behind the wait on the predecessor on purpose: in front of it, steps that
-  // were replayed from a recorded graph came out wrong on a B200 (the same launches issued
-  // one by one did not).  Why is not known; the later place costs nothing.
+  // matching wait stands in front of the first store into another CTA's shared memory.
   if constexpr (clustered) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
 
   // Q^T as the B operand of the score product: column g of the block is query head g of the
