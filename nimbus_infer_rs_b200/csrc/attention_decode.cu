@@ -846,19 +846,7 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
                "attention_decode: query rows must be 16-byte aligned");
     // up to MAX_CLUSTER splits merge through the shared memory of a thread-block cluster, more
     // through the scratch arrays and a counter
-    bool clustered = clusters_allowed > 0 && n_splits >= 2 && n_splits <= MAX_CLUSTER;
-    if (clustered && clusters_allowed == 1) {
-      // launching in clusters has a price of its own; measured on a B200 it is repaid while
-      // the launch is small (up to about two CTAs per SM), where the merge is a large part
-      static int sms = 0;
-      if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-          sms = 148;
-      }
-      clustered = (long long)n_splits * n_kv_heads * n_rows <= 2LL * sms;
-    }
+    const bool clustered = clusters_allowed > 0 && n_splits >= 2 && n_splits <= MAX_CLUSTER;
     rc = out_dtype == NB_F32
              ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
              : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
@@ -884,12 +872,11 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
                           v_col, g_cluster_merge.load(), stream);
 }
 
-// How the splits of the bfloat16 kernel merge: 0 always through the scratch arrays; 1 (the
-// default) through a cluster's shared memory where there are at most 8 of them and the launch
-// has at most two CTAs per SM; 2 through a cluster wherever there are 2 to 8.  Returns the
+// How the splits of the bfloat16 kernel merge: 0 always through the scratch arrays; otherwise
+// (the default) through a cluster's shared memory where there are 2 to 8 of them.  Returns the
 // earlier setting.
 NB_EXPORT int nb_attention_decode_cluster_merge(int mode) {
-  return g_cluster_merge.exchange(mode < 0 ? 0 : mode > 2 ? 2 : mode);
+  return g_cluster_merge.exchange(mode != 0 ? 1 : 0);
 }
 
 // Most splits that merge inside a cluster.

@@ -88,9 +88,8 @@ class CudaBackend:
         # CTAs of a cluster: never / where it is the faster one (a long K over few columns) /
         # wherever it applies
         self.use_rows = int(os.environ.get("NIMBUS_B200_ROWS", "1") or 1)
-        # NIMBUS_B200_DECODE_CLUSTERS=0/1/2: the splits of the bfloat16 decode attention merge
-        # through scratch memory and a counter / inside a thread-block cluster's shared memory
-        # where the launch is small / inside a cluster wherever there are 2 to 8 of them
+        # NIMBUS_B200_DECODE_CLUSTERS=0: the splits of the bfloat16 decode attention merge through
+        # scratch memory and a counter instead of a thread-block cluster's shared memory
         self._cluster_limit = int(self.lib.nb_attention_decode_cluster_limit())
         self._sms = torch.cuda.get_device_properties(self._device_index).multi_processor_count
         self.set_decode_clusters(int(os.environ.get("NIMBUS_B200_DECODE_CLUSTERS", "1") or 1))
@@ -107,11 +106,10 @@ class CudaBackend:
         self.pairs = int(mode)
         self.lib.nb_gemm_tcgen05_use_pairs(self.pairs)
 
-    def set_decode_clusters(self, mode) -> None:
-        """How the splits of the bfloat16 decode attention merge: 0/False through scratch
-        memory, 1/True inside thread-block clusters where the launch is small, 2 inside
-        clusters wherever there are 2 to 8 splits."""
-        self.decode_clusters = int(mode)
+    def set_decode_clusters(self, on) -> None:
+        """Whether 2 to 8 splits of the bfloat16 decode attention merge inside a thread-block
+        cluster (the default) or through scratch memory like any other number of them."""
+        self.decode_clusters = 1 if on else 0
         self.lib.nb_attention_decode_cluster_merge(self.decode_clusters)
 
     def set_overlap(self, on: bool) -> None:
@@ -280,27 +278,23 @@ class CudaBackend:
     # -- cache and attention ----------------------------------------------------------
     def _decode_splits(self, base_ctas: int, pages: int, kv, dtype) -> int:
         """Into how many splits a decode launch cuts each sequence's pages; `base_ctas` is
-        rows x key-value heads.  The tensor-core kernel: as many as keep every CTA of the
-        launch on the GPU at once with four pages in flight each and eight warps (measured on a B200 at
-        contexts of 256 and 1,024 and batches of 1 to 32: a CTA that has to wait for a place
-        costs more than a longer walk), and none that would get no page.  A small launch (at
-        most two CTAs per SM) merges its splits inside thread-block clusters and has at most
-        as many as a cluster holds; the library applies the same rule."""
+        rows x key-value heads.  The tensor-core kernel (swept on a B200 at contexts of 256 and
+        1,024 and batches of 1 to 32): four pages a split (eight warps take two at a time, so
+        a split is two turns of the loop and every page is asked for before the kernel's
+        wait); fewer splits if the launch would not fit on the GPU at once with four pages in
+        flight per CTA, and only counts that deal the pages out evenly; more, while the launch
+        is still smaller than the GPU.  2 to 8 splits merge inside a thread-block cluster."""
         if dtype != torch.bfloat16:
             return max(1, min(pages, DECODE_TARGET_CTAS // base_ctas))
         four_pages = 8 * kv.page * (kv.head_dim + 8) * 2
         room = max(1, min(8, (228 * 1024) // (four_pages + 1024))) * self._sms
-
-        def cut(most):
-            most = max(1, min(pages, most, room // base_ctas))
-            per_split = -(-pages // most)
-            return -(-pages // per_split)
-
-        if self.decode_clusters:
-            n = cut(self._cluster_limit)
-            if self.decode_clusters == 2 or n * base_ctas <= 2 * self._sms:
-                return n
-        return cut(16)
+        most = min(pages, self._cluster_limit if self.decode_clusters else 16)
+        s = max(1, min(most, -(-pages // 4)))
+        while s > 1 and (s * base_ctas > room or pages % s):
+            s -= 1
+        while 2 * s <= most and 2 * s * base_ctas <= self._sms and pages % (2 * s) == 0:
+            s *= 2
+        return s
 
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
         """Scratch of the split decode attention: partial sums per (row, head, split) and one

@@ -687,7 +687,7 @@ def test_decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv, clu
     if dtype == torch.float32 and not clusters:
         pytest.skip("the 32-bit kernel has one way to merge")
     was = ops.decode_clusters
-    ops.set_decode_clusters(2 if clusters else 0)
+    ops.set_decode_clusters(clusters)
     try:
         _decode_attention_over_splits(ops, dtype, H, Hk, hd, window, max_kv)
     finally:
