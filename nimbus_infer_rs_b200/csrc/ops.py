@@ -281,8 +281,9 @@ class CudaBackend:
         rows x key-value heads.  The tensor-core kernel (swept on a B200 at contexts of 256 and
         1,024 and batches of 1 to 32): four pages a split (eight warps take two at a time, so
         a split is two turns of the loop and every page is asked for before the kernel's
-        wait); fewer splits if the launch would not fit on the GPU at once with four pages in
-        flight per CTA, and only counts that deal the pages out evenly; more, while the launch
+        wait); fewer splits if the launch would be more than a third larger than what fits on
+        the GPU at once with four pages in flight per CTA (512 to 576 CTAs of four warps still
+        beat half as many splits, 768 do not), and only counts that deal the pages out evenly; more, while the launch
         is still smaller than the GPU.  2 to 8 splits merge inside a thread-block cluster."""
         if dtype != torch.bfloat16:
             return max(1, min(pages, DECODE_TARGET_CTAS // base_ctas))
@@ -290,7 +291,7 @@ class CudaBackend:
         room = max(1, min(8, (228 * 1024) // (four_pages + 1024))) * self._sms
         most = min(pages, self._cluster_limit if self.decode_clusters else 16)
         s = max(1, min(most, -(-pages // 4)))
-        while s > 1 and (s * base_ctas > room or pages % s):
+        while s > 1 and (s * base_ctas > room * 13 // 10 or pages % s):   # a third over still pays
             s -= 1
         while 2 * s <= most and 2 * s * base_ctas <= self._sms and pages % (2 * s) == 0:
             s *= 2
