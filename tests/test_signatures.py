@@ -34,3 +34,33 @@ def test_declared_signatures_match_the_sources():
             continue
         assert SIGNATURES.get(name) == letters, name
     assert set(SIGNATURES) == set(found) - OTHER
+
+
+# Kernel parameters that point to constants of the model: the only ones that may be
+# `__restrict__` in a kernel that can start before its predecessor has ended.
+CONSTANT_PARAMS = {"gamma", "beta", "bias", "W", "wte", "wpe"}
+
+
+def test_no_restrict_on_step_data_in_kernels_that_start_early():
+    """A kernel that calls nb_grid_dependency_wait() may start while the kernel before it still
+    runs.  Loads through a `const __restrict__` pointer are invariant to the compiler, which may
+    move them in front of that wait, where the predecessor has not written the data yet (it
+    happened to the decode attention's query rows).  So in such kernels only pointers to
+    constants carry the qualifier."""
+    src_dir = Path(csrc_pkg.__file__).parent
+    checked = 0
+    for path in sorted(list(src_dir.glob("*.cu")) + list(src_dir.glob("*.cuh"))):
+        text = path.read_text()
+        for m in re.finditer(r"__global__[^;{]*?(\w+)\s*\(([^)]*)\)\s*\{", text, re.S):
+            name, params = m.group(1), m.group(2)
+            # the kernel's body: up to the next kernel or the end of the file
+            nxt = text.find("__global__", m.end())
+            body = text[m.end(): nxt if nxt >= 0 else len(text)]
+            if "nb_grid_dependency_wait" not in body:
+                continue
+            checked += 1
+            for p in params.split(","):
+                if "__restrict__" in p:
+                    pname = p.strip().split()[-1]
+                    assert pname in CONSTANT_PARAMS, f"{path.name}: {name}({pname}) is __restrict__"
+    assert checked >= 15
