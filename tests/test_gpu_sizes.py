@@ -73,3 +73,41 @@ def test_bfloat16_follows_float32_at_real_sizes(tmp_path_factory, preset):
         e.ops.check_device_errors()
     a, b = outs["bfloat16"].double(), outs["float32"].double()
     assert float((a - b).abs().max() / b.abs().max()) <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("clusters", [1, 0])
+def test_a_decode_session_at_real_head_sizes_and_a_long_context(tmp_path_factory, clusters):
+    """GPT-2 small's widths and heads (two layers), contexts of 700, 130 and 64 tokens in a
+    model of 1,024 positions: the decode session's replayed graph cuts every sequence's 16
+    possible pages into splits that merge inside a thread-block cluster (or, with `clusters`
+    off, through scratch memory), the long sequence reads eleven pages, the short one crosses
+    a page end on its first step.  The logits the session holds after each of 6 steps are the
+    plain implementation's."""
+    from nimbus_infer_rs_b200.engine.decode import DecodeSession
+    obj = dict(preset_json("gpt2"), n_layer=LAYERS, n_positions=1024)
+    cfg = GPT2Config.from_json(obj)
+    d = write_random_model(tmp_path_factory.mktemp("gpt2_long"), cfg, 5, std=0.02, bias_std=0.01,
+                           gamma_jitter=0.02)
+    W = P.PlainWeights(d)
+    n_steps = 6
+    seqs = [random_tokens(cfg.vocab_size, n + n_steps, seed=40 + i) for i, n in enumerate((700, 130, 64))]
+    refs = [P.forward_logits(W, t) for t in seqs]
+    e = Engine.load(d, dtype="bfloat16", cache_tokens=4096)
+    was = e.ops.decode_clusters
+    e.ops.set_decode_clusters(clusters)
+    try:
+        slots = [e.alloc_slot() for _ in seqs]
+        e.step([(s, t[:-n_steps - 1], []) for s, t in zip(slots, seqs)])
+        session = DecodeSession(e, slots, [t[-n_steps - 1] for t in seqs])
+        for k in range(n_steps):
+            session.step([t[len(t) - n_steps - 1 + k] for t in seqs])      # the token each row runs now
+            session.read_tokens()
+            want = torch.stack([ref[len(t) - n_steps - 1 + k] for ref, t in zip(refs, seqs)])
+            assert_close(session.logits.clone(), want, "bfloat16", f"long session step {k}")
+        assert session._graph is not None
+        session.close()
+        for s in slots:
+            e.free_slot(s)
+        e.ops.check_device_errors()
+    finally:
+        e.ops.set_decode_clusters(was)
