@@ -2,12 +2,15 @@
 //
 // The work is reading the cache once, so the kernel is laid out for bandwidth: a CTA takes one
 // (row, key/value head, split of the sequence's pages), streams whole pages (64 keys x head_dim,
-// contiguous) into shared memory with 16-byte cp.async copies, two pages in flight, and all
-// query heads that share the key/value head are served from the same staged page.  Scores,
-// softmax and the weighted sum are fp32; every warp keeps a running (max, sum, accumulator)
-// for its quarter of each page, the warps are merged at the end of the split, and the splits
-// are merged by whichever CTA of the (row, head) finishes last (a counter in scratch memory
-// that it leaves at zero again).
+// contiguous) into shared memory with 16-byte cp.async copies, two or four pages in flight (the
+// first ones asked for before the kernel's wait on its predecessor), and all query heads that
+// share the key/value head are served from the same staged page.  Scores, softmax and the
+// weighted sum are fp32; every warp keeps a running (max, sum, accumulator) for its quarter of
+// a page (the bfloat16 kernel has four warps on a page, or eight on two pages at a time), the
+// warps are merged at the end of the split, and the splits are merged either inside a
+// thread-block cluster (2 to 8 splits of the bfloat16 kernel: partial results into the first
+// CTA's shared memory, one cluster barrier) or by whichever CTA of the (row, head) finishes
+// last (a counter in scratch memory that it leaves at zero again).
 //
 // Scratch (caller-allocated): part_acc [rows][heads][splits][head_dim] fp32, part_ml
 // [rows][heads][splits][2] fp32, counters [rows][kv_heads] int32, zero before the first use.
