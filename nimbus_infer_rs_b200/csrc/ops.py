@@ -31,6 +31,27 @@ STREAM_MAX_ROWS = 16   # ... and with at most this many the kernel that stages w
 ROWS_MAX_ROWS = 128    # up to this many rows a product's weights are the tensor cores' 128-row operand
 
 
+def decode_splits(base_ctas: int, pages: int, page: int, head_dim: int, sms: int, most: int) -> int:
+    """Splits of a sequence's pages in the tensor-core decode attention (swept on a B200 at
+    contexts of 256 and 1,024 and batches of 1 to 32).  Four pages a split: eight warps take
+    two at a time, so a split is two turns of the loop and every page is asked for before the
+    kernel's wait.  Fewer splits if the launch would be more than a third larger than what
+    fits on the GPU at once with four pages in flight per CTA (512 to 576 CTAs of four warps
+    still beat half as many splits, 768 do not), and only counts that deal the pages out
+    evenly (three splits of 16 pages measured 10 % worse than two or four).  More, while the
+    launch is still smaller than the GPU.  `most`: the largest count allowed (what merges
+    inside a thread-block cluster, or 16)."""
+    four_pages = 8 * page * (head_dim + 8) * 2
+    room = max(1, min(8, (228 * 1024) // (four_pages + 1024))) * sms
+    most = max(1, min(pages, most))
+    s = max(1, min(most, -(-pages // 4)))
+    while s > 1 and (s * base_ctas > room * 13 // 10 or pages % s):
+        s -= 1
+    while 2 * s <= most and 2 * s * base_ctas <= sms and pages % (2 * s) == 0:
+        s *= 2
+    return s
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -277,25 +298,13 @@ class CudaBackend:
 
     # -- cache and attention ----------------------------------------------------------
     def _decode_splits(self, base_ctas: int, pages: int, kv, dtype) -> int:
-        """Into how many splits a decode launch cuts each sequence's pages; `base_ctas` is
-        rows x key-value heads.  The tensor-core kernel (swept on a B200 at contexts of 256 and
-        1,024 and batches of 1 to 32): four pages a split (eight warps take two at a time, so
-        a split is two turns of the loop and every page is asked for before the kernel's
-        wait); fewer splits if the launch would be more than a third larger than what fits on
-        the GPU at once with four pages in flight per CTA (512 to 576 CTAs of four warps still
-        beat half as many splits, 768 do not), and only counts that deal the pages out evenly; more, while the launch
-        is still smaller than the GPU.  2 to 8 splits merge inside a thread-block cluster."""
+        """Into how many splits a decode launch cuts each sequence's pages (`base_ctas`: rows x
+        key-value heads).  The 32-bit kernel aims at a fixed number of CTAs; the tensor-core
+        kernel follows `decode_splits`."""
         if dtype != torch.bfloat16:
             return max(1, min(pages, DECODE_TARGET_CTAS // base_ctas))
-        four_pages = 8 * kv.page * (kv.head_dim + 8) * 2
-        room = max(1, min(8, (228 * 1024) // (four_pages + 1024))) * self._sms
-        most = min(pages, self._cluster_limit if self.decode_clusters else 16)
-        s = max(1, min(most, -(-pages // 4)))
-        while s > 1 and (s * base_ctas > room * 13 // 10 or pages % s):   # a third over still pays
-            s -= 1
-        while 2 * s <= most and 2 * s * base_ctas <= self._sms and pages % (2 * s) == 0:
-            s *= 2
-        return s
+        return decode_splits(base_ctas, pages, kv.page, kv.head_dim, self._sms,
+                             self._cluster_limit if self.decode_clusters else 16)
 
     def _decode_scratch(self, device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
         """Scratch of the split decode attention: partial sums per (row, head, split) and one

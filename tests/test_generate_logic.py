@@ -193,3 +193,23 @@ def test_a_preset_name_builds_a_model_with_no_file_on_disk(cpu_backend):
     assert set(info["weight_mb_by_dtype"]) == {"float32"}
     out = e.generate([[1, 2, 3]], SamplingParams(max_new_tokens=4, temperature=0.0))
     assert len(out[0]) == 4
+
+
+def test_splits_of_the_decode_attention():
+    """How many CTAs share a sequence's pages (GPT-2 small's 12 heads of 64, a B200's 148 SMs,
+    pages of 64 tokens): the rule's answers where a sweep on the GPU gave the best or nearly
+    the best count."""
+    from nimbus_infer_rs_b200.csrc.ops import decode_splits
+
+    def s(batch, pages, heads=12, most=8):
+        return decode_splits(batch * heads, pages, 64, 64, 148, most)
+    # context 1,024 (16 pages): four pages a split while the launch fits, more for one row
+    assert [s(b, 16) for b in (1, 2, 4, 8, 12, 16, 24, 32, 64)] == [8, 4, 4, 4, 4, 2, 2, 1, 1]
+    # context 256 (4 pages): no split, but a launch far smaller than the GPU is cut anyway
+    assert [s(b, 4) for b in (1, 2, 4, 8, 32)] == [4, 4, 2, 1, 1]
+    # pages that no count deals out evenly stay whole; one page cannot be cut
+    assert s(3, 5, heads=2) == 1 and s(1, 1) == 1
+    # 16 heads (GPT-2 medium) at batch 8: 512 CTAs are still taken, 768 would not be
+    assert s(8, 16, heads=16) == 4 and s(12, 16, heads=16) == 2
+    # without clusters up to 16 splits
+    assert s(1, 64, most=16) == 16 and s(1, 64) == 8
