@@ -37,6 +37,23 @@ def test_safetensors_round_trip(tmp_path):
             f.tensor("zz")
 
 
+def test_half_precision_bit_patterns_of_the_reference(tmp_path):
+    """Bytes written by hand, not by this library's writer: the F16 patterns and the BF16 pair
+    of the reference's own unit tests (src/safetensors.rs:196-222) come out as the same values."""
+    f16 = [0x0000, 0x3C00, 0x4000, 0x7C00, 0x7E00, 0xFC00]
+    bf16 = [0x3F80, 0x4000]                              # the top halves of 1.0f32 and 2.0f32
+    hdr = json.dumps({"h": {"dtype": "F16", "shape": [6], "data_offsets": [0, 12]},
+                      "w": {"dtype": "BF16", "shape": [2], "data_offsets": [12, 16]}}).encode()
+    body = b"".join(v.to_bytes(2, "little") for v in f16 + bf16)
+    p = tmp_path / "half.safetensors"
+    p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + body)
+    with SafeTensorsFile(p) as f:
+        h = f.tensor("h").float()
+        assert h[:3].tolist() == [0.0, 1.0, 2.0]
+        assert h[3] == float("inf") and torch.isnan(h[4]) and h[5] == float("-inf")
+        assert f.tensor("w").dtype == torch.bfloat16 and f.tensor("w").float().tolist() == [1.0, 2.0]
+
+
 def test_safetensors_bad_files(tmp_path):
     p = tmp_path / "bad.safetensors"
     p.write_bytes(b"\x01\x02")
