@@ -162,7 +162,7 @@ class CudaBackend:
         if tokens.numel() < n or pos.numel() < n or wte.shape[1] != d:
             raise KernelError("embed_pos: shapes do not agree")
         self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
-                   (dtype_code(wte.dtype)), _ptr(out), (n), (d), self._stream())
+                   dtype_code(wte.dtype), _ptr(out), n, d, self._stream())
 
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         _check(x, "x", torch.float32, 2)
@@ -176,7 +176,7 @@ class CudaBackend:
         if x.shape[1] != d or gamma.numel() != d or (rows is None and x.shape[0] < n):
             raise KernelError("layernorm: shapes do not agree")
         self._call("nb_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
-                   (dtype_code(out.dtype)), (n), (d), (eps), self._stream())
+                   dtype_code(out.dtype), n, d, eps, self._stream())
 
     # -- matrix products --------------------------------------------------------------
     def linear(self, x, w, bias, out, act=ACT_NONE, residual=None, norm=None):
@@ -228,10 +228,10 @@ class CudaBackend:
                 self.layernorm(x, norm[0], norm[1], norm[2], h)
                 x, norm = h, None
             gamma, beta, eps = (norm[0], norm[1], norm[2]) if norm is not None else (None, None, 0.0)
-            self._call("nb_gemm_skinny", _ptr(x), (dtype_code(x.dtype)), _ptr(gamma),
-                       _ptr(beta), (eps), _ptr(w), (dtype_code(w.dtype)), _ptr(bias),
-                       _ptr(residual), _ptr(out), (dtype_code(out.dtype)), (M), (N),
-                       (K), (act), self._stream())
+            self._call("nb_gemm_skinny", _ptr(x), dtype_code(x.dtype), _ptr(gamma),
+                       _ptr(beta), eps, _ptr(w), dtype_code(w.dtype), _ptr(bias),
+                       _ptr(residual), _ptr(out), dtype_code(out.dtype), M, N,
+                       K, act, self._stream())
             return
         if norm is not None:
             h = torch.empty((M, K), device=x.device, dtype=norm[3])
@@ -248,14 +248,14 @@ class CudaBackend:
                        dtype_code(out.dtype), M, N, K, act, self._stream())
             return
         if self.use_tcgen05 and self.lib.nb_gemm_tcgen05_supported(
-                (dtype_code(x.dtype)), (dtype_code(w.dtype)), (M), (N), (K)):
+                dtype_code(x.dtype), dtype_code(w.dtype), M, N, K):
             self._call("nb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
-                       (dtype_code(out.dtype)), (M), (N), (K), (act),
+                       dtype_code(out.dtype), M, N, K, act,
                        self._stream())
             return
-        self._call("nb_gemm_simt", _ptr(x), (dtype_code(x.dtype)), _ptr(w),
-                   (dtype_code(w.dtype)), _ptr(bias), _ptr(residual), _ptr(out),
-                   (dtype_code(out.dtype)), (M), (N), (K), (act),
+        self._call("nb_gemm_simt", _ptr(x), dtype_code(x.dtype), _ptr(w),
+                   dtype_code(w.dtype), _ptr(bias), _ptr(residual), _ptr(out),
+                   dtype_code(out.dtype), M, N, K, act,
                    self._stream())
 
     # A kernel whose bounded wait on a barrier ran out says so in a word of pinned host memory
@@ -340,10 +340,10 @@ class CudaBackend:
 
     def kv_append(self, src, k_col, v_col, row_slot, row_pos, kv, n_rows):
         _check(src, "src", kv.k.dtype, 2)
-        self._call("nb_kv_append", _ptr(src), (dtype_code(src.dtype)), (src.shape[1]),
-                   (k_col), (v_col), _ptr(row_slot), _ptr(row_pos), _ptr(kv.k),
-                   _ptr(kv.v), _ptr(kv.block_table), (kv.block_table.shape[1]),
-                   (kv.page), (kv.n_kv_heads), (kv.head_dim), (n_rows),
+        self._call("nb_kv_append", _ptr(src), dtype_code(src.dtype), src.shape[1],
+                   k_col, v_col, _ptr(row_slot), _ptr(row_pos), _ptr(kv.k),
+                   _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1],
+                   kv.page, kv.n_kv_heads, kv.head_dim, n_rows,
                    self._stream())
 
     def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
@@ -358,19 +358,19 @@ class CudaBackend:
         if out.shape[0] < n_rows or out.shape[1] != n_heads * kv.head_dim:
             raise KernelError("attention: output shape does not match")
         if layout.is_decode and self.lib.nb_attention_decode_supported(
-                (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
-                (kv.n_kv_heads), (kv.page)):
+                dtype_code(q_src.dtype), kv.head_dim, n_heads,
+                kv.n_kv_heads, kv.page):
             pages = max(1, -(-layout.max_kv_len // kv.page))
             n_splits = self._decode_splits(n_rows * kv.n_kv_heads, pages, kv, q_src.dtype)
             acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
                                                      kv.head_dim, n_splits)
-            self._call("nb_attention_decode", _ptr(q_src), (dtype_code(q_src.dtype)),
-                       (q_src.shape[1]), (q_col), _ptr(layout.row_slot),
+            self._call("nb_attention_decode", _ptr(q_src), dtype_code(q_src.dtype),
+                       q_src.shape[1], q_col, _ptr(layout.row_slot),
                        _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
-                       (kv.block_table.shape[1]), (kv.page), (n_heads),
-                       (kv.n_kv_heads), (kv.head_dim), _ptr(out),
-                       (dtype_code(out.dtype)), (out.shape[1]), (scale),
-                       (window), (n_rows), (n_splits), _ptr(acc), _ptr(ml),
+                       kv.block_table.shape[1], kv.page, n_heads,
+                       kv.n_kv_heads, kv.head_dim, _ptr(out),
+                       dtype_code(out.dtype), out.shape[1], scale,
+                       window, n_rows, n_splits, _ptr(acc), _ptr(ml),
                        _ptr(counters), (1 if append else 0),
                        (append[0] if append else 0), (append[1] if append else 0),
                        self._stream())
@@ -415,17 +415,17 @@ class CudaBackend:
         if append:
             self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv, n_rows)
         if (not layout.is_decode) and self.lib.nb_attention_prefill_supported(
-                (dtype_code(q_src.dtype)), (kv.head_dim), (n_heads),
-                (kv.n_kv_heads), (kv.page), (q_src.shape[1]), (q_col)):
+                dtype_code(q_src.dtype), kv.head_dim, n_heads,
+                kv.n_kv_heads, kv.page, q_src.shape[1], q_col):
             if layout.n_rows > layout.n_tokens:
                 out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
-            self._call("nb_attention_prefill", _ptr(q_src), (dtype_code(q_src.dtype)),
-                       (q_src.shape[1]), (q_col), _ptr(layout.cu_rows),
+            self._call("nb_attention_prefill", _ptr(q_src), dtype_code(q_src.dtype),
+                       q_src.shape[1], q_col, _ptr(layout.cu_rows),
                        _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
-                       _ptr(kv.block_table), (kv.block_table.shape[1]), (kv.page),
-                       (n_heads), (kv.n_kv_heads), (kv.head_dim), _ptr(out),
-                       (dtype_code(out.dtype)), (out.shape[1]), (scale),
-                       (window), (layout.n_seqs), (layout.max_q_len), self._stream())
+                       _ptr(kv.block_table), kv.block_table.shape[1], kv.page,
+                       n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out),
+                       dtype_code(out.dtype), out.shape[1], scale,
+                       window, layout.n_seqs, layout.max_q_len, self._stream())
             return
         if (not layout.is_decode) and q_src.dtype == torch.float32 and \
                 self.lib.nb_attention_prefill_f32_supported(kv.head_dim, n_heads, kv.n_kv_heads, kv.page):
@@ -438,12 +438,12 @@ class CudaBackend:
                        n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out), dtype_code(out.dtype),
                        out.shape[1], scale, window, layout.n_seqs, layout.max_q_len, self._stream())
             return
-        self._call("nb_attention_generic", _ptr(q_src), (dtype_code(q_src.dtype)),
-                   (q_src.shape[1]), (q_col), _ptr(layout.row_slot), _ptr(layout.row_pos),
-                   _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), (kv.block_table.shape[1]),
-                   (kv.page), (n_heads), (kv.n_kv_heads), (kv.head_dim),
-                   _ptr(out), (dtype_code(out.dtype)), (out.shape[1]), (scale),
-                   (window), (n_rows), self._stream())
+        self._call("nb_attention_generic", _ptr(q_src), dtype_code(q_src.dtype),
+                   q_src.shape[1], q_col, _ptr(layout.row_slot), _ptr(layout.row_pos),
+                   _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1],
+                   kv.page, n_heads, kv.n_kv_heads, kv.head_dim,
+                   _ptr(out), dtype_code(out.dtype), out.shape[1], scale,
+                   window, n_rows, self._stream())
 
     def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
         """tokens <- next_tokens, row_pos += 1 for live rows (between two decode steps)."""
@@ -465,18 +465,18 @@ class CudaBackend:
                 s = (torch.zeros(max(n, 256), dtype=torch.int64, device=logits.device),
                      torch.zeros(max(n, 256), dtype=torch.int32, device=logits.device))
                 self._argmax_scratch[logits.device] = s
-            self._call("nb_argmax_split", _ptr(logits), (n), (v), _ptr(out), _ptr(s[0]),
-                       _ptr(s[1]), (n_ctas), self._stream())
+            self._call("nb_argmax_split", _ptr(logits), n, v, _ptr(out), _ptr(s[0]),
+                       _ptr(s[1]), n_ctas, self._stream())
             return
-        self._call("nb_argmax", _ptr(logits), (n), (v), _ptr(out), self._stream())
+        self._call("nb_argmax", _ptr(logits), n, v, _ptr(out), self._stream())
 
     def sample_temperature(self, logits, temperature, u, out):
         _check(logits, "logits", torch.float32, 2)
         _check(u, "u", torch.float64, 1)
         _check(out, "out", torch.int32, 1)
         n, v = logits.shape
-        self._call("nb_sample_temperature", _ptr(logits), (n), (v),
-                   (temperature), _ptr(u), _ptr(out), self._stream())
+        self._call("nb_sample_temperature", _ptr(logits), n, v,
+                   temperature, _ptr(u), _ptr(out), self._stream())
 
     def sample_top_k(self, logits, k, temperature, u, out):
         """Top-k sampling (no top-p) on the device: ``out[r]`` is drawn with ``u[r]`` among the
@@ -535,8 +535,8 @@ class CudaBackend:
         _check(history, "history", torch.int32, 2)
         _check(history_len, "history_len", torch.int32, 1)
         n, v = logits.shape
-        self._call("nb_repetition_penalty", _ptr(logits), (n), (v), _ptr(history),
-                   (history.shape[1]), _ptr(history_len), (penalty), self._stream())
+        self._call("nb_repetition_penalty", _ptr(logits), n, v, _ptr(history),
+                   history.shape[1], _ptr(history_len), penalty, self._stream())
 
 
 _backend = None
