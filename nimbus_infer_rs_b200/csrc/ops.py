@@ -10,7 +10,6 @@ installs :class:`CudaBackend`.
 """
 from __future__ import annotations
 
-import ctypes
 import os
 
 import torch

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from .. import models  # noqa: F401  (registers the architectures)
-from ..cache import PAGE, CacheError, SequenceCache, pages_for
+from ..cache import SequenceCache
 from ..config.registry import get_architecture, load_config
 from ..csrc import ops as ops_mod
 from ..sampling import BatchSampler, SamplingParams, SequenceSampler

@@ -11,8 +11,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import (INDEX, MATRIX, TABLE, VECTOR, ParamSpec, bind_params, build_part,
-                          collect_param_specs)
+from ..parts.base import ParamSpec, bind_params, build_part, collect_param_specs
 from ..parts.embedding import LMHead, TokenEmbedding
 from .spec import ModelSpec
 

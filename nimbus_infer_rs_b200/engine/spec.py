@@ -8,7 +8,7 @@ of that other layer instead of keeping its own.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 from ..parts.base import PartSpec
 

@@ -3,7 +3,6 @@ other than the engine's tiny models (odd widths, tails, several pages, grouped h
 import ctypes
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -2,7 +2,6 @@
 mixer with state of its own and a toy architecture around it are defined HERE, registered,
 built, loaded and stepped without any change to the package."""
 import json
-import math
 from dataclasses import dataclass
 
 import pytest

@@ -3,7 +3,6 @@ writing <step>.f32; the same requests replayed whole, token by token and in uneq
 must give the plain implementation's logits."""
 import json
 import subprocess
-import sys
 from pathlib import Path
 
 import numpy as np
