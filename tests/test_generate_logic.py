@@ -213,3 +213,47 @@ def test_splits_of_the_decode_attention():
     assert s(8, 16, heads=16) == 4 and s(12, 16, heads=16) == 2
     # without clusters up to 16 splits
     assert s(1, 64, most=16) == 16 and s(1, 64) == 8
+
+
+def test_every_row_of_a_packed_step_says_where_it_belongs():
+    """Any batch, any padding: row r of sequence i carries its token, the position
+    ``pos0[i] + offset`` and the sequence's slot; ``cu_rows`` cuts the rows into the sequences;
+    the wanted places point at rows of their own sequence; padding rows carry -1 / -1."""
+    from hypothesis import given, settings, strategies as st
+
+    from nimbus_infer_rs_b200.engine.batch import pack_step
+
+    seq = st.tuples(st.integers(0, 500), st.lists(st.integers(0, 50_000), min_size=1, max_size=40),
+                    st.integers(0, 900), st.data())
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.lists(seq, min_size=1, max_size=9), st.sampled_from([1, 8, 64]))
+    def check(seqs, pad):
+        entries, pos0 = [], []
+        for slot, toks, p0, data in seqs:
+            wants = data.draw(st.lists(st.integers(0, len(toks) - 1), max_size=4))
+            entries.append((slot, toks, wants))
+            pos0.append(p0)
+        p = pack_step(entries, pos0, pad_rows_to=pad)
+        tokens, row_pos, row_slot, cu_rows, seq_slot, seq_pos0, want = (
+            p.buf[p.offs[i]:p.offs[i + 1]] for i in range(7))
+        n = sum(len(e[1]) for e in entries)
+        assert p.n_tokens == n and p.n_rows % pad == 0 and 0 <= p.n_rows - n < pad
+        assert list(tokens[n:]) == [-1] * (p.n_rows - n) == list(row_slot[n:])
+        assert cu_rows[0] == 0 and cu_rows[-1] == n and len(cu_rows) == len(entries) + 1
+        w = 0
+        for i, (slot, toks, wants) in enumerate(entries):
+            lo, hi = cu_rows[i], cu_rows[i + 1]
+            assert hi - lo == len(toks) and list(tokens[lo:hi]) == toks
+            assert list(row_pos[lo:hi]) == list(range(pos0[i], pos0[i] + len(toks)))
+            assert set(row_slot[lo:hi]) == {slot} and seq_slot[i] == slot and seq_pos0[i] == pos0[i]
+            for x in wants:
+                assert want[w] == lo + x
+                w += 1
+        assert w == p.n_want == len(want)
+        assert p.max_q_len == max(len(e[1]) for e in entries)
+        assert p.max_kv_len == max(a + len(e[1]) for a, e in zip(pos0, entries))
+        assert p.is_decode == all(len(e[1]) == 1 for e in entries)
+        assert p.want_all_rows == (list(want) == list(range(p.n_rows)))
+
+    check()
