@@ -64,3 +64,28 @@ def test_no_restrict_on_step_data_in_kernels_that_start_early():
                     pname = p.strip().split()[-1]
                     assert pname in CONSTANT_PARAMS, f"{path.name}: {name}({pname}) is __restrict__"
     assert checked >= 15
+
+
+def test_the_cpu_stand_in_has_the_signatures_of_the_cuda_backend():
+    """The host-logic tests run the engine on `tests/cpu_backend.py`; what they prove about the
+    engine holds on the GPU only if both backends are called the same way."""
+    import inspect
+
+    import cpu_backend
+    from nimbus_infer_rs_b200.csrc.ops import CudaBackend
+
+    stand_in = next(c for _, c in inspect.getmembers(cpu_backend, inspect.isclass)
+                    if c.__module__ == cpu_backend.__name__ and hasattr(c, "linear"))
+    checked = 0
+    for name, fn in inspect.getmembers(stand_in, inspect.isfunction):
+        if name.startswith("_"):
+            continue
+        real = getattr(CudaBackend, name, None)
+        assert real is not None, f"CudaBackend has no method {name}"
+        mine, theirs = inspect.signature(fn), inspect.signature(real)
+        assert list(mine.parameters) == list(theirs.parameters), name
+        for k, p in mine.parameters.items():
+            q = theirs.parameters[k]
+            assert (p.default is inspect.Parameter.empty) == (q.default is inspect.Parameter.empty), (name, k)
+        checked += 1
+    assert checked >= 12
