@@ -89,3 +89,31 @@ def test_the_cpu_stand_in_has_the_signatures_of_the_cuda_backend():
             assert (p.default is inspect.Parameter.empty) == (q.default is inspect.Parameter.empty), (name, k)
         checked += 1
     assert checked >= 12
+
+
+def test_every_call_into_the_library_passes_as_many_arguments_as_declared():
+    """ctypes would take a call with an argument too few or too many and the kernel would read
+    what lies beside them; count the arguments of every ``_call("nb_...", ...)`` and
+    ``lib.nb_...(...)`` in the package against the declared signatures."""
+    import ast
+
+    root = Path(csrc_pkg.__file__).parent.parent
+    seen = set()
+    for path in sorted(root.rglob("*.py")):
+        for node in ast.walk(ast.parse(path.read_text())):
+            if not isinstance(node, ast.Call) or any(isinstance(a, ast.Starred) for a in node.args):
+                continue
+            f = node.func
+            if isinstance(f, ast.Attribute) and f.attr == "_call" and node.args \
+                    and isinstance(node.args[0], ast.Constant):
+                name, n = node.args[0].value, len(node.args) - 1
+            elif isinstance(f, ast.Attribute) and f.attr.startswith("nb_"):
+                name, n = f.attr, len(node.args)
+            else:
+                continue
+            if name in OTHER:
+                continue
+            assert name in SIGNATURES, f"{path.name}:{node.lineno}: {name} is not declared"
+            assert n == len(SIGNATURES[name]), f"{path.name}:{node.lineno}: {name} takes {len(SIGNATURES[name])}"
+            seen.add(name)
+    assert len(seen) >= 30
