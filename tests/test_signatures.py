@@ -115,5 +115,11 @@ def test_every_call_into_the_library_passes_as_many_arguments_as_declared():
                 continue
             assert name in SIGNATURES, f"{path.name}:{node.lineno}: {name} is not declared"
             assert n == len(SIGNATURES[name]), f"{path.name}:{node.lineno}: {name} takes {len(SIGNATURES[name])}"
+            # and a pointer stands exactly where a pointer is declared
+            for kind, arg in zip(SIGNATURES[name], node.args[len(node.args) - n:]):
+                pointer = isinstance(arg, ast.Call) and (
+                    isinstance(arg.func, ast.Name) and arg.func.id == "_ptr"
+                    or isinstance(arg.func, ast.Attribute) and arg.func.attr in ("_stream", "data_ptr", "byref"))
+                assert pointer == (kind == "p"), f"{path.name}:{node.lineno}: {name}: {ast.unparse(arg)}"
             seen.add(name)
     assert len(seen) >= 30
