@@ -4,10 +4,10 @@ Every kernel of a step reads the batch (tokens, positions, slots, block tables) 
 memory, and no launch shape depends on anything but the step's *shape*: how many rows,
 sequences and wanted places it has, its longest chunk, and (for one-token steps) the range
 its longest sequence falls in.  Rows (beyond 64) and the longest chunk are rounded up to
-multiples of 64 and 128, so that prompts of nearly the same lengths fall into one shape.  So the launches of a step can be recorded once and replayed
-for every later step of the same shape, whatever its tokens, slots and lengths: the host then
-issues one graph launch instead of about a hundred kernel launches, and stays ahead of the
-GPU.  A shape is recorded when it comes for the second time (the first run is plain and has
+multiples of 64 and 128, so that prompts of nearly the same lengths fall into one shape.  So
+the launches of a step can be recorded once and replayed for every later step of the same
+shape, whatever its tokens, slots and lengths: the host then issues one graph launch instead
+of about a hundred kernel launches, and stays ahead of the GPU.  A shape is recorded when it comes for the second time (the first run is plain and has
 warmed every kernel it needs); a bounded number of graphs is kept, the least recently used
 one goes first.
 

@@ -257,3 +257,59 @@ def test_every_row_of_a_packed_step_says_where_it_belongs():
         assert p.want_all_rows == (list(want) == list(range(p.n_rows)))
 
     check()
+
+
+def test_when_a_step_is_recorded_replayed_and_forgotten():
+    """engine/step_graphs.py: a shape runs plainly at first sight, is recorded at the second
+    and replayed from then on; the least recently used recording goes when there are more than
+    `capacity`; steps whose logits would be large, and everything with capacity 0, run plainly.
+    (The recording itself is stubbed: this is about the decisions around it.)"""
+    from types import SimpleNamespace
+
+    from nimbus_infer_rs_b200.engine.batch import pack_step
+    from nimbus_infer_rs_b200.engine.step_graphs import StepGraphs
+
+    class Owner:
+        spec = SimpleNamespace(max_seq_len=1024, vocab_size=100)
+        rt = SimpleNamespace(device=torch.device("cpu"))
+        ops = SimpleNamespace(launches=0)
+    owner = Owner()
+
+    class Recorder(StepGraphs):
+        def _record(self, p, key):
+            entry = {"graph": SimpleNamespace(replay=lambda: replayed.append(key)),
+                     "buf": torch.empty(p.buf.size, dtype=torch.int32),
+                     "logits": torch.zeros(p.n_want, 100), "launches": 7}
+            self._graphs[key] = entry
+            self.captures += 1
+            while len(self._graphs) > self.capacity:
+                self._graphs.popitem(last=False)
+            return entry
+
+    replayed = []
+    g = Recorder(owner, capacity=2)
+    def step(n_seqs, tokens=5):
+        return pack_step([(i, [tokens], [0]) for i in range(n_seqs)], [3] * n_seqs)
+    assert g.run(step(1)) == (False, None) and g.captures == 0          # first sight
+    ok, logits = g.run(step(1, tokens=9))                                 # second: recorded, replayed
+    assert ok and logits.shape == (1, 100) and g.captures == 1 and len(replayed) == 1
+    assert owner.ops.launches == 7                                        # the recording's launches count
+    ok, _ = g.run(step(1))
+    assert ok and g.captures == 1 and g.replays == 2 and owner.ops.launches == 14
+    # the replayed step read this step's batch: the buffer holds its tokens
+    entry = next(iter(g._graphs.values()))
+    assert entry["buf"][0] == 5
+    for n in (2, 3):                                                      # two more shapes
+        assert g.run(step(n)) == (False, None)
+        assert g.run(step(n))[0]
+    assert g.captures == 3 and len(g._graphs) == 2                        # the first one is gone
+    assert g.key(step(1)) not in g._graphs and g.key(step(3)) in g._graphs
+    assert g.run(step(2))[0] and g.captures == 3                          # still there: replayed
+    assert g.run(step(1))[0] and g.captures == 4                          # seen before: recorded anew
+    assert g.key(step(3)) not in g._graphs                                # 2 was used after 3
+    # large logits stay out of graphs; capacity 0 switches recording off
+    big = Recorder(owner, capacity=2, max_logit_bytes=100 * 4)
+    two = pack_step([(0, [1, 2], [0, 1])], [0])
+    assert big.run(two) == (False, None) and big.run(two) == (False, None) and big.captures == 0
+    off = Recorder(owner, capacity=0)
+    assert off.run(step(1)) == (False, None) and off.run(step(1)) == (False, None)
