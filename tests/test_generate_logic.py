@@ -313,3 +313,31 @@ def test_when_a_step_is_recorded_replayed_and_forgotten():
     assert big.run(two) == (False, None) and big.run(two) == (False, None) and big.captures == 0
     off = Recorder(owner, capacity=0)
     assert off.run(step(1)) == (False, None) and off.run(step(1)) == (False, None)
+
+
+def test_generation_across_page_ends_with_a_row_that_stops_on_the_way(model_dirs, cpu_backend):
+    """The decode session's bookkeeping on the host: prompts of 40 and 61 tokens cross a page
+    end (64 tokens) while they decode, one of 64 starts its second page with its first new
+    token, one of 70 stays inside it; one stops early and its row is retired while the others
+    go on; a second batch of the same size finds the first one's kept buffers; grouped heads
+    (tiny C).  All pages and slots come back."""
+    W = P.PlainWeights(model_dirs["C"])
+    eng = Engine.load(model_dirs["C"], dtype="float32", device="cpu", cache_tokens=12 * 64, n_slots=4)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 777, (n,), generator=g).tolist() for n in (40, 61, 64, 70)]
+    free_run = [P.greedy_generate(W, p, 30) for p in prompts]
+    stop = free_run[1][5]                                   # request 1 ends inside its second page
+    params = SamplingParams(max_new_tokens=30, temperature=0.0, stop_tokens=[stop])
+    # greedy tokens depend on nothing but what came before: a run with a stop token is the
+    # free run up to and with the first stop
+    want = [r[:r.index(stop) + 1] if stop in r else r for r in free_run]
+    assert len(want[1]) <= 6 and max(len(w) for w in want) == 30
+    assert eng.generate(prompts, params) == want
+    assert eng.cache.slots.n_free == 4
+    assert all(gr.pool.n_free == gr.pool.n_pages for gr in eng.cache.groups)
+    # the same batch size again, other lengths: the kept session state is found and reset
+    prompts2 = [p[:n] for p, n in zip(prompts[::-1], (66, 2, 63, 1))]
+    want2 = [P.greedy_generate(W, p, 9) for p in prompts2]
+    assert eng.generate(prompts2, SamplingParams(max_new_tokens=9, temperature=0.0)) == want2
+    assert eng.cache.slots.n_free == 4
+    assert all(gr.pool.n_free == gr.pool.n_pages for gr in eng.cache.groups)
